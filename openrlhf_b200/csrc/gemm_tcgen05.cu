@@ -1,0 +1,367 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands staged by TMA).
+//
+//   C[M,N] (+)= alpha * op(A)[M,K] * op(B)[K,N]  (+ bias[N]) (+ residual[M,N])
+//
+// Persistent, warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2..5 = epilogue.
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop of tile i+1.
+// Operand layouts (all row-major tensors in global memory):
+//   A_MN = false: A is [M,K] (K contiguous)     A_MN = true: A is [K,M] (M contiguous, i.e. A^T is used)
+//   B_MN = false: B is [N,K] (K contiguous)     B_MN = true: B is [K,N] (N contiguous)
+// which covers forward (Y = X W^T), dgrad (dX = dY W) and wgrad (dW = dY^T X) of a linear layer without
+// materialising a transpose. Replaces the cuBLAS calls behind nn.Linear in the reference
+// (openrlhf/models/actor.py:149-157 instantiates HF models whose projections are nn.Linear).
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;   // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+
+struct GemmParams {
+  void* C;               // bf16 or fp32, row-major, leading dimension ldc (elements)
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ldc] or null (bf16 outputs only)
+  int M, N, K;
+  int ldc;
+  int out_f32;     // 1: C is fp32
+  int accumulate;  // 1: C += result (fp32 outputs only; uses red.add so split-K tiles may overlap)
+  int k_splits;    // >1 requires out_f32 && accumulate
+  float alpha;
+  int* status;     // device status word (0 = ok)
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int STAGES = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (p.M + BM - 1) / BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int kb_per_split = (kb_total + splits - 1) / splits;
+  const int num_tiles = m_blocks * n_blocks * splits;
+  constexpr int GROUP_M = 16;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+    int split = tile % splits;
+    int t = tile / splits;
+    int per_group = GROUP_M * n_blocks;
+    int g = t / per_group;
+    int first_m = g * GROUP_M;
+    int gsz = min(m_blocks - first_m, GROUP_M);
+    int r = t % per_group;
+    m_blk = first_m + r % gsz;
+    n_blk = r / gsz;
+    kb0 = split * kb_per_split;
+    kb1 = min(kb_total, kb0 + kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk, kb0, kb1;
+        tile_coords(tile, m_blk, n_blk, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, m_blk * BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (BK * 128), &tma_a, &full_bar[stage], m_blk * BM + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, n_blk * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tma_b, &full_bar[stage], n_blk * BN + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        int m_blk, n_blk, kb0, kb1;
+        tile_coords(tile, m_blk, n_blk, kb0, kb1);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: advance 32 B inside the 128 B swizzle row. MN-major: advance 16 k-rows of 128 B.
+            uint64_t adesc = A_MN ? make_smem_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                                  : make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                  : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int m_blk, n_blk, kb0, kb1;
+      tile_coords(tile, m_blk, n_blk, kb0, kb1);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      const bool has_work = kb1 > kb0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * BN + c * 32;
+        if (row_ok && has_work && col0 < p.N) {
+          if (p.out_f32) {
+            float* crow = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  atomicAdd(crow + j, v.x);
+                  atomicAdd(crow + j + 1, v.y);
+                  atomicAdd(crow + j + 2, v.z);
+                  atomicAdd(crow + j + 3, v.w);
+                } else {
+                  *reinterpret_cast<float4*>(crow + j) = v;
+                }
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                float v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]) * p.alpha;
+                if (p.bias != nullptr) {
+                  uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
+                  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float2 f = __bfloat1622float2(b2[q]);
+                    v[2 * q] += f.x;
+                    v[2 * q + 1] += f.y;
+                  }
+                }
+                if (p.residual != nullptr) {
+                  uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldc + col0 + j);
+                  const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float2 f = __bfloat1622float2(r2[q]);
+                    v[2 * q] += f.x;
+                    v[2 * q + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // Teardown. After an error some TMA copies may still be in flight towards this CTA's shared memory:
+  // give them a bounded grace period before the CTA retires.
+  __syncwarp();
+  if (p.status != nullptr && *(volatile int*)p.status != 0) {
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with `ld` elements between rows; box = [box_rows, 64].
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return -2;
+    configured = true;
+  }
+  int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
+  int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1);
+  int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static int g_sm_count = 0;
+
+// C-callable entry point. a_mn / b_mn select the operand layouts documented at the top of this file.
+// lda / ldb are the row strides (elements) of the tensors as they sit in memory. Returns 0 on a successful launch.
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                              int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
+                              int accumulate, int k_splits, float alpha, int bn, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8)) || (N % (out_f32 ? 4 : 8))) return -10;
+  if (k_splits > 1 && !(out_f32 && accumulate)) return -11;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -12;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (bn != 64 && bn != 128 && bn != 256) bn = (N >= 2048 || (long long)M * N >= (long long)128 * 256 * 148) ? 256 : (N >= 512 ? 128 : 64);
+  CUtensorMap ta, tb;
+  int r;
+  // K-major operands: box = 64 (K) x tile rows. MN-major operands: box = 64 (M/N) x 64 (K) per chunk.
+  if (!a_mn) r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
+  else r = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, 64);
+  if (r) return r;
+  if (!b_mn) r = make_tmap_bf16_2d(&tb, B, N, K, ldb, bn, BK);
+  else r = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, 64);
+  if (r) return r;
+  GemmParams p;
+  p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.out_f32 = out_f32; p.accumulate = accumulate; p.k_splits = k_splits; p.alpha = alpha; p.status = status;
+#define B200_DISPATCH(BN_)                                                                  \
+  if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, g_sm_count, stream);     \
+  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, g_sm_count, stream);       \
+  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, p, g_sm_count, stream);       \
+  return launch<BN_, true, true>(ta, tb, p, g_sm_count, stream);
+  if (bn == 256) { B200_DISPATCH(256) }
+  if (bn == 128) { B200_DISPATCH(128) }
+  B200_DISPATCH(64)
+#undef B200_DISPATCH
+}

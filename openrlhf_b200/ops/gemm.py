@@ -1,0 +1,70 @@
+"""bf16 GEMM on tcgen05 tensor cores and the autograd ``linear`` built from it.
+
+``gemm`` maps one-to-one onto the kernel in ``csrc/gemm_tcgen05.cu``; ``linear`` is what the model code calls in
+place of ``nn.Linear`` (the reference's projections are HF ``nn.Linear`` modules: openrlhf/models/actor.py:149-157).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    out_f32: bool = False,
+    accumulate: bool = False,
+    k_splits: int = 1,
+    alpha: float = 1.0,
+    bn: int = 0,
+) -> torch.Tensor:
+    """C[M,N] (+)= alpha * op(A) @ op(B) with bf16 inputs and fp32 accumulation.
+
+    a_mn=False: ``a`` is [M,K]; a_mn=True: ``a`` is [K,M] (its transpose is used).
+    b_mn=False: ``b`` is [N,K]; b_mn=True: ``b`` is [K,N].
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+        if accumulate:
+            out.zero_()
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+        out_f32 = out.dtype == torch.float32
+    if M == 0 or N == 0:
+        return out
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and not out_f32
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and not out_f32
+        assert residual.stride(0) == out.stride(0)
+    st = _lib.status_word(a.device)
+    rc = _lib.lib().b200_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)),
+        ctypes.c_int(int(accumulate)), ctypes.c_int(int(k_splits)), ctypes.c_float(alpha), ctypes.c_int(bn),
+        _lib.ptr(st), _lib.stream_ptr(),
+    )
+    _lib.check_rc(rc, "b200_gemm_bf16")
+    return out
