@@ -1,0 +1,272 @@
+// Token sampler for the rollout engine: temperature, top-k, top-p, Gumbel-max draw and the log-prob of the drawn
+// token under the processed distribution, one CTA per sequence, Philox streams keyed by (seed, sequence, step).
+// Stands in for vLLM's sampler as configured by the reference (SamplingParams with temperature / top_p / top_k and
+// logprobs of the sampled token: openrlhf/trainer/ppo_utils/samples_generator.py:203-211,
+// openrlhf/trainer/ray/vllm_engine.py:295-300 selects "processed_logprobs").
+#include <curand_kernel.h>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+template <typename T>
+__device__ __forceinline__ float load_logit(const T* p, int i);
+template <>
+__device__ __forceinline__ float load_logit<float>(const float* p, int i) { return p[i]; }
+template <>
+__device__ __forceinline__ float load_logit<__nv_bfloat16>(const __nv_bfloat16* p, int i) { return __bfloat162float(p[i]); }
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = threadIdx.x < 32 ? red[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+    t = warp_sum(t);
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = threadIdx.x < 32 ? red[threadIdx.x] : -INFINITY;
+  if (threadIdx.x < 32) {
+    t = warp_max(t);
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restrict__ temperature, float temp_scalar,
+              int top_k, float top_p, unsigned long long seed, const long long* __restrict__ step_ptr,
+              long long step_scalar, long long* __restrict__ out_tok, float* __restrict__ out_logp,
+              const int* __restrict__ active) {
+  __shared__ float red[32];
+  __shared__ float s_best[32];
+  __shared__ int s_idx[32];
+  const int row = blockIdx.x;
+  if (active != nullptr && active[row] == 0) return;
+  const T* z = logits + (size_t)row * ld;
+  const float temp = temperature ? temperature[row] : temp_scalar;
+  const bool greedy = temp <= 1e-6f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  const long long step = step_ptr ? *step_ptr : step_scalar;
+
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, load_logit(z, i));
+  mx = block_reduce_max(mx, red);
+
+  // threshold in x = (z - max) * inv_t space; keep x >= thr
+  float thr = -INFINITY;
+  if (!greedy && ((top_k > 0 && top_k < V) || top_p < 1.f)) {
+    float lo_u = 0.f;  // keep-set threshold in u = exp(x) in [0, 1]
+    if (top_k > 0 && top_k < V) {
+      float lo = 0.f, hi = 1.f;
+      for (int it = 0; it < 26; ++it) {
+        const float mid = 0.5f * (lo + hi);
+        float c = 0.f;
+        for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS)
+          c += (__expf((load_logit(z, i) - mx) * inv_t) >= mid) ? 1.f : 0.f;
+        c = block_reduce_sum(c, red);
+        if (c >= (float)top_k) lo = mid; else hi = mid;
+      }
+      lo_u = lo;
+    }
+    if (top_p < 1.f) {
+      float mass_all = 0.f;
+      for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+        const float u = __expf((load_logit(z, i) - mx) * inv_t);
+        mass_all += (u >= lo_u) ? u : 0.f;
+      }
+      mass_all = block_reduce_sum(mass_all, red);
+      const float target = top_p * mass_all;
+      float lo = lo_u, hi = 1.f;
+      for (int it = 0; it < 26; ++it) {
+        const float mid = 0.5f * (lo + hi);
+        float m = 0.f;
+        for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+          const float u = __expf((load_logit(z, i) - mx) * inv_t);
+          m += (u >= mid) ? u : 0.f;
+        }
+        m = block_reduce_sum(m, red);
+        if (m >= target) lo = mid; else hi = mid;
+      }
+      lo_u = lo;
+    }
+    thr = lo_u > 0.f ? __logf(lo_u) : -INFINITY;
+  }
+
+  curandStatePhilox4_32_10_t rng;
+  if (!greedy) curand_init(seed, (unsigned long long)row * SAMPLE_THREADS + threadIdx.x, (unsigned long long)step * 256ull, &rng);
+  float sum = 0.f, best = -INFINITY;
+  int best_i = 0x7fffffff;
+  float4 u4 = make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+  int k = 0;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS, ++k) {
+    const float x = (load_logit(z, i) - mx) * inv_t;
+    const bool keep = x >= thr;
+    float key = x;
+    if (!greedy) {
+      if ((k & 3) == 0) u4 = curand_uniform4(&rng);
+      const float u = (k & 3) == 0 ? u4.x : ((k & 3) == 1 ? u4.y : ((k & 3) == 2 ? u4.z : u4.w));
+      key = x - __logf(-__logf(u));  // Gumbel noise
+    }
+    if (keep) {
+      sum += __expf(x);
+      if (key > best || (key == best && i < best_i)) { best = key; best_i = i; }
+    }
+  }
+  sum = block_reduce_sum(sum, red);
+  // argmax over the block
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = s_best[threadIdx.x];
+    best_i = s_idx[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+    }
+    if (threadIdx.x == 0) {
+      out_tok[row] = best_i;
+      if (out_logp) {
+        // greedy reports the log-prob under temperature 1 (sum was computed with inv_t = 1 in that case)
+        out_logp[row] = (load_logit(z, best_i) - mx) * inv_t - __logf(sum);
+      }
+    }
+  }
+}
+
+// Log-prob of given tokens under softmax(logits / T): out[t] = z[t, y_t]/T - logsumexp(z[t,:]/T), and optionally the
+// entropy of softmax(z) (untempered, as in openrlhf/models/actor.py:269-285). One CTA per row.
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+logprob_rows_kernel(const T* __restrict__ logits, int ld, int V, const long long* __restrict__ labels, float inv_t,
+                    float* __restrict__ out_logp, float* __restrict__ out_entropy, float* __restrict__ out_lse) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const T* z = logits + (size_t)row * ld;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, load_logit(z, i));
+  mx = block_reduce_max(mx, red);
+  float s = 0.f, s1 = 0.f, sz = 0.f;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+    const float v = load_logit(z, i) - mx;
+    s += __expf(v * inv_t);
+    if (out_entropy) {
+      const float e = __expf(v);
+      s1 += e;
+      sz += e * v;
+    }
+  }
+  s = block_reduce_sum(s, red);
+  if (out_entropy) {
+    s1 = block_reduce_sum(s1, red);
+    sz = block_reduce_sum(sz, red);
+  }
+  if (threadIdx.x == 0) {
+    long long y = labels[row];
+    y = y < 0 ? 0 : (y >= V ? V - 1 : y);
+    out_logp[row] = (load_logit(z, (int)y) - mx) * inv_t - __logf(s);
+    if (out_lse) out_lse[row] = mx * inv_t + __logf(s);
+    if (out_entropy) out_entropy[row] = __logf(s1) - sz / s1;
+  }
+}
+
+
+// In place on bf16 logits: z <- g * inv_t * (onehot(label) - softmax(z * inv_t)); lse = logsumexp(z * inv_t) per row.
+__global__ void __launch_bounds__(256)
+logprob_bwd_rows_kernel(__nv_bfloat16* __restrict__ logits, int T, int V, int ld, const long long* __restrict__ labels,
+                        const float* __restrict__ lse_in, const float* __restrict__ dlogp, float inv_t) {
+  const int nvec = V >> 3;
+  const long long total = (long long)T * nvec;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / nvec), v = (int)(idx % nvec);
+    long long y = labels[t];
+    y = y < 0 ? 0 : (y >= V ? V - 1 : y);
+    __nv_bfloat16* row = logits + (size_t)t * ld;
+    const float lse = lse_in[t];
+    const float g = dlogp[t] * inv_t;
+    uint4 u = reinterpret_cast<uint4*>(row)[v];
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h2[i]);
+      o[2 * i] = -g * __expf(f.x * inv_t - lse);
+      o[2 * i + 1] = -g * __expf(f.y * inv_t - lse);
+    }
+    const int c0 = v * 8;
+    if (y >= c0 && y < c0 + 8) o[y - c0] += g;
+    uint4 w;
+    w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]); w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+    reinterpret_cast<uint4*>(row)[v] = w;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_sample(const void* logits, int is_bf16, int B, int V, int ld, const float* temperature,
+                           float temp_scalar, int top_k, float top_p, unsigned long long seed,
+                           const long long* step_ptr, long long step_scalar, long long* out_tok, float* out_logp,
+                           const int* active, void* stream_) {
+  if (B <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (is_bf16)
+    sample_kernel<__nv_bfloat16><<<B, SAMPLE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, ld, V, temperature,
+                                                               temp_scalar, top_k, top_p, seed, step_ptr, step_scalar,
+                                                               out_tok, out_logp, active);
+  else
+    sample_kernel<float><<<B, SAMPLE_THREADS, 0, st>>>((const float*)logits, ld, V, temperature, temp_scalar, top_k,
+                                                       top_p, seed, step_ptr, step_scalar, out_tok, out_logp, active);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_logprob_rows(const void* logits, int is_bf16, int T, int V, int ld, const long long* labels,
+                                 float temperature, float* out_logp, float* out_entropy, float* out_lse, void* stream_) {
+  if (T <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  const float inv_t = 1.f / temperature;
+  if (is_bf16)
+    logprob_rows_kernel<__nv_bfloat16><<<T, SAMPLE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, ld, V, labels, inv_t,
+                                                                     out_logp, out_entropy, out_lse);
+  else
+    logprob_rows_kernel<float><<<T, SAMPLE_THREADS, 0, st>>>((const float*)logits, ld, V, labels, inv_t, out_logp,
+                                                             out_entropy, out_lse);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_logprob_bwd_rows(void* logits, int T, int V, int ld, const long long* labels, const float* lse,
+                                     const float* dlogp, float inv_t, void* stream_) {
+  if (T <= 0) return 0;
+  if (V % 8 || ld % 8) return -10;
+  long long work = (long long)T * (V / 8);
+  long long blocks = (work + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  logprob_bwd_rows_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      (__nv_bfloat16*)logits, T, V, ld, labels, lse, dlogp, inv_t);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,300 @@
+"""Autograd-aware operator API used by the model code.
+
+Every op dispatches on the device of its input: CUDA tensors run the sm_100a kernels of ``csrc/``; CPU tensors run
+the plain PyTorch restatement in ``ops/reference.py`` (that path exists for the CPU oracle and the unit tests).
+Weight gradients are accumulated in fp32 straight into ``param.main_grad`` when the parameter carries that attribute
+(set by the ZeRO engine), which fuses gradient accumulation into the wgrad GEMM epilogue.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib, reference
+from .gemm import gemm
+
+_c_int = ctypes.c_int
+_c_ll = ctypes.c_longlong
+_c_f = ctypes.c_float
+
+
+def _L():
+    return _lib.lib()
+
+
+def _acc_grad(param: torch.Tensor, grad_fn):
+    """Accumulate a gradient into param.main_grad (fp32) if present, else return it for autograd."""
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        grad_fn(mg)
+        return None
+    buf = torch.zeros(param.shape, dtype=torch.float32, device=param.device)
+    grad_fn(buf)
+    return buf.to(param.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- linear
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.bias_ref = bias
+        ctx.w_ref = w
+        return gemm(x, w, bias=bias, residual=residual)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            T = x.shape[0]
+            tiles = ((w.shape[0] + 127) // 128) * ((w.shape[1] + 255) // 256)
+            splits = max(1, min(8, 148 // max(tiles, 1), T // 512)) if tiles < 148 else 1
+            dw = _acc_grad(ctx.w_ref, lambda buf: gemm(dy, x, a_mn=True, b_mn=True, out=buf, accumulate=True,
+                                                      k_splits=splits))
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _acc_grad(ctx.bias_ref, lambda buf: buf.add_(dy.float().sum(0)))
+        dres = dy if ctx.has_res and ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ w.T (+ bias) (+ residual); x [T, K], w [N, K]."""
+    if not x.is_cuda:
+        return reference.linear(x, w, bias, residual)
+    return _Linear.apply(x, w, bias, residual)
+
+
+# ---------------------------------------------------------------------------------------------- RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        T, H = x.shape
+        y = torch.empty_like(x)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        rc = _L().b200_rmsnorm_fwd(_lib.ptr(x), None, _lib.ptr(w), _lib.ptr(y), None, _lib.ptr(rstd), _c_int(T),
+                                   _c_int(H), _c_int(x.stride(0)), _c_int(y.stride(0)), _c_f(eps), _lib.stream_ptr())
+        _lib.check_rc(rc, "rmsnorm_fwd")
+        ctx.save_for_backward(x, w, rstd)
+        ctx.w_ref = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        xc = x.contiguous()
+        T, H = xc.shape
+        dx = torch.empty_like(xc)
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        dw_buf = mg if mg is not None else torch.zeros(H, dtype=torch.float32, device=x.device)
+        rc = _L().b200_rmsnorm_bwd(_lib.ptr(xc), _lib.ptr(w), _lib.ptr(dy), _lib.ptr(rstd), None, _lib.ptr(dx),
+                                   _lib.ptr(dw_buf), _c_int(T), _c_int(H), _lib.stream_ptr())
+        _lib.check_rc(rc, "rmsnorm_bwd")
+        return dx, (None if mg is not None else dw_buf.to(w.dtype)), None
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    if not x.is_cuda:
+        return reference.rmsnorm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+# ---------------------------------------------------------------------------------------------- RoPE
+_rope_tables: dict = {}
+
+
+def rope_table(head_dim: int, theta: float, max_pos: int, device) -> torch.Tensor:
+    """[max_pos, head_dim/2, 2] fp32 (cos, sin), rounded through bf16 like the HF rotary module's outputs."""
+    key = (head_dim, float(theta), int(max_pos), str(device))
+    tab = _rope_tables.get(key)
+    if tab is None:
+        inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+        ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+        tab = torch.stack([ang.cos(), ang.sin()], dim=-1).to(torch.bfloat16).float().contiguous()
+        _rope_tables[key] = tab
+    return tab
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, pos, table, n_heads, head_dim):
+        out = qkv.clone()
+        _rope_inplace(out, pos, table, n_heads, head_dim, 1.0)
+        ctx.save_for_backward(pos, table)
+        ctx.n_heads, ctx.head_dim = n_heads, head_dim
+        return out
+
+    @staticmethod
+    def backward(ctx, d):
+        pos, table = ctx.saved_tensors
+        d = d.clone()
+        _rope_inplace(d, pos, table, ctx.n_heads, ctx.head_dim, -1.0)
+        return d, None, None, None, None
+
+
+def _rope_inplace(qkv, pos, table, n_heads, head_dim, sign):
+    T = qkv.shape[0]
+    rc = _L().b200_rope(_lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(table), _c_int(T), _c_int(n_heads), _c_int(head_dim),
+                        _c_int(qkv.stride(0)), _c_f(sign), _c_int(table.shape[0]), _lib.stream_ptr())
+    _lib.check_rc(rc, "rope")
+
+
+def rope(qkv: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, n_heads: int, head_dim: int) -> torch.Tensor:
+    """Rotate the first ``n_heads`` heads (q heads then k heads) of every row of qkv [T, *]; pos is int32 [T]."""
+    if not qkv.is_cuda:
+        return reference.rope(qkv, pos, table, n_heads, head_dim)
+    return _Rope.apply(qkv, pos, table, n_heads, head_dim)
+
+
+# ---------------------------------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        T, F2 = gu.shape
+        y = torch.empty(T, F2 // 2, dtype=gu.dtype, device=gu.device)
+        rc = _L().b200_swiglu_fwd(_lib.ptr(gu), _lib.ptr(y), _c_ll(T), _c_int(F2 // 2), _lib.stream_ptr())
+        _lib.check_rc(rc, "swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dgu = torch.empty_like(gu)
+        rc = _L().b200_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dy), _lib.ptr(dgu), _c_ll(gu.shape[0]),
+                                  _c_int(gu.shape[1] // 2), _lib.stream_ptr())
+        _lib.check_rc(rc, "swiglu_bwd")
+        return dgu
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """silu(gu[:, :F]) * gu[:, F:]"""
+    if not gu.is_cuda:
+        return reference.swiglu(gu)
+    return _SwiGLU.apply(gu.contiguous())
+
+
+# ---------------------------------------------------------------------------------------------- embedding
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        T = ids.numel()
+        V, H = table.shape
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+        rc = _L().b200_embedding_fwd(_lib.ptr(ids), _lib.ptr(table), _lib.ptr(out), _c_int(T), _c_int(H), _c_int(V),
+                                     _lib.stream_ptr())
+        _lib.check_rc(rc, "embedding_fwd")
+        ctx.save_for_backward(ids)
+        ctx.table_ref = table
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        table = ctx.table_ref
+        V, H = table.shape
+        dout = dout.contiguous()
+
+        def fn(buf):
+            rc = _L().b200_embedding_bwd(_lib.ptr(ids), _lib.ptr(dout), _lib.ptr(buf), _c_int(ids.numel()), _c_int(H),
+                                         _c_int(V), _lib.stream_ptr())
+            _lib.check_rc(rc, "embedding_bwd")
+
+        return None, _acc_grad(table, fn)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if not table.is_cuda:
+        return reference.embedding(ids, table)
+    return _Embedding.apply(ids.contiguous().long(), table)
+
+
+# ---------------------------------------------------------------------------------------------- attention
+def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
+                     scale: float | None = None) -> torch.Tensor:
+    """Causal attention over a packed token stream. q [T,Hq,D], k/v [T,Hkv,D], cu_seqlens int32 [n+1]."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    if not q.is_cuda:
+        return reference.attention_varlen(q, k, v, cu_seqlens, scale)
+    from .attention import attention_varlen_cuda
+
+    return attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale)
+
+
+# ---------------------------------------------------------------------------------------------- LM head -> log-probs
+class _FusedLogprob(torch.autograd.Function):
+    """log p(label) (and optionally entropy) per token from hidden states, vocabulary streamed in row chunks so the
+    full [T, V] logits never exist; backward recomputes each chunk."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, temperature, want_entropy, chunk):
+        T = h.shape[0]
+        V = w.shape[0]
+        logp = torch.empty(T, dtype=torch.float32, device=h.device)
+        ent = torch.empty(T, dtype=torch.float32, device=h.device) if want_entropy else None
+        lse = torch.empty(T, dtype=torch.float32, device=h.device)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            logits = gemm(h[s:e], w)
+            rc = _L().b200_logprob_rows(_lib.ptr(logits), _c_int(1), _c_int(e - s), _c_int(V), _c_int(logits.stride(0)),
+                                        _lib.ptr(labels[s:e]), _c_f(temperature), _lib.ptr(logp[s:e]),
+                                        _lib.ptr(ent[s:e]) if ent is not None else None, _lib.ptr(lse[s:e]),
+                                        _lib.stream_ptr())
+            _lib.check_rc(rc, "logprob_rows")
+        ctx.save_for_backward(h, w, labels, lse)
+        ctx.temperature, ctx.chunk, ctx.w_ref = temperature, chunk, w
+        ctx.want_entropy = want_entropy
+        if want_entropy:
+            ctx.mark_non_differentiable(ent)
+            return logp, ent
+        return logp, None
+
+    @staticmethod
+    def backward(ctx, dlogp, _dent):
+        h, w, labels, lse = ctx.saved_tensors
+        T, V = h.shape[0], w.shape[0]
+        inv_t = 1.0 / ctx.temperature
+        dh = torch.empty_like(h)
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        dw_buf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dlogp = dlogp.float().contiguous()
+        for s in range(0, T, ctx.chunk):
+            e = min(T, s + ctx.chunk)
+            logits = gemm(h[s:e], w)
+            # d logits = g/T * (onehot - softmax(z/T))
+            rc = _L().b200_logprob_bwd_rows(_lib.ptr(logits), _c_int(e - s), _c_int(V), _c_int(logits.stride(0)),
+                                            _lib.ptr(labels[s:e]), _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]),
+                                            _c_f(inv_t), _lib.stream_ptr())
+            _lib.check_rc(rc, "logprob_bwd_rows")
+            gemm(logits, w, b_mn=True, out=dh[s:e])
+            gemm(logits, h[s:e], a_mn=True, b_mn=True, out=dw_buf, accumulate=True)
+        return dh, (None if mg is not None else dw_buf.to(w.dtype)), None, None, None, None
+
+
+def fused_logprob(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                  want_entropy: bool = False, chunk: int = 4096):
+    """Returns (logp [T] fp32, entropy [T] fp32 or None) for labels [T] given hidden states h [T,H] and lm_head w [V,H].
+
+    Replaces lm_head -> logits.float() -> cross-entropy -> compute_entropy of the reference
+    (openrlhf/models/actor.py:265-296, openrlhf/models/utils.py:139-186).
+    """
+    if not h.is_cuda:
+        return reference.fused_logprob(h, w, labels, temperature, want_entropy)
+    return _FusedLogprob.apply(h.contiguous(), w, labels.contiguous().long(), float(temperature), want_entropy, chunk)
+
+
+# ---------------------------------------------------------------------------------------------- value head
+def value_head(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """[T,H] x [1,H] -> [T] fp32 (tiny GEMV; fp32 accumulate)."""
+    return (h.float() @ w.float().t()).squeeze(-1)

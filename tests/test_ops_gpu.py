@@ -1,0 +1,177 @@
+"""Each CUDA op against the PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    err = (a.float() - b.float()).abs().max().item()
+    ref = b.float().abs().max().item()
+    assert err <= rtol * ref + atol, f"max err {err} vs ref scale {ref}"
+
+
+def test_rmsnorm_fwd_bwd():
+    from openrlhf_b200.ops import functional as F, reference as R
+    torch.manual_seed(0)
+    T, H = 333, 1536
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = F.rmsnorm(x, w, 1e-6)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(); wr = w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    yr.backward(dy.float())
+    _close(y, yr); _close(x.grad, xr.grad); _close(w.grad, wr.grad, rtol=3e-2, atol=0.3)
+
+
+def test_rope_and_swiglu_and_embedding():
+    from openrlhf_b200.ops import functional as F, reference as R
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 257, 12, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    pos = torch.randint(0, 4000, (T,), device="cuda", dtype=torch.int32)
+    tab = F.rope_table(D, 1e6, 4096, "cuda")
+    out = F.rope(qkv, pos, tab, Hq + Hkv, D)
+    ref = R.rope(qkv.detach(), pos, tab, Hq + Hkv, D)
+    _close(out, ref)
+    g = torch.randn_like(out); out.backward(g)
+    # rotation is orthogonal: the backward of a rotation is the inverse rotation
+    back = R.rope(qkv.grad, pos, tab, Hq + Hkv, D)
+    _close(back, g, rtol=3e-2, atol=3e-2)
+    gu = torch.randn(T, 2 * 8960, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = F.swiglu(gu); dy = torch.randn_like(y); y.backward(dy)
+    gr = gu.detach().float().requires_grad_(); yr = torch.nn.functional.silu(gr[:, :8960]) * gr[:, 8960:]; yr.backward(dy.float())
+    _close(y, yr); _close(gu.grad, gr.grad)
+    table = torch.randn(1000, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (T,), device="cuda")
+    e = F.embedding(ids, table); de = torch.randn_like(e); e.backward(de)
+    tr = table.detach().float().requires_grad_(); er = tr[ids]; er.backward(de.float())
+    _close(e, er); _close(table.grad, tr.grad)
+
+
+def test_linear_autograd():
+    from openrlhf_b200.ops import functional as F
+    torch.manual_seed(0)
+    T, K, N = 515, 1536, 2048
+    x = (0.5 * torch.randn(T, K, device="cuda")).to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(N, K, device="cuda")).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(T, N, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = F.linear(x, w, b, res); dy = torch.randn_like(y); y.backward(dy)
+    xr, wr, br, rr = [t.detach().float().requires_grad_() for t in (x, w, b, res)]
+    yr = xr @ wr.t() + br + rr; yr.backward(dy.float())
+    _close(y, yr); _close(x.grad, xr.grad); _close(w.grad, wr.grad); _close(b.grad, br.grad, atol=0.3); _close(res.grad, rr.grad)
+
+
+def test_fused_logprob_fwd_bwd():
+    from openrlhf_b200.ops import functional as F
+    torch.manual_seed(0)
+    T, H, V = 300, 512, 4096
+    h = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(V, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = torch.randint(0, V, (T,), device="cuda")
+    logp, ent = F.fused_logprob(h, w, y, temperature=0.7, want_entropy=True, chunk=128)
+    g = torch.randn(T, device="cuda")
+    logp.backward(g)
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logits = hr @ wr.t()
+    lr = torch.log_softmax(logits / 0.7, -1).gather(-1, y[:, None]).squeeze(-1)
+    p = torch.softmax(logits, -1); er = torch.logsumexp(logits, -1) - (p * logits).sum(-1)
+    lr.backward(g)
+    _close(logp, lr, atol=3e-2); _close(ent, er, atol=3e-2)
+    _close(h.grad, hr.grad, rtol=4e-2, atol=4e-2); _close(w.grad, wr.grad, rtol=4e-2, atol=4e-2)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,splits", [(3, 12, 2, 1), (5, 32, 8, 1), (4, 28, 4, 3), (2, 16, 2, 2)])
+def test_paged_decode(B, Hq, Hkv, splits):
+    from openrlhf_b200.ops import _lib, reference as R
+    from openrlhf_b200.ops.attention import paged_decode
+    torch.manual_seed(0)
+    D, page, num_pages, max_pages = 128, 128, 64, 8
+    k_cache = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    v_cache = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(num_pages, device="cuda")[: B * max_pages].reshape(B, max_pages).int()
+    seq_lens = torch.tensor([1, 127, 128, 129, 700, 1000][:B], device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(D)
+    out = paged_decode(q, k_cache, v_cache, perm, seq_lens, scale, splits=splits)
+    _lib.check_status()
+    ref = R.paged_decode_attention(q, k_cache, v_cache, perm, seq_lens, scale)
+    _close(out, ref, rtol=2e-2, atol=2e-2)
+
+
+def test_rope_kvwrite():
+    from openrlhf_b200.ops import functional as F, reference as R
+    from openrlhf_b200.ops.attention import rope_kvwrite
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 37, 12, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 2000, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(512, device="cuda")[:T].int()
+    tab = F.rope_table(D, 1e6, 4096, "cuda")
+    q_out = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(512, Hkv, D, device="cuda", dtype=torch.bfloat16); vc = torch.zeros_like(kc)
+    rope_kvwrite(qkv, pos, slots, tab, q_out, kc, vc, Hq, Hkv)
+    ref = R.rope(qkv, pos, tab, Hq + Hkv, D)
+    _close(q_out.reshape(T, -1), ref[:, : Hq * D])
+    _close(kc[slots.long()].reshape(T, -1), ref[:, Hq * D:(Hq + Hkv) * D])
+    _close(vc[slots.long()].reshape(T, -1), ref[:, (Hq + Hkv) * D:])
+
+
+def test_sampler_greedy_and_distribution():
+    import ctypes
+    from openrlhf_b200.ops import _lib
+    from openrlhf_b200.ops.sampling import sample
+    torch.manual_seed(0)
+    B, V = 64, 1024
+    logits = torch.randn(B, V, device="cuda").to(torch.bfloat16)
+    tok, lp = sample(logits, temperature=0.0)
+    assert torch.equal(tok, logits.float().argmax(-1))
+    ref_lp = torch.log_softmax(logits.float(), -1).gather(-1, tok[:, None]).squeeze(-1)
+    _close(lp, ref_lp, atol=1e-3)
+    # distribution check on a tiny vocabulary: empirical frequencies match softmax
+    z = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-30.0] * 4], device="cuda").repeat(4096, 1)
+    tok, lp = sample(z, temperature=1.0, seed=123, step=7)
+    freq = torch.bincount(tok, minlength=8).float() / tok.numel()
+    p = torch.softmax(z[0], -1)
+    assert (freq - p).abs().max().item() < 0.03
+    _close(lp, torch.log_softmax(z, -1).gather(-1, tok[:, None]).squeeze(-1), atol=1e-3)
+    # top-p keeps only the head of the distribution
+    tok, lp = sample(z, temperature=1.0, top_p=0.6, seed=5, step=1)
+    assert int(tok.max()) <= 1
+    tok, _ = sample(z, temperature=1.0, top_k=1, seed=5, step=2)
+    assert int(tok.max()) == 0
+
+
+def test_rl_kernels_match_reference():
+    from openrlhf_b200.ops import rl as K
+    torch.manual_seed(0)
+    B, A = 9, 77
+    mask = (torch.rand(B, A, device="cuda") > 0.2).float(); mask[:, 0] = 1
+    logp = -torch.rand(B, A, device="cuda"); old = logp + 0.3 * torch.randn(B, A, device="cuda")
+    adv = torch.randn(B, A, device="cuda"); ref = logp + 0.2 * torch.randn(B, A, device="cuda")
+    roll = old + 0.1 * torch.randn(B, A, device="cuda")
+    for kw in [dict(), dict(dual_clip=3.0), dict(kl_coef=0.05, kl_estimator="k3"), dict(is_mode="tis", is_lo=0.5, is_hi=2.0),
+               dict(is_mode="icepop", is_lo=0.8, is_hi=1.2, kl_coef=0.1, kl_estimator="k2")]:
+        lp_c = logp.clone().requires_grad_(); lp_r = logp.clone().requires_grad_()
+        out_c = K.ppo_loss(lp_c, old, adv, mask, ref_logp=ref, rollout_logp=roll, **kw)
+        out_r = K.ppo_loss_reference(lp_r, old, adv, mask, ref_logp=ref, rollout_logp=roll, **kw)
+        out_c["loss"].backward(); out_r["loss"].backward()
+        for k in ("loss", "policy_loss", "kl_loss", "clip_ratio", "ppo_kl", "vllm_kl"):
+            _close(out_c[k], out_r[k], rtol=1e-3, atol=1e-4)
+        _close(lp_c.grad, lp_r.grad, rtol=1e-3, atol=1e-5)
+    vals = torch.randn(B, A, device="cuda"); r = torch.randn(B, device="cuda"); kl = torch.rand(B, A, device="cuda")
+    for use_v in (True, False):
+        a1, r1, s1 = K.gae_advantages(vals if use_v else None, kl, r, mask, beta=0.1, gamma=0.99, lambd=0.95, clip=(-10, 10))
+        a2, r2, s2 = K.gae_advantages_reference(vals if use_v else None, kl, r, mask, beta=0.1, gamma=0.99, lambd=0.95, clip=(-10, 10))
+        _close(a1, a2, rtol=1e-3, atol=1e-4); _close(r1, r2, rtol=1e-3, atol=1e-4); _close(s1, s2, rtol=1e-3, atol=1e-4)
+    w1 = K.masked_whiten(adv.clone(), mask); w2 = K.masked_whiten_reference(adv.clone(), mask)
+    _close(w1 * mask, w2 * mask, rtol=1e-3, atol=1e-4)
+    v = vals.clone().requires_grad_(); v2 = vals.clone().requires_grad_()
+    l1 = K.value_loss(v, vals + 0.3, r1, mask, clip_eps=0.2); l2 = K.value_loss_reference(v2, vals + 0.3, r1, mask, clip_eps=0.2)
+    l1.backward(); l2.backward()
+    _close(l1, l2, rtol=1e-3, atol=1e-5); _close(v.grad, v2.grad, rtol=1e-3, atol=1e-6)
