@@ -26,7 +26,8 @@ struct GemmParams {
   int ldc;
   int out_f32;     // 1: C is fp32
   int accumulate;  // 1: C += result (fp32 outputs only; uses red.add so split-K tiles may overlap)
-  int k_splits;    // >1 requires out_f32 && accumulate
+  int k_splits;    // >1 requires out_f32, and either accumulate or a per-split output slab (split_stride)
+  long long split_stride;  // elements between the fp32 output slabs of consecutive K splits (0: all splits share C)
   float alpha;
   int* status;     // device status word (0 = ok)
 };
@@ -193,7 +194,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int col0 = n_blk * BN + c * 32;
         if (row_ok && has_work && col0 < p.N) {
           if (p.out_f32) {
-            float* crow = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+            float* crow = reinterpret_cast<float*>(p.C) + (size_t)(tile % splits) * p.split_stride +
+                          (size_t)row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col0 + j < p.N) {
@@ -318,21 +320,67 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// out[m, n] = bf16(sum_s ws[s, m, n] + bias[n] + residual[m, n]); ws holds the fp32 partial products of a split-K GEMM.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, const __nv_bfloat16* __restrict__ bias,
+                     const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int M, int N, int ldc) {
+  const int nvec = N >> 2;
+  const long long total = (long long)M * nvec;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / nvec), v = (int)(idx % nvec);
+    float4 acc = reinterpret_cast<const float4*>(ws + (size_t)m * N)[v];
+    for (int s = 1; s < splits; ++s) {
+      const float4 t = reinterpret_cast<const float4*>(ws + (size_t)s * slab + (size_t)m * N)[v];
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    if (bias != nullptr) {
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(bias + v * 4);
+      float2 a = __bfloat1622float2(b2[0]), b = __bfloat1622float2(b2[1]);
+      acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+    }
+    if (residual != nullptr) {
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(residual + (size_t)m * ldc + v * 4);
+      float2 a = __bfloat1622float2(r2[0]), b = __bfloat1622float2(r2[1]);
+      acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + (size_t)m * ldc + v * 4) = o;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 static int g_sm_count = 0;
 
+// Second half of a split-K bf16 GEMM: reduce the fp32 slabs in `ws` ([splits, M, N]) and apply bias / residual.
+extern "C" int b200_splitk_reduce(const float* ws, int splits, const void* bias, const void* residual, void* out, int M,
+                                  int N, int ldc, void* stream_) {
+  if (M <= 0 || N <= 0) return 0;
+  if (N % 4 || ldc % 4) return -10;
+  long long work = (long long)M * (N / 4);
+  long long blocks = (work + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      ws, splits, (long long)M * N, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, M,
+      N, ldc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 // C-callable entry point. a_mn / b_mn select the operand layouts documented at the top of this file.
 // lda / ldb are the row strides (elements) of the tensors as they sit in memory. Returns 0 on a successful launch.
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
                               int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
-                              int accumulate, int k_splits, float alpha, int bn, int* status, void* stream_) {
+                              int accumulate, int k_splits, long long split_stride, float alpha, int bn, int* status,
+                              void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8)) || (N % (out_f32 ? 4 : 8))) return -10;
-  if (k_splits > 1 && !(out_f32 && accumulate)) return -11;
+  if (k_splits > 1 && !(out_f32 && (accumulate || split_stride > 0))) return -11;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -12;
   if (g_sm_count == 0) {
     int dev = 0;
@@ -354,7 +402,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc;
-  p.out_f32 = out_f32; p.accumulate = accumulate; p.k_splits = k_splits; p.alpha = alpha; p.status = status;
+  p.out_f32 = out_f32; p.accumulate = accumulate; p.k_splits = k_splits; p.split_stride = split_stride; p.alpha = alpha; p.status = status;
 #define B200_DISPATCH(BN_)                                                                  \
   if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, g_sm_count, stream);     \
   if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, g_sm_count, stream);       \

@@ -1,0 +1,76 @@
+"""Policy / reference model wrapper with the reference's ``Actor.forward`` contract
+(openrlhf/models/actor.py:221-296): padded ``sequences (B,T)`` + ``action_mask (B,A)`` + ``attention_mask (B,T)`` in,
+per-action log-probs ``(B,A)`` out, with optional entropy. Internally the batch is always packed (no padding reaches
+a kernel) and the LM head is fused with the log-softmax so ``[T,V]`` logits are never materialised.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from .config import ModelConfig
+from .packing import PackedBatch, pack_padded, unpack_to_padded
+from .transformer import TransformerLM
+
+
+@dataclass
+class ActorOutput:
+    logits: torch.Tensor | None = None
+    aux_loss: torch.Tensor | None = None
+    entropy: torch.Tensor | None = None
+    log_probs: torch.Tensor | None = None
+
+
+class Actor(nn.Module):
+    def __init__(self, pretrain_or_model, device="cuda", temperature: float = 1.0, packing_samples: bool = True,
+                 shard_world: int = 1, seed: int = 0, **_unused):
+        super().__init__()
+        if isinstance(pretrain_or_model, TransformerLM):
+            self.model = pretrain_or_model
+        else:
+            from .hf_io import load_pretrained
+
+            self.model = load_pretrained(pretrain_or_model, device=device, shard_world=shard_world, seed=seed)
+        self.cfg: ModelConfig = self.model.cfg
+        self.temperature = temperature
+        self.packing_samples = packing_samples
+
+    def gradient_checkpointing_enable(self, **_kw):
+        self.model.gradient_checkpointing = True
+
+    def gradient_checkpointing_disable(self):
+        self.model.gradient_checkpointing = False
+
+    # ------------------------------------------------------------------ native packed API
+    def forward_packed(self, pb: PackedBatch, return_entropy: bool = False, context_parallel=None):
+        """Per-token log-prob of the next token over the packed stream: returns (logp [T], entropy [T] | None, aux)."""
+        if context_parallel is not None and context_parallel.size > 1:
+            return context_parallel.forward_logprobs(self.model, pb, self.temperature, return_entropy)
+        h, aux = self.model(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+        logp, ent = self.model.logprobs(h, pb.labels, self.temperature, return_entropy)
+        return logp, ent, aux
+
+    # ------------------------------------------------------------------ reference-compatible padded API
+    def forward(self, sequences: torch.LongTensor, action_mask: torch.Tensor | None = None,
+                attention_mask: torch.Tensor | None = None, return_output: bool = False,
+                allgather_logits: bool = False, return_logprobs: bool = False, ring_attn_group=None,
+                packed_seq_lens=None, return_entropy: bool = False, context_parallel=None):
+        if attention_mask is None:
+            attention_mask = torch.ones_like(sequences)
+        pb = pack_padded(sequences, attention_mask)
+        logp_t, ent_t, aux = self.forward_packed(pb, return_entropy, context_parallel)
+        log_probs = unpack_to_padded(logp_t, pb)[:, :-1]
+        out = ActorOutput(aux_loss=aux)
+        if return_entropy:
+            out.entropy = unpack_to_padded(ent_t, pb)[:, :-1]
+        if action_mask is None:
+            out.log_probs = log_probs
+            return (log_probs, out) if return_output else log_probs
+        A = action_mask.shape[1]
+        action_log_probs = log_probs[:, -A:] * action_mask.float()
+        out.log_probs = action_log_probs
+        if return_entropy and out.entropy is not None:
+            out.entropy = out.entropy[:, -A:]
+        return (action_log_probs, out) if return_output else action_log_probs

@@ -1,0 +1,99 @@
+"""Mixture-of-experts block of the Qwen3-MoE architecture: top-k softmax router, SwiGLU experts stored as fused 3-D
+tensors (gate_up [E, 2I, H], down [E, H, I]) and the load-balancing auxiliary loss.
+
+Behavioural parity target: transformers' Qwen3MoeSparseMoeBlock / load_balancing_loss_func, which the reference
+trains through ``output.aux_loss`` (openrlhf/trainer/ray/ppo_actor.py:339-343). Tokens are sorted by expert once and
+each expert runs on its contiguous slice of rows, so expert GEMMs see dense [rows_e, H] operands.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import functional as F
+from ..ops.gemm import gemm
+
+
+class _ExpertLinear(torch.autograd.Function):
+    """y = x @ W[e].T for one expert; the weight gradient is accumulated into W.main_grad[e] when present."""
+
+    @staticmethod
+    def forward(ctx, x, W, e):
+        ctx.save_for_backward(x)
+        ctx.W, ctx.e = W, e
+        if x.is_cuda and x.shape[0] > 0:
+            return gemm(x, W.detach()[e])
+        return (x.float() @ W.detach()[e].float().t()).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        W, e = ctx.W, ctx.e
+        w = W.detach()[e]
+        dy = dy.contiguous()
+        if x.is_cuda and x.shape[0] > 0:
+            dx = gemm(dy, w, b_mn=True)
+        else:
+            dx = (dy.float() @ w.float()).to(x.dtype)
+        mg = getattr(W, "main_grad", None)
+        if mg is not None:
+            if x.is_cuda and x.shape[0] > 0:
+                gemm(dy, x, a_mn=True, b_mn=True, out=mg[e], accumulate=True)
+            else:
+                mg[e].add_(dy.float().t() @ x.float())
+            return dx, None, None
+        dW = torch.zeros_like(W, dtype=torch.float32)
+        dW[e] = dy.float().t() @ x.float()
+        return dx, dW.to(W.dtype), None
+
+
+def router_topk(x, router_w, top_k: int, norm_topk: bool):
+    """Returns (weights [T,k] fp32, experts [T,k] int64, probs [T,E] fp32)."""
+    logits = F.linear(x, router_w).float()
+    probs = torch.softmax(logits, dim=-1)
+    w, idx = probs.topk(top_k, dim=-1)
+    if norm_topk:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx, probs
+
+
+def load_balancing_loss(probs: torch.Tensor, idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """E * sum_e mean_tokens(onehot top-k)_e * mean_tokens(softmax)_e for one layer."""
+    T, k = idx.shape
+    counts = torch.zeros(num_experts, dtype=torch.float32, device=probs.device)
+    counts.scatter_add_(0, idx.reshape(-1), torch.ones(T * k, dtype=torch.float32, device=probs.device))
+    f = counts / max(T, 1)
+    P = probs.mean(0)
+    return num_experts * (f * P).sum()
+
+
+def moe_forward(x, router_w, gate_up, down, top_k: int, norm_topk: bool, expert_range: tuple[int, int] | None = None):
+    """x [T,H] -> (y [T,H], aux_loss). `expert_range` restricts computation to local experts (expert parallelism:
+    rows routed to other ranks are handled by the caller's dispatch/combine)."""
+    T, H = x.shape
+    E = gate_up.shape[0]
+    w, idx, probs = router_topk(x, router_w, top_k, norm_topk)
+    aux = load_balancing_loss(probs, idx, E)
+    flat_e = idx.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    tok = order // top_k
+    sorted_e = flat_e[order]
+    counts = torch.bincount(sorted_e, minlength=E).tolist()
+    xs = x[tok]                                   # [T*k, H] rows grouped by expert
+    outs = []
+    start = 0
+    e0, e1 = expert_range if expert_range is not None else (0, E)
+    for e in range(E):
+        n = counts[e]
+        rows = xs[start:start + n]
+        if n == 0 or not (e0 <= e < e1):
+            outs.append(rows.new_zeros(n, H))
+        else:
+            gu = _ExpertLinear.apply(rows, gate_up, e)
+            a = F.swiglu(gu)
+            outs.append(_ExpertLinear.apply(a, down, e))
+        start += n
+    ys = torch.cat(outs, 0)                        # [T*k, H]
+    wk = w.reshape(-1)[order].to(ys.dtype)[:, None]
+    y = torch.zeros_like(x)
+    y.index_add_(0, tok, ys * wk)
+    return y, aux

@@ -77,6 +77,16 @@ def check_status(device: torch.device | None = None) -> None:
         raise KernelError(f"kernel status {code}: {ERROR_NAMES.get(code, 'unknown')}")
 
 
+LAUNCHES = 0  # number of kernel launches issued through this library (graph replays add their captured count)
+
+
+def count_launches(n: int) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
 def check_rc(rc: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         raise KernelError(f"{what}: launch failed with code {rc}")

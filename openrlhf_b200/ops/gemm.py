@@ -26,6 +26,7 @@ def gemm(
     k_splits: int = 1,
     alpha: float = 1.0,
     bn: int = 0,
+    split_stride: int = 0,
 ) -> torch.Tensor:
     """C[M,N] (+)= alpha * op(A) @ op(B) with bf16 inputs and fp32 accumulation.
 
@@ -48,8 +49,12 @@ def gemm(
         if accumulate:
             out.zero_()
     else:
-        assert out.shape == (M, N) and out.stride(1) == 1
+        assert out.stride(-1) == 1
         out_f32 = out.dtype == torch.float32
+    if split_stride:
+        assert out.dtype == torch.float32 and out.numel() >= k_splits * split_stride
+    else:
+        assert out.shape == (M, N)
     if M == 0 or N == 0:
         return out
     if bias is not None:
@@ -61,10 +66,51 @@ def gemm(
     rc = _lib.lib().b200_gemm_bf16(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
-        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(N if split_stride else out.stride(0)),
         ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)),
-        ctypes.c_int(int(accumulate)), ctypes.c_int(int(k_splits)), ctypes.c_float(alpha), ctypes.c_int(bn),
+        ctypes.c_int(int(accumulate)), ctypes.c_int(int(k_splits)), ctypes.c_longlong(int(split_stride)),
+        ctypes.c_float(alpha), ctypes.c_int(bn),
         _lib.ptr(st), _lib.stream_ptr(),
     )
     _lib.check_rc(rc, "b200_gemm_bf16")
+    return out
+
+
+_splitk_ws: dict = {}
+_splitk_retired: list = []  # outgrown buffers stay alive: captured CUDA graphs may still point at them
+
+
+def splitk_workspace(device, numel: int) -> torch.Tensor:
+    """fp32 scratch for split-K partial products, grown on demand and reused by every call on the device."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _splitk_ws.get(key)
+    if ws is None or ws.numel() < numel:
+        if ws is not None:
+            _splitk_retired.append(ws)
+        ws = torch.empty(max(numel, 1 << 24), dtype=torch.float32, device=device)
+        _splitk_ws[key] = ws
+    return ws
+
+
+def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, bias: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None, out: torch.Tensor | None = None, bn: int = 0,
+                workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 C = A @ B^T (+bias)(+residual) for small M: K is cut into `splits` slabs so that every SM streams a share
+    of the weights; fp32 partial products go to a scratch buffer and a second kernel reduces them."""
+    M, K = a.shape
+    N = b.shape[0]
+    kb_total = (K + 63) // 64
+    per = (kb_total + splits - 1) // splits
+    splits = (kb_total + per - 1) // per          # no empty K slab
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if splits <= 1:
+        return gemm(a, b, bias=bias, residual=residual, out=out, bn=bn)
+    ws = workspace if workspace is not None else splitk_workspace(a.device, splits * M * N)
+    assert ws.numel() >= splits * M * N
+    gemm(a, b, out=ws, k_splits=splits, split_stride=M * N, bn=bn)
+    rc = _lib.lib().b200_splitk_reduce(_lib.ptr(ws), ctypes.c_int(splits), _lib.ptr(bias), _lib.ptr(residual),
+                                       _lib.ptr(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(out.stride(0)),
+                                       _lib.stream_ptr())
+    _lib.check_rc(rc, "splitk_reduce")
     return out

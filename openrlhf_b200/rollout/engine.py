@@ -1,0 +1,487 @@
+"""Rollout engine: paged KV cache, slot-based continuous batching, CUDA-graph decode loop, prefix sharing for the
+n samples of a prompt, sleep / wake and in-place weight updates.
+
+This is the component that takes the place of vLLM in the reference (openrlhf/trainer/ray/vllm_engine.py:63-208 wraps
+``vllm.AsyncLLMEngine``; sampling parameters come from openrlhf/trainer/ppo_utils/samples_generator.py:203-211).
+Token-in / token-out API: ``generate(prompt_token_ids, sampling_params)`` returns objects with
+``.outputs[i].token_ids / .logprobs / .finish_reason`` like the engine the reference's agent executors talk to.
+
+Execution model: every request owns one row ("slot") of a set of static device tensors for its lifetime; one decode
+step for all rows is captured once per batch-size bucket as a CUDA graph (embedding -> [RMSNorm, qkv GEMM,
+RoPE+KV-write, paged tcgen05 attention, o-proj GEMM(+residual), RMSNorm, gate_up GEMM, SwiGLU, down GEMM(+residual)]
+x L -> RMSNorm -> lm_head GEMM -> sampler -> advance) and replayed per token; the host only intervenes every few steps
+to hand out KV pages and retire finished rows.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.transformer import TransformerLM
+from ..ops import _lib
+from ..ops import functional as F
+from ..ops.attention import PAGE, paged_decode, rope_kvwrite
+from ..ops.gemm import gemm
+from ..ops.sampling import sample
+from .block_manager import BlockManager
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    max_tokens: int | None = 16
+    min_tokens: int = 0
+    n: int = 1
+    logprobs: int | None = None
+    ignore_eos: bool = False
+    stop_token_ids: list | None = None
+    seed: int | None = None
+    skip_special_tokens: bool = False
+    include_stop_str_in_output: bool = False
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: list
+    logprobs: list | None
+    finish_reason: str
+    text: str = ""
+    cumulative_logprob: float = 0.0
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    prompt_token_ids: list
+    outputs: list = field(default_factory=list)
+    finished: bool = True
+
+
+@dataclass
+class _Row:
+    request_id: int
+    sample_index: int
+    prompt_len: int
+    max_tokens: int
+    pages: list
+    gen: int = 0  # tokens generated so far as far as the host knows (upper bound for finished rows)
+
+
+class RolloutEngine:
+    def __init__(self, model: TransformerLM, max_num_seqs: int = 256, max_model_len: int = 4096,
+                 num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
+                 eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16):
+        assert model.cfg.head_dim == 128, "the decode attention kernel is specialised for head_dim 128"
+        self.model = model
+        self.cfg: ModelConfig = model.cfg
+        self.device = model.flat.device
+        self.max_num_seqs = max_num_seqs
+        self.max_model_len = max_model_len
+        self.max_pages = (max_model_len + PAGE - 1) // PAGE
+        self.seed = seed
+        self.eos = self.cfg.eos_token_id if eos_token_id is None else eos_token_id
+        self.use_cuda_graph = use_cuda_graph
+        self.check_interval = check_interval
+        cfg = self.cfg
+        bytes_per_page = 2 * cfg.num_hidden_layers * PAGE * cfg.kv_size * 2
+        if num_pages is None:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(total * gpu_memory_utilization) - (total - free)
+            num_pages = max(8, min(budget // bytes_per_page, max_num_seqs * self.max_pages + 1))
+        self.num_pages = int(num_pages)
+        self.blocks = BlockManager(self.num_pages)
+        self.dummy_page = self.blocks.alloc()  # page 0 backs inactive rows
+        self.kv = None
+        self._alloc_kv()
+        B = max_num_seqs
+        dev = self.device
+        self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.seq_lens = torch.ones(B, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.block_table = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32, device=dev)
+        self.block_table_host = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32).pin_memory()
+        self.active = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.gen_count = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.max_tok = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.min_tok = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.ignore_eos = torch.zeros(B, dtype=torch.bool, device=dev)
+        self.temperature = torch.ones(B, dtype=torch.float32, device=dev)
+        self.step_counter = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.max_new_cap = max_model_len
+        self.out_tokens = torch.zeros(B, self.max_new_cap, dtype=torch.int64, device=dev)
+        self.out_logprobs = torch.zeros(B, self.max_new_cap, dtype=torch.float32, device=dev)
+        self.q_buf = torch.empty(B, cfg.num_attention_heads, 128, dtype=torch.bfloat16, device=dev)
+        self.attn_buf = torch.empty_like(self.q_buf)
+        self.next_tok = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.next_lp = torch.zeros(B, dtype=torch.float32, device=dev)
+        self.rows: list[_Row | None] = [None] * B
+        self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.graph_launches: dict[tuple, int] = {}
+        self.top_p, self.top_k = 1.0, -1
+        self.sleeping = False
+        self.paused = False
+        self.decode_steps = 0
+        _lib.status_word(self.device)
+        self.model.rope(self.device)
+
+    # ------------------------------------------------------------------ memory
+    def _alloc_kv(self):
+        cfg = self.cfg
+        self.kv = torch.zeros(cfg.num_hidden_layers, 2, self.num_pages * PAGE, cfg.num_key_value_heads, 128,
+                              dtype=torch.bfloat16, device=self.device)
+
+    def sleep(self, level: int = 1):
+        """Release the KV cache (and captured graphs that point into it). Weights stay resident: trainer and rollout
+        share them on this GPU. Counterpart of vLLM sleep mode as used at openrlhf/trainer/ray/vllm_engine.py:138-153."""
+        self.graphs.clear()
+        self.kv = None
+        torch.cuda.empty_cache()
+        self.sleeping = True
+
+    def wake_up(self, tags=None):
+        if tags is not None and "kv_cache" not in tags:
+            return  # weights are always resident
+        if self.kv is None:
+            self._alloc_kv()
+        self.sleeping = False
+
+    def reset_prefix_cache(self):
+        return True
+
+    def pause_generation(self):
+        self.paused = True
+
+    def resume_generation(self):
+        self.paused = False
+
+    def get_num_unfinished_requests(self) -> int:
+        return sum(r is not None for r in self.rows)
+
+    @torch.no_grad()
+    def update_weights(self, flat_src: torch.Tensor):
+        """Copy a new set of weights (same flat layout) into the engine's buffer; a no-op when they alias."""
+        if flat_src.data_ptr() != self.model.flat.data_ptr():
+            self.model.flat.copy_(flat_src, non_blocking=True)
+
+    # ------------------------------------------------------------------ model execution
+    @torch.no_grad()
+    def _prefill(self, prompts: list[list[int]], row_groups: list[list[int]]):
+        """Run the prompts through the model once each, fill their KV pages, and return last-position logits [P, V]."""
+        cfg, m = self.cfg, self.model
+        dev = self.device
+        lens = [len(p) for p in prompts]
+        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=dev)
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
+        cu = torch.zeros(len(prompts) + 1, dtype=torch.int32)
+        cu[1:] = torch.cumsum(torch.tensor(lens, dtype=torch.int32), 0)
+        cu = cu.to(dev)
+        # slot of every prompt token in the first row of its group (full pages are shared with the other rows)
+        slot_list = []
+        for p, rows in zip(prompts, row_groups):
+            pages = self.rows[rows[0]].pages
+            for t in range(len(p)):
+                slot_list.append(pages[t // PAGE] * PAGE + t % PAGE)
+        slots = torch.tensor(slot_list, dtype=torch.int64, device=dev)
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+
+        def attn_fn(i, q, k, v):
+            self.kv[i, 0].index_copy_(0, slots, k)
+            self.kv[i, 1].index_copy_(0, slots, v)
+            return F.attention_varlen(q, k, v, cu, max(lens))
+
+        was_training = m.training
+        m.eval()
+        h, _ = m(ids, pos, cu, max(lens), attn_fn=attn_fn)
+        m.train(was_training)
+        last = (cu[1:] - 1).long()
+        logits = gemm(h[last].contiguous(), m.lm_head_weight())
+        # partial last page: every other row of the group gets its own copy
+        for p, rows in zip(prompts, row_groups):
+            n_full = len(p) // PAGE
+            if len(p) % PAGE and len(rows) > 1:
+                src = self.rows[rows[0]].pages[n_full]
+                for r in rows[1:]:
+                    dst = self.rows[r].pages[n_full]
+                    self.kv[:, :, dst * PAGE:(dst + 1) * PAGE].copy_(self.kv[:, :, src * PAGE:(src + 1) * PAGE])
+        return logits
+
+    def _decode_step(self, B: int):
+        """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
+        cfg, m = self.cfg, self.model
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        table = m.rope(self.device)
+        tok, pos, slots = self.tok[:B], self.pos[:B], self.slots[:B]
+        bt, sl = self.block_table[:B], self.seq_lens[:B]
+        q_buf, attn_buf = self.q_buf[:B], self.attn_buf[:B]
+        h = F.embedding(tok, m.p("embed.weight"))
+        for i in range(cfg.num_hidden_layers):
+            pre = f"layers.{i}."
+            x = F.rmsnorm(h, m.p(pre + "norm1.weight"), cfg.rms_norm_eps)
+            qkv = decode_gemm(x, m.p(pre + "qkv.weight"), m._params.get(pre + "qkv.bias"))
+            if cfg.qk_norm:
+                T = qkv.shape[0]
+                qk = qkv[:, : (Hq + Hkv) * 128].reshape(T, Hq + Hkv, 128)
+                qn = F.rmsnorm(qk[:, :Hq].reshape(-1, 128), m.p(pre + "q_norm.weight"), cfg.rms_norm_eps).view(T, -1)
+                kn = F.rmsnorm(qk[:, Hq:].reshape(-1, 128), m.p(pre + "k_norm.weight"), cfg.rms_norm_eps).view(T, -1)
+                qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * 128:]], dim=1)
+            rope_kvwrite(qkv, pos, slots, table, q_buf, self.kv[i, 0], self.kv[i, 1], Hq, Hkv)
+            paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
+            h = decode_gemm(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"), None, h)
+            x = F.rmsnorm(h, m.p(pre + "norm2.weight"), cfg.rms_norm_eps)
+            if cfg.is_moe_layer(i):
+                from ..models.moe import moe_forward
+
+                y, _ = moe_forward(x, m.p(pre + "router.weight"), m.p(pre + "experts.gate_up"),
+                                   m.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob)
+                h = h + y
+            else:
+                gu = decode_gemm(x, m.p(pre + "gate_up.weight"))
+                a = F.swiglu(gu)
+                h = decode_gemm(a, m.p(pre + "down.weight"), None, h)
+        x = F.rmsnorm(h, m.p("norm.weight"), cfg.rms_norm_eps)
+        logits = gemm(x, m.lm_head_weight())
+        sample(logits, temperature=self.temperature[:B], top_k=self.top_k, top_p=self.top_p, seed=self.seed,
+               step=self.step_counter, out_tokens=self.next_tok[:B], out_logprobs=self.next_lp[:B],
+               active=self.active[:B])
+        self._advance(B)
+
+    def _advance(self, B: int):
+        act = self.active[:B].bool()
+        g = self.gen_count[:B].long().clamp_max(self.max_new_cap - 1)
+        rows = torch.arange(B, device=self.device)
+        nt = torch.where(act, self.next_tok[:B], self.tok[:B])
+        self.out_tokens[rows, g] = torch.where(act, nt, self.out_tokens[rows, g])
+        self.out_logprobs[rows, g] = torch.where(act, self.next_lp[:B], self.out_logprobs[rows, g])
+        inc = act.int()
+        self.gen_count[:B] += inc
+        gc = self.gen_count[:B]
+        hit_eos = (nt == self.eos) & ~self.ignore_eos[:B] & (gc >= self.min_tok[:B])
+        done = act & (hit_eos | (gc >= self.max_tok[:B]))
+        still = act & ~done
+        self.tok[:B] = nt
+        self.pos[:B] += still.int()
+        self.seq_lens[:B] += still.int()
+        self.active[:B] = still.int()
+        p = self.pos[:B].long()
+        page = self.block_table[:B].gather(1, (p // PAGE).clamp_max(self.max_pages - 1)[:, None]).squeeze(1)
+        self.slots[:B] = (page * PAGE + (p % PAGE).int()).int()
+        self.step_counter += 1
+
+    def _run_decode(self, B: int):
+        if not self.use_cuda_graph:
+            self._decode_step(B)
+            return
+        key = (B, self.top_k, self.top_p)
+        g = self.graphs.get(key)
+        if g is None:
+            # warm up outside capture (lazy library state, status word, rope table), then capture
+            saved = self._snapshot_state(B)
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_step(B)
+            torch.cuda.current_stream().wait_stream(s)
+            self._restore_state(saved, B)
+            g = torch.cuda.CUDAGraph()
+            before = _lib.LAUNCHES
+            with torch.cuda.graph(g):
+                self._decode_step(B)
+            self.graph_launches[key] = _lib.LAUNCHES - before
+            self._restore_state(saved, B)
+            self.graphs[key] = g
+        g.replay()
+        _lib.count_launches(self.graph_launches[key])
+
+    def _state_tensors(self):
+        return [self.tok, self.pos, self.seq_lens, self.slots, self.active, self.gen_count, self.step_counter,
+                self.out_tokens, self.out_logprobs]
+
+    def _snapshot_state(self, B):
+        return [t.clone() for t in self._state_tensors()]
+
+    def _restore_state(self, saved, B):
+        for t, s in zip(self._state_tensors(), saved):
+            t.copy_(s)
+
+    # ------------------------------------------------------------------ scheduling
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.max_num_seqs)
+
+    def _ensure_pages(self, row: int, upto_pos: int):
+        r = self.rows[row]
+        need = min(upto_pos, self.max_model_len - 1) // PAGE + 1
+        changed = False
+        while len(r.pages) < need:
+            pg = self.blocks.alloc()
+            r.pages.append(pg)
+            self.block_table_host[row, len(r.pages) - 1] = pg
+            changed = True
+        return changed
+
+    def _release_row(self, row: int):
+        r = self.rows[row]
+        for pg in r.pages:
+            self.blocks.free(pg)
+        self.rows[row] = None
+        self.block_table_host[row].fill_(self.dummy_page)
+
+    @torch.no_grad()
+    def generate(self, prompt_token_ids: list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
+                 request_ids: list[int] | None = None) -> list[RequestOutput]:
+        """Blocking batch generation with continuous batching: requests wait when rows or KV pages run out."""
+        if self.sleeping:
+            self.wake_up()
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompt_token_ids)
+        sp0 = sampling_params[0]
+        self.top_p, self.top_k = float(sp0.top_p), int(sp0.top_k)
+        if sp0.seed is not None:
+            self.seed = sp0.seed
+        pending = list(range(len(prompt_token_ids)))
+        results: dict[int, RequestOutput] = {}
+        collected: dict[tuple, CompletionOutput] = {}
+        req_ids = request_ids or list(range(len(prompt_token_ids)))
+        row_of: dict[int, tuple[int, int]] = {}
+        while pending or any(r is not None for r in self.rows):
+            # ---- admit as many pending prompts as rows / pages allow, then prefill them together
+            admitted, groups = [], []
+            free_rows = [i for i, r in enumerate(self.rows) if r is None]
+            while pending:
+                ridx = pending[0]
+                sp = sampling_params[ridx]
+                prompt = prompt_token_ids[ridx]
+                max_new = sp.max_tokens if sp.max_tokens is not None else max(1, self.max_model_len - len(prompt))
+                max_new = max(1, min(max_new, self.max_model_len - len(prompt)))
+                pages_needed = sp.n * ((len(prompt) + max_new) // PAGE + 1)
+                if len(free_rows) < sp.n or self.blocks.num_free() < pages_needed + 1:
+                    break
+                pending.pop(0)
+                rows = [free_rows.pop(0) for _ in range(sp.n)]
+                n_full = len(prompt) // PAGE
+                shared = [self.blocks.alloc() for _ in range(n_full)]
+                for j, r in enumerate(rows):
+                    if j > 0:
+                        for pg in shared:
+                            self.blocks.share(pg)
+                    self.rows[r] = _Row(req_ids[ridx], j, len(prompt), max_new, list(shared))
+                    self.block_table_host[r].fill_(self.dummy_page)
+                    for t, pg in enumerate(shared):
+                        self.block_table_host[r, t] = pg
+                    self._ensure_pages(r, len(prompt))
+                    row_of[r] = (ridx, j)
+                admitted.append(ridx)
+                groups.append(rows)
+            if admitted:
+                self._start_rows([prompt_token_ids[i] for i in admitted], groups, [sampling_params[i] for i in admitted])
+            if not any(r is not None for r in self.rows):
+                if pending:
+                    raise RuntimeError("a request does not fit into the KV cache / row budget of the rollout engine")
+                break
+            # ---- decode until something finishes or pages are needed
+            high = max(i for i, r in enumerate(self.rows) if r is not None) + 1
+            B = self._bucket(high)
+            steps = self.check_interval
+            live = [i for i, r in enumerate(self.rows) if r is not None]
+            steps = max(1, min([steps] + [self.rows[i].max_tokens - self.rows[i].gen for i in live if self.rows[i].max_tokens > self.rows[i].gen] or [1]))
+            changed = False
+            for i in live:
+                r = self.rows[i]
+                changed |= self._ensure_pages(i, r.prompt_len + r.gen + steps)
+            if changed:
+                self.block_table.copy_(self.block_table_host, non_blocking=True)
+            for _ in range(steps):
+                self._run_decode(B)
+            self.decode_steps += steps
+            for i in live:
+                self.rows[i].gen = min(self.rows[i].gen + steps, self.rows[i].max_tokens)
+            # ---- retire finished rows
+            act = self.active[:B].cpu()
+            gcount = self.gen_count[:B].cpu()
+            done_rows = [i for i in live if act[i] == 0]
+            if done_rows:
+                toks = self.out_tokens[:B].cpu()
+                lps = self.out_logprobs[:B].cpu()
+                for i in done_rows:
+                    r = self.rows[i]
+                    n = int(gcount[i])
+                    ridx, j = row_of.pop(i)
+                    tl = toks[i, :n].tolist()
+                    reason = "stop" if (n < r.max_tokens or (tl and tl[-1] == self.eos and not sampling_params[ridx].ignore_eos)) else "length"
+                    if n >= r.max_tokens and not (tl and tl[-1] == self.eos and not sampling_params[ridx].ignore_eos):
+                        reason = "length"
+                    want_lp = sampling_params[ridx].logprobs is not None
+                    lpl = lps[i, :n].tolist()
+                    collected[(ridx, j)] = CompletionOutput(j, tl, lpl if want_lp else None, reason,
+                                                            cumulative_logprob=float(sum(lpl)))
+                    self._release_row(i)
+            _lib.check_status(self.device)
+        for ridx in range(len(prompt_token_ids)):
+            outs = [collected[(ridx, j)] for j in range(sampling_params[ridx].n)]
+            results[ridx] = RequestOutput(req_ids[ridx], list(prompt_token_ids[ridx]), outs)
+        return [results[i] for i in range(len(prompt_token_ids))]
+
+    def _start_rows(self, prompts, groups, sps):
+        """Prefill admitted prompts and initialise the device state of their rows with the first sampled token."""
+        dev = self.device
+        self.block_table.copy_(self.block_table_host, non_blocking=True)
+        logits = self._prefill(prompts, groups)                      # [P, V]
+        rep = torch.tensor([len(g) for g in groups], device=dev)
+        rows = torch.tensor([r for g in groups for r in g], dtype=torch.int64, device=dev)
+        lg = logits.repeat_interleave(rep, dim=0)                    # one row per sample
+        temps = torch.tensor([sp.temperature for sp, g in zip(sps, groups) for _ in g], dtype=torch.float32, device=dev)
+        tok, lp = sample(lg, temperature=temps, top_k=self.top_k, top_p=self.top_p, seed=self.seed ^ 0x5DEECE66D,
+                         step=int(self.decode_steps) * 4096 + int(rows[0].item()))
+        plen = torch.tensor([len(p) for p, g in zip(prompts, groups) for _ in g], dtype=torch.int32, device=dev)
+        maxt = torch.tensor([self.rows[r].max_tokens for g in groups for r in g], dtype=torch.int32, device=dev)
+        mint = torch.tensor([sp.min_tokens for sp, g in zip(sps, groups) for _ in g], dtype=torch.int32, device=dev)
+        ign = torch.tensor([sp.ignore_eos for sp, g in zip(sps, groups) for _ in g], dtype=torch.bool, device=dev)
+        self.out_tokens[rows, 0] = tok
+        self.out_logprobs[rows, 0] = lp
+        done = ((tok == self.eos) & ~ign & (mint <= 1)) | (maxt <= 1)
+        self.tok[rows] = tok
+        self.pos[rows] = plen
+        self.seq_lens[rows] = plen + 1
+        self.gen_count[rows] = 1
+        self.max_tok[rows] = maxt
+        self.min_tok[rows] = mint
+        self.ignore_eos[rows] = ign
+        self.temperature[rows] = temps
+        self.active[rows] = (~done).int()
+        page = self.block_table[rows].gather(1, (plen.long() // PAGE)[:, None]).squeeze(1)
+        self.slots[rows] = (page * PAGE + (plen % PAGE)).int()
+        for g in groups:
+            for r in g:
+                self.rows[r].gen = 1
+
+
+# ---------------------------------------------------------------------------------------------- decode GEMM
+_SPLITK_WS: dict = {}
+
+
+def decode_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Small-M linear for the decode loop: picks a narrow N tile and split-K so that all SMs stream weights."""
+    from ..ops.gemm import gemm_splitk
+
+    M, K = x.shape
+    N = w.shape[0]
+    if M > 256:
+        return gemm(x, w, bias=bias, residual=residual)
+    bn = 64 if N <= 4096 else 128
+    tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+    kb = (K + 63) // 64
+    splits = max(1, min(148 // max(tiles, 1), kb // 4))
+    if splits <= 1:
+        return gemm(x, w, bias=bias, residual=residual, bn=bn)
+    return gemm_splitk(x, w, splits, bias=bias, residual=residual, bn=bn)
