@@ -10,11 +10,45 @@ from . import _lib
 PAGE = 128  # tokens per KV page (one tcgen05 kv tile)
 
 
-def attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale):
-    """Packed causal GQA attention with autograd (library varlen kernel; see DESIGN notes on the attention path)."""
+_varlen_impl = None
+
+
+def _pick_varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale):
+    """First working library varlen kernel on this GPU (flash-attn, then torch's varlen_attn)."""
+    global _varlen_impl
+    errors = []
+    try:
+        from flash_attn import flash_attn_varlen_func
+
+        def fa(q, k, v, cu, mx, sc):
+            return flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, softmax_scale=sc, causal=True)
+
+        with torch.no_grad():
+            fa(q[:8].contiguous(), k[:8].contiguous(), v[:8].contiguous(),
+               torch.tensor([0, 8], dtype=torch.int32, device=q.device), 8, scale)
+            torch.cuda.synchronize()
+        _varlen_impl = fa
+        return
+    except Exception as e:  # noqa: BLE001
+        errors.append(f"flash_attn: {e}")
     from torch.nn.attention.varlen import varlen_attn
 
-    return varlen_attn(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, is_causal=True, scale=scale)
+    def tv(q, k, v, cu, mx, sc):
+        rep = q.shape[1] // k.shape[1]
+        if rep > 1:
+            k = k.repeat_interleave(rep, dim=1)
+            v = v.repeat_interleave(rep, dim=1)
+        return varlen_attn(q.contiguous(), k.contiguous(), v.contiguous(), cu, cu, mx, mx, scale=sc,
+                           window_size=(-1, 0))
+
+    _varlen_impl = tv
+
+
+def attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale):
+    """Packed causal GQA attention with autograd, through a library varlen flash-attention kernel."""
+    if _varlen_impl is None:
+        _pick_varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale)
+    return _varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale)
 
 
 _decode_ws: dict = {}
