@@ -380,3 +380,43 @@ extern "C" int b200_rope_kvwrite(const void* qkv, const int* pos, const int* slo
       (__nv_bfloat16*)v_cache, T, Hq, Hkv, ld, max_pos);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in no_alloc.h). The split-KV partials go to a fixed array of this translation
+// unit instead of a caller workspace. In host code the array's name is only a handle for the runtime, not a device
+// address, so its address is resolved once per device with cudaGetSymbolAddress and then passed to the kernel.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[B200_NOALLOC_MAX_PARTIAL_ROWS * (HD + 2)];
+
+static float* noalloc_scratch_for_current_device(int* err) {
+  constexpr int MAX_DEV = 64;
+  static float* ptrs[MAX_DEV] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) { *err = -21; return nullptr; }
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) { *err = -21; return nullptr; }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  *err = 0;
+  return ptrs[dev];
+}
+
+extern "C" int b200_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                        const int* block_table, const int* seq_lens, void* out, int B, int Hq, int Hkv,
+                                        int num_pages, int max_pages, int splits, float scale, int* status,
+                                        void* stream_) {
+  if (B <= 0) return 0;
+  if (splits < 1) return -10;
+  const long long rows = (long long)B * Hq * splits;
+  if (rows > B200_NOALLOC_MAX_PARTIAL_ROWS) return -20;
+  int err = 0;
+  float* scratch = noalloc_scratch_for_current_device(&err);
+  if (scratch == nullptr) return err;
+  float* part_o = scratch;                                              // [rows, HD]
+  float* part_ml = scratch + (size_t)B200_NOALLOC_MAX_PARTIAL_ROWS * HD;  // [rows, 2]
+  return b200_attn_decode(q, k_cache, v_cache, block_table, seq_lens, out, part_o, part_ml, B, Hq, Hkv, num_pages,
+                          max_pages, splits, scale, status, stream_);
+}
