@@ -96,7 +96,7 @@ class ZeroEngine:
         if not train:
             return
         on_gpu = self.flat.is_cuda
-        self.grad_flat = self._alloc_grad(use_symm if use_symm is not None else (on_gpu and self.world > 1))
+        self.grad_flat = self._alloc_grad(bool(use_symm) and on_gpu and self.world > 1)
         for s, p in model.named_specs():
             p.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.shape)
         sl = slice(self.lo, self.hi)

@@ -1,0 +1,34 @@
+"""Small distributed helpers (barrier + device sync; rendezvous defaults)."""
+from __future__ import annotations
+
+import datetime
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def torch_dist_barrier_and_cuda_sync() -> None:
+    """Barrier over the default group followed by a device synchronize (after checkpoints, syncs and offloads)."""
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def init_process_group(backend: str | None = None, timeout_minutes: int = 60) -> tuple[int, int, int]:
+    """Initialise the default group from torchrun-style environment variables. Returns (rank, local_rank, world)."""
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kw = {}
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            kw["device_id"] = torch.device(f"cuda:{local}")
+        dist.init_process_group(backend, timeout=datetime.timedelta(minutes=timeout_minutes), **kw)
+    return rank, local, world
