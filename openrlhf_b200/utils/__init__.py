@@ -1,0 +1,1 @@
+from .config import hierarchize  # noqa: F401

@@ -1,0 +1,346 @@
+"""Training strategy: the object the SPMD trainers and the RL workers drive their engines through.
+
+Same surface as the reference's ``DeepspeedStrategy`` (openrlhf/utils/deepspeed/deepspeed.py:60-782):
+``setup_distributed``, ``prepare``, ``backward``, ``optimizer_step``, ``get_grad_norm``, ``setup_dataloader``,
+``save_model``, ``save_ckpt``, ``load_ckpt``, ``all_reduce``, ``all_gather``, ``moving_average``, rank helpers, the
+``(dp, sp, tp)`` mesh with tp fastest, and ``accumulated_gradient``. Underneath sits this framework's ZeRO engine
+(``parallel/zero.py``) instead of DeepSpeed.
+"""
+from __future__ import annotations
+
+import gc
+import logging
+import os
+import random
+from collections import defaultdict
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..parallel.zero import LRScheduler, ZeroEngine
+from . import checkpoint as ckpt
+from .distributed_sampler import DistributedSampler
+from .distributed_util import init_process_group, torch_dist_barrier_and_cuda_sync
+
+logger = logging.getLogger(__name__)
+
+
+class RankMesh:
+    """rank = ((dp * SP) + sp) * TP + tp. Builds the dp / sp / tp process groups lazily."""
+
+    def __init__(self, world: int, sp: int = 1, tp: int = 1, rank: int = 0):
+        if world % (sp * tp):
+            raise ValueError(f"world size {world} is not divisible by ring_attn_size*tensor_parallel_size = {sp * tp}")
+        self.world, self.sp, self.tp, self.dp = world, sp, tp, world // (sp * tp)
+        self.rank = rank
+        self.tp_rank = rank % tp
+        self.sp_rank = (rank // tp) % sp
+        self.dp_rank = rank // (tp * sp)
+        self._groups: dict = {}
+
+    def ranks_of(self, dim: str, rank: int | None = None) -> list[int]:
+        r = self.rank if rank is None else rank
+        tp_r, sp_r, dp_r = r % self.tp, (r // self.tp) % self.sp, r // (self.tp * self.sp)
+        if dim == "tp":
+            return [(dp_r * self.sp + sp_r) * self.tp + t for t in range(self.tp)]
+        if dim == "sp":
+            return [(dp_r * self.sp + s) * self.tp + tp_r for s in range(self.sp)]
+        if dim == "dp":
+            return [(d * self.sp + sp_r) * self.tp + tp_r for d in range(self.dp)]
+        raise KeyError(dim)
+
+    def group(self, dim: str):
+        """Process group of this rank along `dim` (every rank must call this for the same dims in the same order)."""
+        if self.world == 1 or not dist.is_initialized():
+            return None
+        if dim in self._groups:
+            return self._groups[dim]
+        mine = None
+        seen = set()
+        for r in range(self.world):
+            ranks = tuple(self.ranks_of(dim, r))
+            if ranks in seen:
+                continue
+            seen.add(ranks)
+            g = dist.new_group(list(ranks))
+            if self.rank in ranks:
+                mine = g
+        self._groups[dim] = mine
+        return mine
+
+
+class _Prepared(nn.Module):
+    """What ``prepare`` returns for a model: the module plus its engine (``.engine``) behind the same call syntax."""
+
+    def __init__(self, module: nn.Module, engine: ZeroEngine | None):
+        super().__init__()
+        self.module = module
+        self.engine = engine
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(super().__getattr__("module"), name)
+
+
+def _inner_lm(module):
+    """The TransformerLM inside an Actor / RewardModel / CriticModel / _Prepared wrapper."""
+    m = module
+    for _ in range(4):
+        if hasattr(m, "specs") and hasattr(m, "flat"):
+            return m
+        m = getattr(m, "module", None) or getattr(m, "model", None)
+        if m is None:
+            break
+    raise TypeError("object does not wrap a TransformerLM")
+
+
+class Strategy:
+    CKPT_METRIC_FILENAME = ckpt.METRIC_FILE
+
+    def __init__(self, seed: int = 42, full_determinism: bool = False, max_norm: float = 0.0,
+                 micro_train_batch_size: int = 1, train_batch_size: int = 1, zero_stage: int = 2, args=None) -> None:
+        self.args = args
+        self.seed, self.full_determinism, self.max_norm = seed, full_determinism, max_norm
+        self.micro_train_batch_size, self.train_batch_size = micro_train_batch_size, train_batch_size
+        self.stage = zero_stage
+        ds = getattr(args, "ds", SimpleNamespace()) if args is not None else SimpleNamespace()
+        self.param_dtype = getattr(ds, "param_dtype", "bf16")
+        self.ring_attn_size = int(getattr(ds, "ring_attn_size", 1) or 1)
+        self.ds_tensor_parallel_size = int(getattr(ds, "tensor_parallel_size", 1) or 1)
+        self.adam_offload = getattr(ds, "adam_offload", False)
+        self.use_dynamic_batch = bool(getattr(getattr(args, "train", SimpleNamespace()), "dynamic_batch_enable", False)) \
+            if args is not None else False
+        self.is_rlhf = False
+        self.time_steps = defaultdict(int)
+        self.world_size, self.rank, self.local_rank = 1, 0, 0
+        self.mesh = RankMesh(1)
+        self.accumulated_gradient = 1
+
+    # ------------------------------------------------------------------ distributed set-up
+    def set_seed(self, seed: int) -> None:
+        random.seed(seed)
+        np.random.seed(seed)
+        torch.manual_seed(seed)
+        if torch.cuda.is_available():
+            torch.cuda.manual_seed_all(seed)
+
+    def setup_distributed(self, timeout_minutes: int = 60, backend: str | None = None) -> None:
+        if self.full_determinism:
+            torch.use_deterministic_algorithms(True, warn_only=True)
+        self.set_seed(self.seed)
+        self.rank, self.local_rank, self.world_size = init_process_group(backend, timeout_minutes)
+        if torch.cuda.is_available():
+            torch.cuda.set_device(self.local_rank)
+        self.mesh = RankMesh(self.world_size, self.ring_attn_size, self.ds_tensor_parallel_size, self.rank)
+        for dim in ("dp", "sp", "tp"):
+            self.mesh.group(dim)
+        dp = self.mesh.dp
+        self.accumulated_gradient = max(1, self.train_batch_size * self.ring_attn_size * self.ds_tensor_parallel_size
+                                        // max(self.micro_train_batch_size, 1) // max(self.world_size, 1))
+        if self.use_dynamic_batch:
+            self.accumulated_gradient = 1
+        self.dp_size = dp
+
+    @property
+    def ring_attn_group(self):
+        return self.mesh.group("sp") if self.ring_attn_size > 1 else None
+
+    @property
+    def ds_device_mesh(self):
+        return {"dp": SimpleNamespace(get_group=lambda: self.mesh.group("dp")),
+                "sp": SimpleNamespace(get_group=lambda: self.mesh.group("sp")),
+                "tp": SimpleNamespace(get_group=lambda: self.mesh.group("tp"))} if self.world_size > 1 else None
+
+    def dp_group(self):
+        return self.mesh.group("dp")
+
+    def device(self):
+        return torch.device("cuda", self.local_rank) if torch.cuda.is_available() else torch.device("cpu")
+
+    # ------------------------------------------------------------------ engines
+    def create_optimizer(self, model, **kwargs):
+        return kwargs  # optimizer hyper-parameters; the engine is built in prepare()
+
+    def prepare(self, *models_or_model_optim_pairs, is_rlhf: bool = False):
+        """Each argument is a module (inference only) or a ``(module, cfg)`` pair where cfg holds optimizer / schedule
+        settings (keys: lr, betas, eps, weight_decay, lr_scheduler, lr_warmup_ratio, min_lr_ratio, max_steps).
+        Returns the prepared object(s): modules with ``.engine`` attached."""
+        self.is_rlhf = is_rlhf
+        out = []
+        for arg in models_or_model_optim_pairs:
+            if isinstance(arg, tuple):
+                module, cfg = arg
+                cfg = dict(cfg or {})
+                lm = _inner_lm(module)
+                sched = LRScheduler(cfg.get("lr", 1e-6), cfg.get("max_steps", 1000), cfg.get("lr_warmup_ratio", 0.03),
+                                    cfg.get("min_lr_ratio", 0.1), cfg.get("lr_scheduler", "cosine_with_min_lr"))
+                eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
+                                 eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
+                                 max_norm=self.max_norm, zero_stage=self.stage, group=self.mesh.group("dp"),
+                                 scheduler=sched, use_symm=cfg.get("use_symm"))
+                out.append(_Prepared(module, eng))
+            else:
+                if arg is not None:
+                    arg.eval() if hasattr(arg, "eval") else None
+                out.append(_Prepared(arg, None) if arg is not None else None)
+        return out[0] if len(out) == 1 else out
+
+    def backward(self, loss: torch.Tensor, model, optimizer=None, **kwargs) -> None:
+        model.engine.backward(loss / self.accumulated_gradient)
+
+    def optimizer_step(self, optimizer, model, scheduler=None, name: str = "model", **kwargs) -> bool:
+        """Counts micro-steps; runs the optimizer at the accumulation boundary. Returns True when it stepped."""
+        self.time_steps[name] += 1
+        if self.time_steps[name] % self.accumulated_gradient:
+            return False
+        model.engine.step()
+        return True
+
+    def get_grad_norm(self, model) -> float:
+        return model.engine.grad_norm()
+
+    def moving_average(self, model, model_ema, beta: float = 0.992, device: str = "cpu") -> None:
+        """ema <- beta * ema + (1 - beta) * param on the flat buffers (shard-local; no gathers needed)."""
+        self.time_steps["ema"] += 1
+        if self.time_steps["ema"] % self.accumulated_gradient:
+            return
+        src, dst = _inner_lm(model).flat, _inner_lm(model_ema).flat
+        with torch.no_grad():
+            dst.mul_(beta).add_(src.to(dst.device, dst.dtype), alpha=1 - beta)
+
+    # ------------------------------------------------------------------ data
+    def setup_dataloader(self, replay_buffer, batch_size: int, pin_memory: bool = False, shuffle: bool = True,
+                         collate_fn=None, drop_last: bool = True, sampler=None, consumed_samples: int = 0,
+                         num_workers: int = 0):
+        try:
+            from torchdata.stateful_dataloader import StatefulDataLoader as Loader
+        except Exception:  # noqa: BLE001
+            from torch.utils.data import DataLoader as Loader
+        if sampler is None and dist.is_initialized() and self.mesh.dp > 1:
+            sampler = DistributedSampler(replay_buffer, num_replicas=self.mesh.dp, rank=self.mesh.dp_rank,
+                                         shuffle=shuffle, seed=self.seed, drop_last=drop_last,
+                                         consumed_samples=consumed_samples)
+            shuffle = False
+        elif sampler is None and consumed_samples:
+            sampler = DistributedSampler(replay_buffer, num_replicas=1, rank=0, shuffle=shuffle, seed=self.seed,
+                                         drop_last=drop_last, consumed_samples=consumed_samples)
+            shuffle = False
+        return Loader(replay_buffer, batch_size=batch_size, sampler=sampler, shuffle=shuffle if sampler is None else False,
+                      drop_last=drop_last, collate_fn=collate_fn, pin_memory=pin_memory, num_workers=num_workers)
+
+    # ------------------------------------------------------------------ reductions
+    def all_reduce(self, data, op: str = "mean"):
+        if op not in ("mean", "max", "sum"):
+            raise AssertionError(op)
+        if isinstance(data, dict):
+            keys = list(data.keys())
+            if not keys:
+                return data
+            # one packed collective per reduction type instead of one per key
+            vals = torch.tensor([float(data[k]) for k in keys], dtype=torch.float64)
+            red = self.all_reduce(vals, op)
+            return {k: (red[i].item()) for i, k in enumerate(keys)}
+        is_tensor = isinstance(data, torch.Tensor)
+        t = data if is_tensor else torch.tensor([data], dtype=torch.float64)
+        if self.world_size > 1 and dist.is_initialized():
+            cpu = t.device.type == "cpu"
+            backend = dist.get_backend()
+            work = t.to(self.device()) if (cpu and backend == "nccl") else t.clone()
+            dist.all_reduce(work, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+            if op == "mean":
+                work = work / self.world_size
+            t = work.to(t.device) if cpu else work
+        return t if is_tensor else t.item()
+
+    def all_gather(self, data):
+        if isinstance(data, dict):
+            return {k: self.all_gather(v) for k, v in data.items()}
+        t = data if isinstance(data, torch.Tensor) else torch.tensor([data])
+        if self.world_size == 1 or not dist.is_initialized():
+            return t
+        cpu = t.device.type == "cpu"
+        work = t.to(self.device()) if (cpu and dist.get_backend() == "nccl") else t
+        parts = [torch.zeros_like(work) for _ in range(self.world_size)]
+        dist.all_gather(parts, work.contiguous())
+        res = torch.cat(parts)
+        return res.cpu() if cpu else res
+
+    def print(self, *msg):
+        if self.is_rank_0():
+            print(*msg)
+
+    def is_rank_0(self) -> bool:
+        return self.get_rank() == 0
+
+    def get_rank(self) -> int:
+        return dist.get_rank() if dist.is_initialized() else 0
+
+    # ------------------------------------------------------------------ saving / loading
+    def save_model(self, model, tokenizer, output_dir: str, **kwargs) -> None:
+        """HF-format export (weights only): every rank writes its share of the shards, rank 0 the index + config."""
+        from ..models.hf_io import save_pretrained
+
+        lm = _inner_lm(model)
+        extra = {}
+        inner = getattr(model, "module", model)
+        if lm.with_value_head:
+            extra = {"value_head_prefix": lm.cfg.value_head_prefix,
+                     "normalize_reward": bool(getattr(inner, "normalize_reward", lm.cfg.normalize_reward)),
+                     "mean": float(getattr(inner, "mean", torch.tensor([lm.cfg.mean]))[0]),
+                     "std": float(getattr(inner, "std", torch.tensor([lm.cfg.std]))[0])}
+        lora = getattr(inner, "lora", None) or getattr(lm, "lora", None)
+        if lora is not None:
+            if self.is_rank_0():
+                lora.save_adapter(output_dir)
+            return
+        save_pretrained(lm, output_dir, tokenizer=tokenizer if self.is_rank_0() else None, extra_config=extra,
+                        rank=self.rank if self.world_size > 1 else 0, world=max(self.world_size, 1))
+        torch_dist_barrier_and_cuda_sync()
+
+    def save_ckpt(self, model, save_dir: str, tag=None, max_num: int = 3, max_mem: float = 1000, client_state=None,
+                  save_latest: bool = True, metric_value=None, metric_key=None) -> None:
+        tag = tag or f"global_step{self.time_steps.get('model', 0)}"
+        if self.is_rank_0():
+            ckpt.rotate(save_dir, tag, max_num, max_mem, log=self.print)
+        torch_dist_barrier_and_cuda_sync()
+        eng = model.engine
+        ckpt.save_sharded(eng, save_dir, tag, client_state, save_latest, rank=eng.rank, world=eng.world)
+        torch_dist_barrier_and_cuda_sync()
+        if self.is_rank_0():
+            ckpt.write_metric(os.path.join(save_dir, tag), metric_value, metric_key)
+        gc.collect()
+
+    def load_ckpt(self, model, load_dir: str, tag=None, load_module_strict: bool = True,
+                  load_optimizer_states: bool = True, load_lr_scheduler_states: bool = True,
+                  load_module_only: bool = False):
+        path, states = ckpt.load_sharded(model.engine, load_dir, tag,
+                                         load_optimizer_states and not load_module_only,
+                                         load_lr_scheduler_states and not load_module_only)
+        if path is None:
+            self.print(f"Warning: no checkpoint found at {load_dir}, skipping checkpoint loading.")
+            return None, {}
+        return path, states
+
+
+DeepspeedStrategy = Strategy  # the name user code written against the reference imports
+
+
+def get_strategy(args) -> Strategy:
+    """Build the strategy from the hierarchical flag namespace (openrlhf/utils/utils.py:25-37)."""
+    train = getattr(args, "train", SimpleNamespace())
+    ds = getattr(args, "ds", SimpleNamespace())
+    actor = getattr(args, "actor", None)
+    max_norm = getattr(actor, "max_norm", None) if actor is not None else None
+    if max_norm is None:
+        max_norm = getattr(args, "max_norm", 1.0)
+    return Strategy(seed=getattr(train, "seed", 42), full_determinism=getattr(train, "full_determinism_enable", False),
+                    max_norm=max_norm, micro_train_batch_size=getattr(train, "micro_batch_size", 1),
+                    train_batch_size=getattr(train, "batch_size", 128), zero_stage=getattr(ds, "zero_stage", 2), args=args)
