@@ -22,6 +22,12 @@ class ActorOutput:
     entropy: torch.Tensor | None = None
     log_probs: torch.Tensor | None = None
 
+    def __contains__(self, key) -> bool:
+        return getattr(self, key, None) is not None
+
+    def __getitem__(self, key):
+        return getattr(self, key)
+
 
 class Actor(nn.Module):
     def __init__(self, pretrain_or_model, device="cuda", temperature: float = 1.0, packing_samples: bool = True,

@@ -131,6 +131,13 @@ class ZeroEngine:
     def backward(self, loss: torch.Tensor):
         loss.backward()
         self.micro_steps += 1
+        # gradients that arrived through plain autograd (CPU restatements, small torch ops such as the value head)
+        # are folded into the fp32 flat buffer next to the ones the kernels accumulated there directly
+        with torch.no_grad():
+            for _, p in self.model.named_specs():
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                    p.grad = None
 
     def zero_grad(self):
         self.grad_flat.zero_()
