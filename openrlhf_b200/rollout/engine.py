@@ -46,13 +46,21 @@ class SamplingParams:
 
 
 @dataclass
+class Logprob:
+    logprob: float
+    rank: int | None = None
+    decoded_token: str | None = None
+
+
+@dataclass
 class CompletionOutput:
     index: int
     token_ids: list
-    logprobs: list | None
+    logprobs: list | None          # [{token_id: Logprob}] per generated token when requested
     finish_reason: str
     text: str = ""
     cumulative_logprob: float = 0.0
+    logprob_values: list | None = None   # plain floats, always filled
 
 
 @dataclass
@@ -122,6 +130,11 @@ class RolloutEngine:
         self.next_tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.next_lp = torch.zeros(B, dtype=torch.float32, device=dev)
         self.rows: list[_Row | None] = [None] * B
+        from collections import deque
+
+        self.waiting = deque()
+        self._req: dict = {}
+        self._batch_counter = 0
         self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self.graph_launches: dict[tuple, int] = {}
         self.top_p, self.top_k = 1.0, -1
@@ -336,100 +349,130 @@ class RolloutEngine:
         self.rows[row] = None
         self.block_table_host[row].fill_(self.dummy_page)
 
+    # ------------------------------------------------------------------ request API (continuous batching)
+    def add_request(self, request_id, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
+        """Queue one request; it is admitted by a later ``step()`` when rows and KV pages are available."""
+        self.waiting.append((request_id, list(prompt_token_ids), sampling_params))
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting) or any(r is not None for r in self.rows)
+
+    def _max_new(self, prompt, sp) -> int:
+        m = sp.max_tokens if sp.max_tokens is not None else max(1, self.max_model_len - len(prompt))
+        return max(1, min(m, self.max_model_len - len(prompt)))
+
     @torch.no_grad()
-    def generate(self, prompt_token_ids: list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
-                 request_ids: list[int] | None = None) -> list[RequestOutput]:
-        """Blocking batch generation with continuous batching: requests wait when rows or KV pages run out."""
+    def step(self) -> list[RequestOutput]:
+        """Admit waiting requests (prefill), run a burst of decode steps for all live rows, retire finished rows.
+        Returns the requests whose samples have all finished."""
         if self.sleeping:
             self.wake_up()
-        if isinstance(sampling_params, SamplingParams):
-            sampling_params = [sampling_params] * len(prompt_token_ids)
-        sp0 = sampling_params[0]
-        self.top_p, self.top_k = float(sp0.top_p), int(sp0.top_k)
-        if sp0.seed is not None:
-            self.seed = sp0.seed
-        pending = list(range(len(prompt_token_ids)))
-        results: dict[int, RequestOutput] = {}
-        collected: dict[tuple, CompletionOutput] = {}
-        req_ids = request_ids or list(range(len(prompt_token_ids)))
-        row_of: dict[int, tuple[int, int]] = {}
-        while pending or any(r is not None for r in self.rows):
-            # ---- admit as many pending prompts as rows / pages allow, then prefill them together
-            admitted, groups = [], []
-            free_rows = [i for i, r in enumerate(self.rows) if r is None]
-            while pending:
-                ridx = pending[0]
-                sp = sampling_params[ridx]
-                prompt = prompt_token_ids[ridx]
-                max_new = sp.max_tokens if sp.max_tokens is not None else max(1, self.max_model_len - len(prompt))
-                max_new = max(1, min(max_new, self.max_model_len - len(prompt)))
-                pages_needed = sp.n * ((len(prompt) + max_new) // PAGE + 1)
-                if len(free_rows) < sp.n or self.blocks.num_free() < pages_needed + 1:
-                    break
-                pending.pop(0)
-                rows = [free_rows.pop(0) for _ in range(sp.n)]
-                n_full = len(prompt) // PAGE
-                shared = [self.blocks.alloc() for _ in range(n_full)]
-                for j, r in enumerate(rows):
-                    if j > 0:
-                        for pg in shared:
-                            self.blocks.share(pg)
-                    self.rows[r] = _Row(req_ids[ridx], j, len(prompt), max_new, list(shared))
-                    self.block_table_host[r].fill_(self.dummy_page)
-                    for t, pg in enumerate(shared):
-                        self.block_table_host[r, t] = pg
-                    self._ensure_pages(r, len(prompt))
-                    row_of[r] = (ridx, j)
-                admitted.append(ridx)
-                groups.append(rows)
-            if admitted:
-                self._start_rows([prompt_token_ids[i] for i in admitted], groups, [sampling_params[i] for i in admitted])
-            if not any(r is not None for r in self.rows):
-                if pending:
+        finished: list[RequestOutput] = []
+        if self.paused:
+            return finished
+        # ---- admission
+        admitted, groups = [], []
+        free_rows = [i for i, r in enumerate(self.rows) if r is None]
+        while self.waiting:
+            rid, prompt, sp = self.waiting[0]
+            if len(prompt) >= self.max_model_len:
+                prompt = prompt[-(self.max_model_len - 1):]
+            max_new = self._max_new(prompt, sp)
+            pages_needed = sp.n * ((len(prompt) + max_new) // PAGE + 1)
+            if len(free_rows) < sp.n or self.blocks.num_free() < pages_needed + 1:
+                if not any(r is not None for r in self.rows) and not admitted:
+                    self.waiting.popleft()
                     raise RuntimeError("a request does not fit into the KV cache / row budget of the rollout engine")
                 break
-            # ---- decode until something finishes or pages are needed
-            high = max(i for i, r in enumerate(self.rows) if r is not None) + 1
-            B = self._bucket(high)
-            steps = self.check_interval
-            live = [i for i, r in enumerate(self.rows) if r is not None]
-            steps = max(1, min([steps] + [self.rows[i].max_tokens - self.rows[i].gen for i in live if self.rows[i].max_tokens > self.rows[i].gen] or [1]))
-            changed = False
-            for i in live:
-                r = self.rows[i]
-                changed |= self._ensure_pages(i, r.prompt_len + r.gen + steps)
-            if changed:
-                self.block_table.copy_(self.block_table_host, non_blocking=True)
-            for _ in range(steps):
-                self._run_decode(B)
-            self.decode_steps += steps
-            for i in live:
-                self.rows[i].gen = min(self.rows[i].gen + steps, self.rows[i].max_tokens)
-            # ---- retire finished rows
-            act = self.active[:B].cpu()
+            self.waiting.popleft()
+            if (self.top_p, self.top_k) != (float(sp.top_p), int(sp.top_k)):
+                if any(r is not None for r in self.rows) or admitted:
+                    self.waiting.appendleft((rid, prompt, sp))   # nucleus settings are per batch: wait for a drain
+                    break
+                self.top_p, self.top_k = float(sp.top_p), int(sp.top_k)
+            rows = [free_rows.pop(0) for _ in range(sp.n)]
+            shared = [self.blocks.alloc() for _ in range(len(prompt) // PAGE)]
+            for j, r in enumerate(rows):
+                if j > 0:
+                    for pg in shared:
+                        self.blocks.share(pg)
+                self.rows[r] = _Row(rid, j, len(prompt), max_new, list(shared))
+                self.block_table_host[r].fill_(self.dummy_page)
+                for t, pg in enumerate(shared):
+                    self.block_table_host[r, t] = pg
+                self._ensure_pages(r, len(prompt))
+            self._req[rid] = (prompt, sp, {})
+            admitted.append((prompt, sp))
+            groups.append(rows)
+        if admitted:
+            self._start_rows([a[0] for a in admitted], groups, [a[1] for a in admitted])
+        live = [i for i, r in enumerate(self.rows) if r is not None]
+        if not live:
+            return finished
+        # ---- decode burst
+        B = self._bucket(max(live) + 1)
+        left = [self.rows[i].max_tokens - self.rows[i].gen for i in live if self.rows[i].max_tokens > self.rows[i].gen]
+        steps = max(1, min([self.check_interval] + left)) if left else 0
+        changed = False
+        for i in live:
+            r = self.rows[i]
+            changed |= self._ensure_pages(i, r.prompt_len + r.gen + steps)
+        if changed:
+            self.block_table.copy_(self.block_table_host, non_blocking=True)
+        for _ in range(steps):
+            self._run_decode(B)
+        self.decode_steps += steps
+        for i in live:
+            self.rows[i].gen = min(self.rows[i].gen + steps, self.rows[i].max_tokens)
+        # ---- retirement
+        act = self.active[:B].cpu()
+        done_rows = [i for i in live if act[i] == 0]
+        if done_rows:
             gcount = self.gen_count[:B].cpu()
-            done_rows = [i for i in live if act[i] == 0]
-            if done_rows:
-                toks = self.out_tokens[:B].cpu()
-                lps = self.out_logprobs[:B].cpu()
-                for i in done_rows:
-                    r = self.rows[i]
-                    n = int(gcount[i])
-                    ridx, j = row_of.pop(i)
-                    tl = toks[i, :n].tolist()
-                    reason = "stop" if (n < r.max_tokens or (tl and tl[-1] == self.eos and not sampling_params[ridx].ignore_eos)) else "length"
-                    if n >= r.max_tokens and not (tl and tl[-1] == self.eos and not sampling_params[ridx].ignore_eos):
-                        reason = "length"
-                    want_lp = sampling_params[ridx].logprobs is not None
-                    lpl = lps[i, :n].tolist()
-                    collected[(ridx, j)] = CompletionOutput(j, tl, lpl if want_lp else None, reason,
-                                                            cumulative_logprob=float(sum(lpl)))
-                    self._release_row(i)
-            _lib.check_status(self.device)
-        for ridx in range(len(prompt_token_ids)):
-            outs = [collected[(ridx, j)] for j in range(sampling_params[ridx].n)]
-            results[ridx] = RequestOutput(req_ids[ridx], list(prompt_token_ids[ridx]), outs)
-        return [results[i] for i in range(len(prompt_token_ids))]
+            idx = torch.tensor(done_rows, device=self.device)
+            toks = self.out_tokens[idx].cpu()
+            lps = self.out_logprobs[idx].cpu()
+            for k, i in enumerate(done_rows):
+                r = self.rows[i]
+                prompt, sp, parts = self._req[r.request_id]
+                n = int(gcount[i])
+                tl = toks[k, :n].tolist()
+                hit_eos = bool(tl) and tl[-1] == self.eos and not sp.ignore_eos
+                reason = "stop" if hit_eos else "length"
+                lpl = lps[k, :n].tolist()
+                lp_out = [{t: Logprob(l)} for t, l in zip(tl, lpl)] if sp.logprobs is not None else None
+                parts[r.sample_index] = CompletionOutput(r.sample_index, tl, lp_out, reason,
+                                                         cumulative_logprob=float(sum(lpl)), logprob_values=lpl)
+                self._release_row(i)
+                if len(parts) == sp.n:
+                    finished.append(RequestOutput(r.request_id, list(prompt), [parts[j] for j in range(sp.n)]))
+                    del self._req[r.request_id]
+        _lib.check_status(self.device)
+        return finished
+
+    @torch.no_grad()
+    def generate(self, prompt_token_ids: list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
+                 request_ids: list | None = None) -> list[RequestOutput]:
+        """Blocking batch generation on top of the request API (requests wait when rows or KV pages run out)."""
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompt_token_ids)
+        if sampling_params and sampling_params[0].seed is not None:
+            self.seed = sampling_params[0].seed
+        base = self._batch_counter
+        self._batch_counter += len(prompt_token_ids)
+        keys = [("batch", base + i) for i in range(len(prompt_token_ids))]
+        for k, p, sp in zip(keys, prompt_token_ids, sampling_params):
+            self.add_request(k, p, sp)
+        got: dict = {}
+        while len(got) < len(keys):
+            for ro in self.step():
+                got[ro.request_id] = ro
+        outs = []
+        for i, k in enumerate(keys):
+            ro = got[k]
+            ro.request_id = request_ids[i] if request_ids else i
+            outs.append(ro)
+        return outs
 
     def _start_rows(self, prompts, groups, sps):
         """Prefill admitted prompts and initialise the device state of their rows with the first sampled token."""

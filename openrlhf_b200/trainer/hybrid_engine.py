@@ -126,7 +126,7 @@ class HybridRLWorker:
                 am = torch.zeros(T - 1, dtype=torch.bool)
                 am[len(p) - 1:] = True
                 rl = torch.zeros(T - 1, dtype=torch.float32)
-                rl[len(p) - 1:] = torch.tensor(c.logprobs, dtype=torch.float32)
+                rl[len(p) - 1:] = torch.tensor(c.logprob_values, dtype=torch.float32)
                 exps.append(Experience(
                     sequences=seq, attention_mask=torch.ones(T, dtype=torch.long), action_mask=am,
                     rollout_log_probs=rl, response_length=torch.tensor(float(len(r))),

@@ -63,7 +63,7 @@ def test_rollout_matches_trainer_logprobs_and_greedy():
         chosen = lp.gather(-1, torch.tensor(toks, device="cuda")[:, None]).squeeze(-1)
         # greedy tokens are (near-)argmax of the trainer's logits and log-probs agree
         assert (lp.max(-1).values - chosen).max() < 0.05
-        assert (chosen.cpu() - torch.tensor(o.outputs[0].logprobs)).abs().max() < 0.05
+        assert (chosen.cpu() - torch.tensor(o.outputs[0].logprob_values)).abs().max() < 0.05
     # sampled generation with n > 1 shares the prompt pages and yields distinct continuations
     outs = eng.generate([prompts[1]], SamplingParams(temperature=1.0, max_tokens=20, n=4, logprobs=1, ignore_eos=True))
     conts = {tuple(c.token_ids) for c in outs[0].outputs}
