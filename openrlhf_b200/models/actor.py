@@ -31,7 +31,8 @@ class ActorOutput:
 
 class Actor(nn.Module):
     def __init__(self, pretrain_or_model, device="cuda", temperature: float = 1.0, packing_samples: bool = True,
-                 shard_world: int = 1, seed: int = 0, **_unused):
+                 shard_world: int = 1, seed: int = 0, lora_rank: int = 0, lora_alpha: float = 16,
+                 target_modules="all-linear", lora_dropout: float = 0.0, **_unused):
         super().__init__()
         if isinstance(pretrain_or_model, TransformerLM):
             self.model = pretrain_or_model
@@ -40,6 +41,12 @@ class Actor(nn.Module):
 
             self.model = load_pretrained(pretrain_or_model, device=device, shard_world=shard_world, seed=seed)
         self.cfg: ModelConfig = self.model.cfg
+        self.lora = None
+        if lora_rank and lora_rank > 0:
+            from .lora import LoraAdapters
+
+            self.lora = LoraAdapters(self.model, lora_rank, lora_alpha, target_modules, lora_dropout, seed)
+            self.lora._cfg = self.cfg
         self.temperature = temperature
         self.packing_samples = packing_samples
 

@@ -95,6 +95,7 @@ class TransformerLM(nn.Module):
             self._params[s.name] = p
             self.register_parameter(s.name.replace(".", "__"), p)
         self.gradient_checkpointing = False
+        self.lora = None                      # optional LoraAdapters (models/lora.py)
         self.max_pos = min(cfg.max_position_embeddings, 1 << 17)
         if seed is not None:
             self.reset_parameters(init_std, seed)
@@ -133,11 +134,20 @@ class TransformerLM(nn.Module):
         return F.rope_table(self.cfg.head_dim, self.cfg.rope_theta, self.max_pos, device)
 
     # ------------------------------------------------------------------ forward
+    def _lin(self, i: int, target: str, x, bias=None, residual=None):
+        """Projection `target` of layer i, plus its low-rank adapter when adapters are attached."""
+        y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, residual)
+        if self.lora is not None:
+            d = self.lora.delta(i, target, x)
+            if d is not None:
+                y = y + d.to(y.dtype)
+        return y
+
     def _attention_block(self, i: int, h, pos, cu_seqlens, max_seqlen, attn_fn=None):
         cfg = self.cfg
         pre = f"layers.{i}."
         x = F.rmsnorm(h, self.p(pre + "norm1.weight"), cfg.rms_norm_eps)
-        qkv = F.linear(x, self.p(pre + "qkv.weight"), self._params.get(pre + "qkv.bias"))
+        qkv = self._lin(i, "qkv", x, self._params.get(pre + "qkv.bias"))
         T = qkv.shape[0]
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         if cfg.qk_norm:
@@ -153,7 +163,7 @@ class TransformerLM(nn.Module):
             a = attn_fn(i, q, k, v)
         else:
             a = F.attention_varlen(q, k, v, cu_seqlens, max_seqlen)
-        return F.linear(a.reshape(T, Hq * D), self.p(pre + "o.weight"), None, h)
+        return self._lin(i, "o", a.reshape(T, Hq * D), None, h)
 
     def _mlp_block(self, i: int, h):
         cfg = self.cfg
@@ -165,9 +175,9 @@ class TransformerLM(nn.Module):
             y, aux = moe_forward(x, self.p(pre + "router.weight"), self.p(pre + "experts.gate_up"),
                                  self.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob)
             return h + y, aux
-        gu = F.linear(x, self.p(pre + "gate_up.weight"))
+        gu = self._lin(i, "gate_up", x)
         a = F.swiglu(gu)
-        return F.linear(a, self.p(pre + "down.weight"), None, h), None
+        return self._lin(i, "down", a, None, h), None
 
     def _layer(self, i, h, pos, cu_seqlens, max_seqlen, attn_fn=None):
         h = self._attention_block(i, h, pos, cu_seqlens, max_seqlen, attn_fn)
