@@ -1,0 +1,241 @@
+// In-kernel NVLink collectives over symmetric (peer-mapped) buffers for the ZeRO engine and weight resharding.
+//
+//   symm_barrier      epoch-numbered flag barrier across ranks; every wait is bounded and reports through a status word
+//   zero_reduce       reduce-scatter fused with scaling and the gradient-norm partial: the shard owner pulls its slice
+//                     of every peer's fp32 gradient buffer (P2P loads, or one NVLS multimem.ld_reduce per 16 B), sums in
+//                     rank order, writes the reduced shard locally and accumulates sum(g^2)
+//   zero_adam_gather  fused AdamW on the owned fp32 master shard + bf16 cast + all-gather: the new bf16 values are
+//                     stored straight into every peer's parameter buffer (P2P stores or one NVLS multimem.st)
+//   reshard_copy      plan-driven gather of weight pieces (from local or peer buffers) into another layout
+//
+// Together they replace DeepSpeed's bucketed NCCL reduce-scatter -> FusedAdam -> all-gather sequence
+// (engine.backward / engine.step at openrlhf/utils/deepspeed/deepspeed.py:177-194) and the per-parameter
+// gather + broadcast weight sync of openrlhf/trainer/ray/ppo_actor.py:408-489.
+// No TMA is involved here: all remote traffic is plain ld/st/multimem issued by the consuming or producing thread.
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int MAX_PEERS = 16;
+
+struct PeerTable {
+  void* ptr[MAX_PEERS];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Each rank writes `epoch` into slot [channel][rank] of every peer's signal pad, then waits until all slots of its own
+// pad reach `epoch`. Epochs only grow, so no slot ever needs resetting. wait_limit_ns bounds the wait.
+__global__ void symm_barrier_kernel(PeerTable pads, int rank, int world, int channel, unsigned int epoch,
+                                    unsigned long long wait_limit_ns, int* status) {
+  const int t = threadIdx.x;
+  __threadfence_system();
+  if (t < world) {
+    unsigned int* remote = reinterpret_cast<unsigned int*>(pads.ptr[t]) + channel * MAX_PEERS + rank;
+    st_release_sys(remote, epoch);
+  }
+  if (t < world) {
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pads.ptr[rank]) + channel * MAX_PEERS + t;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      const unsigned int v = ld_acquire_sys(mine);
+      if ((int)(v - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > wait_limit_ns) {
+        atomicCAS(status, 0, ERR_TIMEOUT_FLAG);
+        atomicExch(status + 1, t);  // which peer never arrived
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+}
+
+// reduced[i] = scale * sum_r grad_r[lo + i]; scalars[0] += sum reduced^2. n is a multiple of 4.
+__global__ void __launch_bounds__(256)
+zero_reduce_kernel(PeerTable grads, int world, long long lo, long long n, float scale, float* __restrict__ reduced,
+                   float* __restrict__ scalars) {
+  __shared__ float red[8];
+  float ss = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int r = 0; r < world; ++r) {
+      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.ptr[r]) + lo)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    reinterpret_cast<float4*>(reduced)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float t = red[threadIdx.x];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffu, t, o);
+    if (threadIdx.x == 0) atomicAdd(scalars, t);
+  }
+}
+
+// Same reduction through the NVSwitch: one multimem.ld_reduce returns the sum over all ranks of 4 floats.
+__global__ void __launch_bounds__(256)
+zero_reduce_nvls_kernel(const float* __restrict__ mc_grad, long long lo, long long n, float scale,
+                        float* __restrict__ reduced, float* __restrict__ scalars) {
+  __shared__ float red[8];
+  float ss = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc;
+    const float* addr = mc_grad + lo + i * 4;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                 : "l"(addr)
+                 : "memory");
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    reinterpret_cast<float4*>(reduced)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float t = red[threadIdx.x];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffu, t, o);
+    if (threadIdx.x == 0) atomicAdd(scalars, t);
+  }
+}
+
+// AdamW on the owned shard, then the bf16 result goes to every rank's parameter buffer at [lo, lo+n).
+// scalars[2] = clip coefficient x gradient scale (device scalar, no host round trip). n multiple of 8.
+__global__ void __launch_bounds__(256)
+zero_adam_gather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                        const float* __restrict__ g, PeerTable params, __nv_bfloat16* mc_param, int world, long long lo,
+                        long long n, const float* __restrict__ scalars, float lr, float beta1, float beta2, float eps,
+                        float wd, float bc1, float bc2, const unsigned char* __restrict__ decay_mask) {
+  const float gs = scalars[2];
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float p[8], mm[8], vv[8], gg[8];
+    *reinterpret_cast<float4*>(p) = reinterpret_cast<const float4*>(master)[2 * i];
+    *reinterpret_cast<float4*>(p + 4) = reinterpret_cast<const float4*>(master)[2 * i + 1];
+    *reinterpret_cast<float4*>(mm) = reinterpret_cast<const float4*>(m)[2 * i];
+    *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<const float4*>(m)[2 * i + 1];
+    *reinterpret_cast<float4*>(vv) = reinterpret_cast<const float4*>(v)[2 * i];
+    *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<const float4*>(v)[2 * i + 1];
+    *reinterpret_cast<float4*>(gg) = reinterpret_cast<const float4*>(g)[2 * i];
+    *reinterpret_cast<float4*>(gg + 4) = reinterpret_cast<const float4*>(g)[2 * i + 1];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = gg[k] * gs;
+      mm[k] = beta1 * mm[k] + (1.f - beta1) * gk;
+      vv[k] = beta2 * vv[k] + (1.f - beta2) * gk * gk;
+      const float decay = (decay_mask == nullptr || decay_mask[i * 8 + k]) ? (1.f - lr * wd) : 1.f;
+      p[k] = p[k] * decay - lr * (mm[k] / bc1) / (sqrtf(vv[k] / bc2) + eps);
+    }
+    reinterpret_cast<float4*>(master)[2 * i] = *reinterpret_cast<float4*>(p);
+    reinterpret_cast<float4*>(master)[2 * i + 1] = *reinterpret_cast<float4*>(p + 4);
+    reinterpret_cast<float4*>(m)[2 * i] = *reinterpret_cast<float4*>(mm);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = *reinterpret_cast<float4*>(mm + 4);
+    reinterpret_cast<float4*>(v)[2 * i] = *reinterpret_cast<float4*>(vv);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+    if (mc_param != nullptr) {
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_param + lo + i * 8),
+                   "f"(__uint_as_float(o.x)), "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)),
+                   "f"(__uint_as_float(o.w))
+                   : "memory");
+    } else {
+#pragma unroll 4
+      for (int r = 0; r < world; ++r)
+        reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.ptr[r]) + lo)[i] = o;
+    }
+  }
+}
+
+// One block per plan entry: copy `rows` rows of `row_elems` bf16 from (src rank buffer + src_off, stride src_ld) to
+// (dst + dst_off, stride dst_ld). row_elems, offsets and strides are multiples of 8 elements.
+struct ReshardEntry {
+  long long src_off, dst_off;
+  int rows, row_elems, src_ld, dst_ld, src_rank, pad;
+};
+__global__ void __launch_bounds__(256)
+reshard_copy_kernel(const ReshardEntry* __restrict__ plan, PeerTable srcs, __nv_bfloat16* __restrict__ dst) {
+  const ReshardEntry e = plan[blockIdx.x];
+  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(srcs.ptr[e.src_rank]) + e.src_off;
+  __nv_bfloat16* out = dst + e.dst_off;
+  const int vec_per_row = e.row_elems >> 3;
+  const long long total = (long long)e.rows * vec_per_row;
+  for (long long i = blockIdx.y * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.y * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row);
+    reinterpret_cast<uint4*>(out + (size_t)r * e.dst_ld)[c] = reinterpret_cast<const uint4*>(src + (size_t)r * e.src_ld)[c];
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static PeerTable make_table(const void* const* ptrs, int world) {
+  PeerTable t;
+  for (int i = 0; i < MAX_PEERS; ++i) t.ptr[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
+  return t;
+}
+
+extern "C" int b200_symm_barrier(const void* const* pad_ptrs, int rank, int world, int channel, unsigned int epoch,
+                                 double wait_limit_s, int* status, void* stream) {
+  if (world > MAX_PEERS || channel < 0 || channel >= 8) return -10;
+  symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_table(pad_ptrs, world), rank, world, channel, epoch, (unsigned long long)(wait_limit_s * 1e9), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_zero_reduce(const void* const* grad_ptrs, const void* mc_grad, int world, long long lo,
+                                long long n, float scale, float* reduced, float* scalars, int sms, void* stream) {
+  if (world > MAX_PEERS || (n & 3) || (lo & 3)) return -10;
+  int grid = sms > 0 ? sms : 148 * 4;
+  if (mc_grad != nullptr)
+    zero_reduce_nvls_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float*>(mc_grad), lo, n, scale, reduced, scalars);
+  else
+    zero_reduce_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_table(grad_ptrs, world), world, lo,
+                                                                                 n, scale, reduced, scalars);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_zero_adam_gather(float* master, float* m, float* v, const float* g, const void* const* param_ptrs,
+                                     void* mc_param, int world, long long lo, long long n, const float* scalars,
+                                     float lr, float beta1, float beta2, float eps, float wd, int step,
+                                     const unsigned char* decay_mask, int sms, void* stream) {
+  if (world > MAX_PEERS || (n & 7) || (lo & 7)) return -10;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  int grid = sms > 0 ? sms : 148 * 4;
+  zero_adam_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      master, m, v, g, make_table(param_ptrs, world), reinterpret_cast<__nv_bfloat16*>(mc_param), world, lo, n, scalars,
+      lr, beta1, beta2, eps, wd, bc1, bc2, decay_mask);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_reshard_copy(const void* plan_dev, int n_entries, const void* const* src_ptrs, int world, void* dst,
+                                 void* stream) {
+  if (n_entries <= 0) return 0;
+  if (world > MAX_PEERS) return -10;
+  dim3 grid(n_entries, 8);
+  reshard_copy_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const ReshardEntry*>(plan_dev), make_table(src_ptrs, world), reinterpret_cast<__nv_bfloat16*>(dst));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

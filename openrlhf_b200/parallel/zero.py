@@ -69,7 +69,7 @@ class LRScheduler:
 class ZeroEngine:
     def __init__(self, model, lr: float = 1e-6, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  max_norm: float = 1.0, zero_stage: int = 2, group=None, scheduler: LRScheduler | None = None,
-                 train: bool = True, use_symm: bool | None = None):
+                 train: bool = True, use_symm: bool | None = None, symm=None):
         self.model = model
         self.flat = model.flat
         self.device = self.flat.device
@@ -96,7 +96,12 @@ class ZeroEngine:
         if not train:
             return
         on_gpu = self.flat.is_cuda
-        self.grad_flat = self._alloc_grad(bool(use_symm) and on_gpu and self.world > 1)
+        self.symm = symm if (symm is not None and on_gpu and self.world > 1) else None
+        if self.symm is not None:
+            assert self.symm.param.data_ptr() == self.flat.data_ptr(), "the model must be built on symm.param"
+            self.grad_flat = self.symm.grad
+        else:
+            self.grad_flat = torch.zeros(self.padded, dtype=torch.float32, device=self.device)
         for s, p in model.named_specs():
             p.main_grad = self.grad_flat[s.offset:s.offset + s.numel].view(s.shape)
         sl = slice(self.lo, self.hi)
@@ -117,15 +122,6 @@ class ZeroEngine:
     def padded_numel(total_numel: int, world: int) -> int:
         per = ((total_numel + world - 1) // world + 255) // 256 * 256
         return per * world
-
-    def _alloc_grad(self, use_symm: bool) -> torch.Tensor:
-        if use_symm:
-            from .symm import SymmBuffers
-
-            self.symm = SymmBuffers(self.group, self.padded, self.device, self.flat)
-            self.flat = self.symm.param          # the model's parameters now live in symmetric memory
-            return self.symm.grad
-        return torch.zeros(self.padded, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ training API
     def backward(self, loss: torch.Tensor):
@@ -208,7 +204,7 @@ class ZeroEngine:
                                        ctypes.c_int(int(zero_grad)), _lib.stream_ptr()), "adamw")
         else:
             # decoupled weight decay only on matrices: pre-scale the masked master weights, then plain Adam
-            self.master.mul_(torch.where(self.decay_mask, 1.0 - lr * self.wd, 1.0))
+            self.master.mul_(torch.where(self.decay_mask.bool(), 1.0 - lr * self.wd, 1.0))
             _lib.check_rc(L.b200_adamw(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
                                        _lib.ptr(g), _lib.ptr(pbf), ctypes.c_longlong(n), scale_ptr, ctypes.c_float(lr),
                                        ctypes.c_float(self.betas[0]), ctypes.c_float(self.betas[1]),
@@ -232,7 +228,7 @@ class ZeroEngine:
         self.exp_avg_sq.mul_(b2).addcmul_(gg, gg, value=1 - b2)
         bc1, bc2 = 1 - b1 ** self.opt_step, 1 - b2 ** self.opt_step
         if self.decay_mask is not None:
-            self.master.mul_(torch.where(self.decay_mask, 1.0 - lr * self.wd, 1.0))
+            self.master.mul_(torch.where(self.decay_mask.bool(), 1.0 - lr * self.wd, 1.0))
         denom = (self.exp_avg_sq / bc2).sqrt_().add_(self.eps)
         self.master.addcdiv_(self.exp_avg / bc1, denom, value=-lr)
         self.flat[self.lo:self.hi].copy_(self.master.to(self.flat.dtype))

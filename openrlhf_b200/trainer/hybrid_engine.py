@@ -63,7 +63,7 @@ class HybridRLWorker:
     def __init__(self, model_cfg: ModelConfig | str, args: SimpleNamespace | None = None, device=None,
                  reward_fn: Callable | None = None, max_steps: int = 1000, seed: int = 0, group=None,
                  max_num_seqs: int = 256, num_pages: int | None = None, use_cuda_graph: bool = True,
-                 with_critic: bool | None = None):
+                 with_critic: bool | None = None, use_symm: bool = False):
         self.args = args or default_rl_args()
         a = self.args
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -72,7 +72,17 @@ class HybridRLWorker:
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         cfg = ModelConfig.from_pretrained(model_cfg) if isinstance(model_cfg, str) else model_cfg
         self.cfg = cfg
-        self.model = TransformerLM(cfg, device=self.device, seed=seed, shard_world=self.world)
+        self.symm = None
+        flat = None
+        if use_symm and self.world > 1:
+            from ..parallel.symm import SymmBuffers
+            from ..models.transformer import build_param_specs, ALIGN
+
+            specs = build_param_specs(cfg)
+            total = specs[-1].offset + (specs[-1].numel + ALIGN - 1) // ALIGN * ALIGN
+            self.symm = SymmBuffers(group, ZeroEngine.padded_numel(total, self.world), self.device)
+            flat = self.symm.param
+        self.model = TransformerLM(cfg, device=self.device, seed=seed, shard_world=self.world, flat=flat)
         self.actor = Actor(self.model, temperature=a.rollout.temperature)
         if a.actor.gradient_checkpointing_enable:
             self.actor.gradient_checkpointing_enable()
@@ -80,7 +90,7 @@ class HybridRLWorker:
                             a.actor.lr_scheduler)
         self.engine = ZeroEngine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas), eps=a.actor.adam.eps,
                                  weight_decay=a.actor.adam.weight_decay, max_norm=a.actor.max_norm,
-                                 zero_stage=a.ds.zero_stage, group=group, scheduler=sched)
+                                 zero_stage=a.ds.zero_stage, group=group, scheduler=sched, symm=self.symm)
         self.ref = None
         if a.algo.kl.init_coef > 0:
             ref_model = TransformerLM(cfg, device=self.device, seed=None)

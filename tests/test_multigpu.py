@@ -1,0 +1,24 @@
+"""Multi-GPU tests: run the scripts of tests/dist_scripts under torchrun when at least two GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(script, nproc=2, env=None, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "dist_scripts", script)]
+    e = dict(os.environ)
+    e.update(env or {})
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def test_symm_optimizer_step_matches_nccl():
+    out = _run("zero_symm_vs_nccl.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "zero_symm_vs_nccl ok" in out
