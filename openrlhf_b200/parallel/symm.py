@@ -55,7 +55,7 @@ class SymmBuffers:
         if use_nvls is None:
             use_nvls = os.environ.get("OPENRLHF_B200_NVLS", "0") == "1"
         self.mc_param = self.mc_grad = 0
-        if use_nvls and self._hp.has_multicast_support():
+        if use_nvls and int(getattr(self._hp, 'multicast_ptr', 0) or 0) != 0:
             self.mc_param = int(self._hp.multicast_ptr)
             self.mc_grad = int(self._hg.multicast_ptr) if self._hg is not None else 0
         self.epoch = 0

@@ -43,7 +43,9 @@ def main():
         a, b = m_s.flat[:total].float(), m_n.flat[:total].float()
         diff = (a - b).abs().max().item()
         gn = abs(e_s.grad_norm() - e_n.grad_norm())
-        assert diff <= 1e-2 * b.abs().max().item() * 2 ** -6 + 1e-6, f"step {step}: param diff {diff}"
+        # the two paths sum the ranks in different orders: allow one bf16 ulp of the largest parameter
+        assert diff <= b.abs().max().item() * 2 ** -7, f"step {step}: param diff {diff}"
+        assert (a - b).abs().mean().item() <= 1e-6, "parameters drift apart on average"
         assert gn < 1e-3 * max(e_n.grad_norm(), 1e-6), f"grad norm differs by {gn}"
         assert float(e_s.grad_flat.abs().max()) == 0.0
     # every rank ends with the same full parameter buffer
