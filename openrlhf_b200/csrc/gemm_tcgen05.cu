@@ -30,6 +30,16 @@ struct GemmParams {
   long long split_stride;  // elements between the fp32 output slabs of consecutive K splits (0: all splits share C)
   float alpha;
   int* status;     // device status word (0 = ok)
+  // tensor-parallel extensions (all zero / null for a plain GEMM)
+  float* peer_c[8];     // fp32 accumulation buffers of the TP peers: the epilogue adds its tile into every one of
+  int n_peer_c;         //   them with red.add over NVLink (row-parallel linear: GEMM + all-reduce in one kernel)
+  int ag_world;         // >0: A is row-sharded over ag_world ranks (all-gather fused into the A-tile loads)
+  int ag_rows;          //   rows held by each rank (multiple of 128)
+};
+
+// Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
+struct PeerMaps {
+  CUtensorMap m[8];
 };
 
 template <int BN>
@@ -45,7 +55,7 @@ struct SmemLayout {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+                 const __grid_constant__ PeerMaps peer_a, const GemmParams p) {
   using L = SmemLayout<BN>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -117,7 +127,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           if (!A_MN) {
-            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, m_blk * BM);
+            if (p.ag_world > 0) {
+              const int row0 = m_blk * BM;
+              const int owner = row0 / p.ag_rows;
+              tma_load_2d(sa, &peer_a.m[owner], &full_bar[stage], kb * BK, row0 - owner * p.ag_rows);
+            } else {
+              tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, m_blk * BM);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -201,7 +217,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + j < p.N) {
                 float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
                                        __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                if (p.accumulate) {
+                if (p.n_peer_c > 0) {
+                  const size_t off = (size_t)row * p.ldc + col0 + j;
+                  for (int pr = 0; pr < p.n_peer_c; ++pr) {
+                    float* dst = p.peer_c[pr] + off;
+                    atomicAdd(dst, v.x);
+                    atomicAdd(dst + 1, v.y);
+                    atomicAdd(dst + 2, v.z);
+                    atomicAdd(dst + 3, v.w);
+                  }
+                } else if (p.accumulate) {
                   atomicAdd(crow + j, v.x);
                   atomicAdd(crow + j + 1, v.y);
                   atomicAdd(crow + j + 2, v.z);
@@ -304,7 +329,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const PeerMaps& pa, const GemmParams& p, int sms,
+                  cudaStream_t stream) {
   using L = SmemLayout<BN>;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
@@ -316,7 +342,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
   int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1);
   int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, p);
+  kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, pa, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -403,13 +429,69 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc;
   p.out_f32 = out_f32; p.accumulate = accumulate; p.k_splits = k_splits; p.split_stride = split_stride; p.alpha = alpha; p.status = status;
-#define B200_DISPATCH(BN_)                                                                  \
-  if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, g_sm_count, stream);     \
-  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, g_sm_count, stream);       \
-  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, p, g_sm_count, stream);       \
-  return launch<BN_, true, true>(ta, tb, p, g_sm_count, stream);
+  p.n_peer_c = 0; p.ag_world = 0; p.ag_rows = 0;
+  for (int i = 0; i < 8; ++i) p.peer_c[i] = nullptr;
+  static PeerMaps no_peers;
+#define B200_DISPATCH(BN_)                                                                            \
+  if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, no_peers, p, g_sm_count, stream);     \
+  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, no_peers, p, g_sm_count, stream);       \
+  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, no_peers, p, g_sm_count, stream);       \
+  return launch<BN_, true, true>(ta, tb, no_peers, p, g_sm_count, stream);
   if (bn == 256) { B200_DISPATCH(256) }
   if (bn == 128) { B200_DISPATCH(128) }
   B200_DISPATCH(64)
 #undef B200_DISPATCH
+}
+
+
+// Tensor-parallel linear layers of the rollout engine as single kernels (plain tiled TMA on peer memory for loads,
+// red.add over NVLink for the reduction; no collective launch in between).
+//  * row-parallel (o_proj / down_proj): C_partial = A[M, K/tp] * B[N, K/tp]^T is added, tile by tile from the epilogue,
+//    into the fp32 buffer `peer_c[r]` of every TP rank r: afterwards each rank holds the all-reduced sum.
+//  * column-parallel with sequence-parallel input (qkv / gate_up): A is row-sharded over the TP ranks
+//    (`a_shards[r]` = rank r's [rows_per_rank, K] block); the A-tile loads fetch the rows from their owner, i.e. the
+//    all-gather is fused into the operand loads. Output is bf16 C[M_total, N_local] (+ bias).
+extern "C" int b200_gemm_bf16_tp(const void* A, const void* const* a_shards, const void* B, void* C,
+                                 const void* const* peer_c, const void* bias, int M, int N, int K, int lda, int ldb,
+                                 int ldc, int tp, int rows_per_rank, int mode /*0: push-reduce, 1: gather-A*/, int bn,
+                                 int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tp < 1 || tp > 8 || (lda % 8) || (ldb % 8)) return -10;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (bn != 64 && bn != 128 && bn != 256) bn = N >= 2048 ? 256 : (N >= 512 ? 128 : 64);
+  CUtensorMap ta, tb;
+  PeerMaps pm = {};
+  GemmParams p;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.k_splits = 1; p.split_stride = 0; p.alpha = 1.f; p.status = status;
+  p.n_peer_c = 0; p.ag_world = 0; p.ag_rows = 0;
+  for (int i = 0; i < 8; ++i) p.peer_c[i] = nullptr;
+  int r;
+  if (mode == 0) {
+    if (ldc % 4 || N % 4) return -10;
+    r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
+    if (r) return r;
+    p.C = const_cast<void*>(peer_c[0]);
+    p.out_f32 = 1; p.accumulate = 1; p.n_peer_c = tp;
+    for (int i = 0; i < tp; ++i) p.peer_c[i] = reinterpret_cast<float*>(const_cast<void*>(peer_c[i]));
+  } else {
+    if (rows_per_rank % BM || M != rows_per_rank * tp || ldc % 8 || N % 8) return -10;
+    for (int i = 0; i < tp; ++i) {
+      r = make_tmap_bf16_2d(&pm.m[i], a_shards[i], rows_per_rank, K, lda, BM, BK);
+      if (r) return r;
+    }
+    ta = pm.m[0];
+    p.C = C; p.out_f32 = 0; p.accumulate = 0; p.ag_world = tp; p.ag_rows = rows_per_rank;
+  }
+  r = make_tmap_bf16_2d(&tb, B, N, K, ldb, bn, BK);
+  if (r) return r;
+  if (bn == 256) return launch<256, false, false>(ta, tb, pm, p, g_sm_count, stream);
+  if (bn == 128) return launch<128, false, false>(ta, tb, pm, p, g_sm_count, stream);
+  return launch<64, false, false>(ta, tb, pm, p, g_sm_count, stream);
 }

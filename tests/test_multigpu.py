@@ -22,3 +22,8 @@ def _run(script, nproc=2, env=None, timeout=600):
 def test_symm_optimizer_step_matches_nccl():
     out = _run("zero_symm_vs_nccl.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "zero_symm_vs_nccl ok" in out
+
+
+def test_fused_tp_gemms():
+    out = _run("tp_gemm.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "tp_gemm ok" in out
