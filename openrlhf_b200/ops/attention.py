@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -44,11 +45,98 @@ def _pick_varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale):
     _varlen_impl = tv
 
 
-def attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale):
-    """Packed causal GQA attention with autograd, through a library varlen flash-attention kernel."""
+def _query_tiles(cu_seqlens: torch.Tensor, T: int, n_seqs: int):
+    """Device-side list of 128-row query tiles: (tile_seq [n], tile_q0 [n]); n = T//128 + n_seqs is an upper bound,
+    surplus entries carry tile_seq = n_seqs (the kernel skips them). No host synchronisation."""
+    n = T // 128 + n_seqs
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).long()
+    per = (lens + 127) // 128
+    ends = torch.cumsum(per, 0)
+    t = torch.arange(n, device=cu_seqlens.device)
+    seq = torch.searchsorted(ends, t, right=True)
+    starts = ends - per
+    q0 = (t - starts[seq.clamp_max(n_seqs - 1)]) * 128
+    return seq.int().contiguous(), q0.int().contiguous(), n
+
+
+def attn_fwd_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, scale: float):
+    """tcgen05 causal varlen forward. q [T,Hq,128], k/v [T,Hkv,128] (views with a common row stride are fine).
+    Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D
+    assert k.stride(1) == D and v.stride(1) == D and k.stride(2) == 1 and v.stride(2) == 1
+    n_seqs = cu_seqlens.numel() - 1
+    tile_seq, tile_q0, n = _query_tiles(cu_seqlens, T, n_seqs)
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    rc = _lib.lib().b200_attn_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.c_int(q.stride(0)), ctypes.c_int(k.stride(0)),
+        ctypes.c_int(v.stride(0)), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0), _lib.ptr(cu_seqlens),
+        _lib.ptr(tile_seq), _lib.ptr(tile_q0), ctypes.c_int(n), _lib.ptr(out), ctypes.c_int(Hq * D), _lib.ptr(lse),
+        ctypes.c_int(n_seqs), ctypes.c_int(T), ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_float(scale),
+        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "attn_fwd")
+    return out, lse
+
+
+class _AttnVarlen(torch.autograd.Function):
+    """Forward on this repository's tcgen05 kernel; backward through a library varlen flash-attention backward fed
+    with that forward's output and log-sum-exp (or, if that entry point is unusable, by re-running the library
+    forward under autograd)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
+        out, lse = attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
+        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        global _fa_bwd_ok
+        if _fa_bwd_ok is not False:
+            try:
+                from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+                dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+                qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+                dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+                _flash_attn_varlen_backward(dout.contiguous(), qc, kc, vc, out, lse, dq, dk, dv, cu, cu,
+                                            ctx.max_seqlen, ctx.max_seqlen, 0.0, ctx.scale, True, -1, -1, 0.0, None,
+                                            False, None)
+                _fa_bwd_ok = True
+                return dq, dk, dv, None, None, None
+            except Exception:  # noqa: BLE001
+                if _fa_bwd_ok is True:
+                    raise
+                _fa_bwd_ok = False
+        with torch.enable_grad():
+            qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
+            o = _library_varlen(qd, kd, vd, cu, ctx.max_seqlen, ctx.scale)
+            dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), dout)
+        return dq, dk, dv, None, None, None
+
+
+_fa_bwd_ok = None
+USE_OWN_FWD = os.environ.get("OPENRLHF_B200_ATTN_FWD", "1") == "1"
+
+
+def _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale):
     if _varlen_impl is None:
         _pick_varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale)
     return _varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale)
+
+
+def attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale):
+    """Packed causal GQA attention with autograd."""
+    if USE_OWN_FWD and q.shape[-1] == 128 and q.dtype == torch.bfloat16 and q.stride(1) == 128 and k.stride(1) == 128 \
+            and v.stride(1) == 128:
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+            return _AttnVarlen.apply(q, k, v, cu_seqlens, max_seqlen, scale)
+        return attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)[0]
+    return _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale)
 
 
 _decode_ws: dict = {}

@@ -175,3 +175,44 @@ def test_rl_kernels_match_reference():
     l1 = K.value_loss(v, vals + 0.3, r1, mask, clip_eps=0.2); l2 = K.value_loss_reference(v2, vals + 0.3, r1, mask, clip_eps=0.2)
     l1.backward(); l2.backward()
     _close(l1, l2, rtol=1e-3, atol=1e-5); _close(v.grad, v2.grad, rtol=1e-3, atol=1e-6)
+
+
+@pytest.mark.parametrize("Hq,Hkv,lens", [(4, 2, [1, 127, 128, 129, 300]), (12, 2, [513, 40]), (8, 8, [1024])])
+def test_attn_fwd_tcgen05(Hq, Hkv, lens):
+    from openrlhf_b200.ops import _lib, reference as R
+    from openrlhf_b200.ops.attention import attn_fwd_tcgen05
+    torch.manual_seed(0)
+    T, D = sum(lens), 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    out, lse = attn_fwd_tcgen05(q, k, v, cu, scale)
+    _lib.check_status()
+    ref = R.attention_varlen(q, k, v, cu, scale)
+    _close(out, ref, rtol=2e-2, atol=2e-2)
+    # log-sum-exp against a direct computation for the first sequence / head 0
+    L = lens[0]
+    s = (q[:L, 0].float() @ k[:L, 0].float().t()) * scale
+    s = s.masked_fill(~torch.ones(L, L, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    _close(lse[0, :L], torch.logsumexp(s, -1), rtol=1e-2, atol=1e-2)
+
+
+def test_attention_autograd_matches_reference():
+    from openrlhf_b200.ops import functional as F, reference as R
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 300, 4, 2, 128
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cu = torch.tensor([0, 100, 300], device="cuda", dtype=torch.int32)
+    out = F.attention_varlen(q, k, v, cu, 200)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = R.attention_varlen(qr, kr, vr, cu, 1 / math.sqrt(D))
+    ref.backward(g.float())
+    _close(out, ref); _close(q.grad, qr.grad, rtol=3e-2, atol=3e-2)
+    _close(k.grad, kr.grad, rtol=3e-2, atol=3e-2); _close(v.grad, vr.grad, rtol=3e-2, atol=3e-2)
