@@ -127,7 +127,8 @@ def main():
 
     worker = HybridRLWorker(args.model, rl_args, device=f"cuda:{local}", reward_fn=rule_reward, seed=0, group=group,
                             max_num_seqs=P * n, num_pages=P * n * ((L + new) // 128 + 1) + P * (L // 128) + 8,
-                            use_cuda_graph=not args.no_graph)
+                            use_cuda_graph=not args.no_graph,
+                            use_symm=world > 1 and os.environ.get("OPENRLHF_B200_SYMM", "1") == "1")
     vocab = worker.cfg.vocab_size
     g = torch.Generator().manual_seed(1234 + rank)
     total_steps = args.warmup + 2 * args.steps
@@ -189,7 +190,7 @@ def main():
             "config": {"model": args.model, "global_batch": P * n * world, "seq_len": L + new,
                        "prompts_per_gpu": P, "prompt_len": L, "n_samples_per_prompt": n, "max_new_tokens": new,
                        "estimator": "reinforce_baseline", "zero_stage": 2, "micro_batch": args.micro,
-                       "parallelism": f"dp{world}", "l2": "working set (3 GB weights + KV cache) is larger than L2"},
+                       "parallelism": f"dp{world}", "optimizer_step": ("peer-memory kernels" if worker.symm is not None else ("nccl" if world > 1 else "local")), "l2": "working set (3 GB weights + KV cache) is larger than L2"},
             "clocks": clocks,
             "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": P * L * 8,
                     "d2h_bytes_per_step": d2h // args.steps},
