@@ -394,3 +394,137 @@ extern "C" int b200_cast_f32_bf16(const float* src, void* dst, long long n, void
   cast_f32_bf16_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, STREAM(stream)>>>(src, (__nv_bfloat16*)dst, n);
   return LAUNCH_OK();
 }
+
+// ------------------------------------------------------------------ fused decode-path kernels
+namespace b200 {
+
+// h = bf16(sum_s ws[s] (+ residual)); x = rmsnorm(h) * w. One block per row. Finishes a split-K GEMM and runs the
+// following RMSNorm in the same pass (rollout decode loop: o_proj / down_proj -> next norm).
+__global__ void __launch_bounds__(NORM_THREADS)
+splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long slab,
+                             const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
+                             __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ x_out, int M, int N,
+                             float eps) {
+  extern __shared__ uint4 row_cache[];
+  __shared__ float red[32];
+  const int nvec = N >> 3;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS) {
+      float f[8];
+      const float4* base = reinterpret_cast<const float4*>(ws + (size_t)row * N) + 2 * v;
+      float4 a = base[0], b = base[1];
+      for (int s = 1; s < splits; ++s) {
+        const float4* bs = reinterpret_cast<const float4*>(ws + (size_t)s * slab + (size_t)row * N) + 2 * v;
+        const float4 c = bs[0], d = bs[1];
+        a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+        b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+      }
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+      if (residual != nullptr) {
+        float g[8];
+        unpack8(reinterpret_cast<const uint4*>(residual + (size_t)row * N)[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i]);
+      const uint4 u = pack8(f);
+      reinterpret_cast<uint4*>(h_out + (size_t)row * N)[v] = u;
+      row_cache[v] = u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = block_sum<NORM_THREADS>(ss, red);
+    const float rstd = rsqrtf(ss / (float)N + eps);
+    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS) {
+      float f[8], g[8];
+      unpack8(row_cache[v], f);
+      unpack8(reinterpret_cast<const uint4*>(w)[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * rstd) * g[i];
+      reinterpret_cast<uint4*>(x_out + (size_t)row * N)[v] = pack8(f);
+    }
+    __syncthreads();
+  }
+}
+
+// Finishes the split-K qkv projection (sum of slabs + bias), applies RoPE to q and k, writes q compactly and k, v
+// into the paged KV cache. head_dim 128.
+__global__ void rope_kvwrite_splitk_kernel(const float* __restrict__ ws, int splits, long long slab,
+                                           const __nv_bfloat16* __restrict__ bias, const int* __restrict__ pos,
+                                           const int* __restrict__ slots, const float2* __restrict__ cos_sin,
+                                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                           __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv, int max_pos) {
+  constexpr int HALF = 64;
+  const int heads = Hq + 2 * Hkv;
+  const int ld = heads * 128;
+  const long long total = (long long)T * heads * (HALF / 2);
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % (HALF / 2)) * 2;
+    const int head = (int)((idx / (HALF / 2)) % heads);
+    const int t = (int)(idx / ((long long)(HALF / 2) * heads));
+    const size_t off = (size_t)t * ld + head * 128 + i;
+    float2 lo = *reinterpret_cast<const float2*>(ws + off);
+    float2 hi = *reinterpret_cast<const float2*>(ws + off + HALF);
+    for (int s = 1; s < splits; ++s) {
+      const float2 a = *reinterpret_cast<const float2*>(ws + (size_t)s * slab + off);
+      const float2 b = *reinterpret_cast<const float2*>(ws + (size_t)s * slab + off + HALF);
+      lo.x += a.x; lo.y += a.y; hi.x += b.x; hi.y += b.y;
+    }
+    if (bias != nullptr) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + head * 128 + i));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias + head * 128 + i + HALF));
+      lo.x += a.x; lo.y += a.y; hi.x += b.x; hi.y += b.y;
+    }
+    // the unfused path rounds the projection to bf16 before the rotation: keep the same rounding points
+    lo.x = round_bf16(lo.x); lo.y = round_bf16(lo.y); hi.x = round_bf16(hi.x); hi.y = round_bf16(hi.y);
+    __nv_bfloat16* dst;
+    if (head < Hq) {
+      dst = q_out + ((size_t)t * Hq + head) * 128;
+    } else {
+      const int slot = slots[t];
+      if (slot < 0) continue;
+      if (head < Hq + Hkv) dst = k_cache + ((size_t)slot * Hkv + (head - Hq)) * 128;
+      else dst = v_cache + ((size_t)slot * Hkv + (head - Hq - Hkv)) * 128;
+    }
+    if (head < Hq + Hkv) {
+      int pp = pos[t];
+      pp = pp < 0 ? 0 : (pp >= max_pos ? max_pos - 1 : pp);
+      const float2 c0 = cos_sin[(size_t)pp * HALF + i], c1 = cos_sin[(size_t)pp * HALF + i + 1];
+      float2 ol, oh;
+      ol.x = lo.x * c0.x - hi.x * c0.y;
+      oh.x = hi.x * c0.x + lo.x * c0.y;
+      ol.y = lo.y * c1.x - hi.y * c1.y;
+      oh.y = hi.y * c1.x + lo.y * c1.y;
+      lo = ol;
+      hi = oh;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(lo.x, lo.y);
+    *reinterpret_cast<__nv_bfloat162*>(dst + i + HALF) = __floats2bfloat162_rn(hi.x, hi.y);
+  }
+}
+
+}  // namespace b200
+
+extern "C" int b200_splitk_reduce_rmsnorm(const float* ws, int splits, const void* residual, const void* w, void* h_out,
+                                          void* x_out, int M, int N, float eps, void* stream) {
+  if (M <= 0) return 0;
+  if (N % 8 || N > 16384) return -10;
+  int grid = M < 148 * 8 ? M : 148 * 8;
+  splitk_reduce_rmsnorm_kernel<<<grid, NORM_THREADS, (N / 8) * sizeof(uint4), STREAM(stream)>>>(
+      ws, splits, (long long)M * N, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)h_out,
+      (__nv_bfloat16*)x_out, M, N, eps);
+  return LAUNCH_OK();
+}
+extern "C" int b200_rope_kvwrite_splitk(const float* ws, int splits, const void* bias, const int* pos, const int* slots,
+                                        const void* cos_sin, void* q_out, void* k_cache, void* v_cache, int T, int Hq,
+                                        int Hkv, int max_pos, void* stream) {
+  if (T <= 0) return 0;
+  long long work = (long long)T * (Hq + 2 * Hkv) * 32;
+  rope_kvwrite_splitk_kernel<<<grid_for(work, 256, 148 * 16), 256, 0, STREAM(stream)>>>(
+      ws, splits, (long long)T * (Hq + 2 * Hkv) * 128, (const __nv_bfloat16*)bias, pos, slots, (const float2*)cos_sin,
+      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, Hq, Hkv, max_pos);
+  return LAUNCH_OK();
+}

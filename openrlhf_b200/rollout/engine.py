@@ -14,6 +14,7 @@ to hand out KV pages and retire finished rows.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass, field
 
@@ -228,6 +229,62 @@ class RolloutEngine:
     def _decode_step(self, B: int):
         """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
         cfg, m = self.cfg, self.model
+        fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None
+        if fused:
+            logits = self._decode_layers_fused(B)
+        else:
+            logits = self._decode_layers_generic(B)
+        sample(logits, temperature=self.temperature[:B], top_k=self.top_k, top_p=self.top_p, seed=self.seed,
+               step=self.step_counter, out_tokens=self.next_tok[:B], out_logprobs=self.next_lp[:B],
+               active=self.active[:B])
+        self._advance(B)
+
+    def _decode_layers_fused(self, B: int):
+        """Dense decoder layers in 8 launches each: every split-K projection leaves fp32 slabs in the workspace and the
+        kernel that follows finishes the reduction together with its own work (bias + RoPE + KV write after qkv,
+        residual + RMSNorm after o_proj and down_proj)."""
+        cfg, m = self.cfg, self.model
+        L = _lib.lib()
+        Hq, Hkv, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        table = m.rope(self.device)
+        tok, pos, slots = self.tok[:B], self.pos[:B], self.slots[:B]
+        bt, sl = self.block_table[:B], self.seq_lens[:B]
+        q_buf, attn_buf = self.q_buf[:B], self.attn_buf[:B]
+        st = _lib.stream_ptr
+        i32, f32 = ctypes.c_int, ctypes.c_float
+
+        def reduce_norm(ws, splits, residual, w):
+            h = torch.empty(B, H, dtype=torch.bfloat16, device=self.device)
+            x = torch.empty_like(h)
+            rc = L.b200_splitk_reduce_rmsnorm(_lib.ptr(ws), i32(splits), _lib.ptr(residual), _lib.ptr(w), _lib.ptr(h),
+                                              _lib.ptr(x), i32(B), i32(H), f32(cfg.rms_norm_eps), st())
+            _lib.check_rc(rc, "splitk_reduce_rmsnorm")
+            return h, x
+
+        h = F.embedding(tok, m.p("embed.weight"))
+        x = F.rmsnorm(h, m.p("layers.0.norm1.weight"), cfg.rms_norm_eps)
+        nl = cfg.num_hidden_layers
+        for i in range(nl):
+            pre = f"layers.{i}."
+            ws, s = gemm_to_workspace(x, m.p(pre + "qkv.weight"))
+            rc = L.b200_rope_kvwrite_splitk(_lib.ptr(ws), i32(s), _lib.ptr(m._params.get(pre + "qkv.bias")),
+                                            _lib.ptr(pos), _lib.ptr(slots), _lib.ptr(table), _lib.ptr(q_buf),
+                                            _lib.ptr(self.kv[i, 0]), _lib.ptr(self.kv[i, 1]), i32(B), i32(Hq), i32(Hkv),
+                                            i32(table.shape[0]), st())
+            _lib.check_rc(rc, "rope_kvwrite_splitk")
+            paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
+            ws, s = gemm_to_workspace(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"))
+            h, x = reduce_norm(ws, s, h, m.p(pre + "norm2.weight"))
+            gu = gemm(x, m.p(pre + "gate_up.weight"), bn=128)
+            a = F.swiglu(gu)
+            ws, s = gemm_to_workspace(a, m.p(pre + "down.weight"))
+            nxt = m.p(f"layers.{i + 1}.norm1.weight") if i + 1 < nl else m.p("norm.weight")
+            h, x = reduce_norm(ws, s, h, nxt)
+        return gemm(x, m.lm_head_weight())
+
+    def _decode_layers_generic(self, B: int):
+        cfg, m = self.cfg, self.model
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         scale = 1.0 / math.sqrt(cfg.head_dim)
         table = m.rope(self.device)
@@ -238,7 +295,8 @@ class RolloutEngine:
         for i in range(cfg.num_hidden_layers):
             pre = f"layers.{i}."
             x = F.rmsnorm(h, m.p(pre + "norm1.weight"), cfg.rms_norm_eps)
-            qkv = decode_gemm(x, m.p(pre + "qkv.weight"), m._params.get(pre + "qkv.bias"))
+            qkv = m._lin(i, "qkv", x, m._params.get(pre + "qkv.bias")) if m.lora is not None else \
+                decode_gemm(x, m.p(pre + "qkv.weight"), m._params.get(pre + "qkv.bias"))
             if cfg.qk_norm:
                 T = qkv.shape[0]
                 qk = qkv[:, : (Hq + Hkv) * 128].reshape(T, Hq + Hkv, 128)
@@ -247,7 +305,8 @@ class RolloutEngine:
                 qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * 128:]], dim=1)
             rope_kvwrite(qkv, pos, slots, table, q_buf, self.kv[i, 0], self.kv[i, 1], Hq, Hkv)
             paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
-            h = decode_gemm(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"), None, h)
+            ao = attn_buf.view(B, Hq * 128)
+            h = m._lin(i, "o", ao, None, h) if m.lora is not None else decode_gemm(ao, m.p(pre + "o.weight"), None, h)
             x = F.rmsnorm(h, m.p(pre + "norm2.weight"), cfg.rms_norm_eps)
             if cfg.is_moe_layer(i):
                 from ..models.moe import moe_forward
@@ -255,16 +314,14 @@ class RolloutEngine:
                 y, _ = moe_forward(x, m.p(pre + "router.weight"), m.p(pre + "experts.gate_up"),
                                    m.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob)
                 h = h + y
+            elif m.lora is not None:
+                h = m._lin(i, "down", F.swiglu(m._lin(i, "gate_up", x)), None, h)
             else:
                 gu = decode_gemm(x, m.p(pre + "gate_up.weight"))
                 a = F.swiglu(gu)
                 h = decode_gemm(a, m.p(pre + "down.weight"), None, h)
         x = F.rmsnorm(h, m.p("norm.weight"), cfg.rms_norm_eps)
-        logits = gemm(x, m.lm_head_weight())
-        sample(logits, temperature=self.temperature[:B], top_k=self.top_k, top_p=self.top_p, seed=self.seed,
-               step=self.step_counter, out_tokens=self.next_tok[:B], out_logprobs=self.next_lp[:B],
-               active=self.active[:B])
-        self._advance(B)
+        return gemm(x, m.lm_head_weight())
 
     def _advance(self, B: int):
         act = self.active[:B].bool()
@@ -509,7 +566,24 @@ class RolloutEngine:
 
 
 # ---------------------------------------------------------------------------------------------- decode GEMM
-_SPLITK_WS: dict = {}
+def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor):
+    """Split-K projection for small M whose fp32 slabs stay in the shared workspace for the next kernel to reduce.
+    Returns (workspace, number of slabs)."""
+    from ..ops.gemm import splitk_workspace
+
+    M, K = x.shape
+    N = w.shape[0]
+    bn = 64 if N <= 4096 else 128
+    tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+    kb = (K + 63) // 64
+    splits = max(1, min(148 // max(tiles, 1), kb // 4))
+    per = (kb + splits - 1) // splits
+    splits = (kb + per - 1) // per
+    ws = splitk_workspace(x.device, splits * M * N)
+    gemm(x, w, out=ws, k_splits=splits, split_stride=M * N, bn=bn)
+    return ws, splits
+
+
 
 
 def decode_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,

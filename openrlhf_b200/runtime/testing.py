@@ -51,3 +51,8 @@ class EchoWorker:
 
     def die(self):
         os._exit(3)
+
+
+class EnvWorker:
+    def env(self, keys):
+        return {k: os.environ.get(k) for k in keys}
