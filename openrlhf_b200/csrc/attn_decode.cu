@@ -54,6 +54,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
+  pdl_wait();   // seq_lens / block_table / q / the KV cache come from earlier kernels of the stream
   const int len = p.seq_lens[b];
   const int n_tiles_all = (len + PAGE - 1) / PAGE;
   const int tiles_per_split = (n_tiles_all + p.splits - 1) / p.splits;
@@ -82,6 +83,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;        // 16 columns
   const uint32_t tmem_o = tmem_base + 32;   // 16 columns
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (n_tiles > 0) {
     if (warp == 0) {
@@ -358,8 +361,7 @@ extern "C" int b200_attn_decode(const void* q, const void* k_cache, const void* 
   p.part_o = part_o; p.part_ml = part_ml; p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
   dim3 grid(Hkv, B, splits);
-  attn_decode_kernel<<<grid, 192, DecSmem::TOTAL, stream>>>(tq, tk, tv, p);
-  if (cudaGetLastError() != cudaSuccess) return -3;
+  if (launch_pdl(attn_decode_kernel, grid, dim3(192), (size_t)DecSmem::TOTAL, stream, tq, tk, tv, p) != cudaSuccess) return -3;
   if (splits > 1) {
     attn_decode_merge_kernel<<<B * Hq, HD, 0, stream>>>(part_o, part_ml, reinterpret_cast<__nv_bfloat16*>(out), B * Hq,
                                                         splits);

@@ -52,6 +52,8 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int T, int H, int ldx, int ldy,
                    float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ uint4 row_cache[];  // H/8 vectors
   __shared__ float red[32];
   const int nvec = H >> 3;
@@ -169,6 +171,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restri
 // ------------------------------------------------------------------ SwiGLU: y = silu(g) * u, gu = [g | u]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, long long T,
                                   int F) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int nvec = F >> 3;
   const long long total = T * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -212,6 +216,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ------------------------------------------------------------------ embedding
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, int T, int H, int V) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int nvec = H >> 3;
   const long long total = (long long)T * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -310,10 +316,9 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, v
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8 || ldy % 8 || H > 16384) return -10;
   int grid = T < 148 * 8 ? T : 148 * 8;
-  rmsnorm_fwd_kernel<<<grid, NORM_THREADS, (H / 8) * sizeof(uint4), STREAM(stream)>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-      (__nv_bfloat16*)h_out, rstd, T, H, ldx, ldy, eps);
-  return LAUNCH_OK();
+  return launch_pdl(rmsnorm_fwd_kernel, dim3(grid), dim3(NORM_THREADS), (size_t)(H / 8) * sizeof(uint4), STREAM(stream),
+                    (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+                    (__nv_bfloat16*)h_out, rstd, T, H, ldx, ldy, eps) == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in,
                                 void* dx, float* dw, int T, int H, void* stream) {
@@ -337,9 +342,8 @@ extern "C" int b200_rope(void* qkv, const int* pos, const void* cos_sin, int T, 
 extern "C" int b200_swiglu_fwd(const void* gu, void* y, long long T, int F, void* stream) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256, 148 * 16), 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)gu,
-                                                                                      (__nv_bfloat16*)y, T, F);
-  return LAUNCH_OK();
+  return launch_pdl(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256, 148 * 16)), dim3(256), (size_t)0, STREAM(stream),
+                    (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, T, F) == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_swiglu_bwd(const void* gu, const void* dy, void* dgu, long long T, int F, void* stream) {
   if (T <= 0) return 0;
@@ -352,9 +356,8 @@ extern "C" int b200_embedding_fwd(const long long* ids, const void* table, void*
                                   void* stream) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  embedding_fwd_kernel<<<grid_for((long long)T * (H / 8), 256, 148 * 16), 256, 0, STREAM(stream)>>>(
-      ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V);
-  return LAUNCH_OK();
+  return launch_pdl(embedding_fwd_kernel, dim3(grid_for((long long)T * (H / 8), 256, 148 * 16)), dim3(256), (size_t)0,
+                    STREAM(stream), ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V) == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_embedding_bwd(const long long* ids, const void* dout, float* grad_table, int T, int H, int V,
                                   void* stream) {
@@ -405,6 +408,8 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long
                              const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
                              __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ x_out, int M, int N,
                              float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ uint4 row_cache[];
   __shared__ float red[32];
   const int nvec = N >> 3;
@@ -456,6 +461,8 @@ __global__ void rope_kvwrite_splitk_kernel(const float* __restrict__ ws, int spl
                                            const int* __restrict__ slots, const float2* __restrict__ cos_sin,
                                            __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                                            __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv, int max_pos) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int HALF = 64;
   const int heads = Hq + 2 * Hkv;
   const int ld = heads * 128;
@@ -513,18 +520,17 @@ extern "C" int b200_splitk_reduce_rmsnorm(const float* ws, int splits, const voi
   if (M <= 0) return 0;
   if (N % 8 || N > 16384) return -10;
   int grid = M < 148 * 8 ? M : 148 * 8;
-  splitk_reduce_rmsnorm_kernel<<<grid, NORM_THREADS, (N / 8) * sizeof(uint4), STREAM(stream)>>>(
-      ws, splits, (long long)M * N, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)h_out,
-      (__nv_bfloat16*)x_out, M, N, eps);
-  return LAUNCH_OK();
+  return launch_pdl(splitk_reduce_rmsnorm_kernel, dim3(grid), dim3(NORM_THREADS), (size_t)(N / 8) * sizeof(uint4),
+                    STREAM(stream), ws, splits, (long long)M * N, (const __nv_bfloat16*)residual,
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, M, N, eps) == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_rope_kvwrite_splitk(const float* ws, int splits, const void* bias, const int* pos, const int* slots,
                                         const void* cos_sin, void* q_out, void* k_cache, void* v_cache, int T, int Hq,
                                         int Hkv, int max_pos, void* stream) {
   if (T <= 0) return 0;
   long long work = (long long)T * (Hq + 2 * Hkv) * 32;
-  rope_kvwrite_splitk_kernel<<<grid_for(work, 256, 148 * 16), 256, 0, STREAM(stream)>>>(
-      ws, splits, (long long)T * (Hq + 2 * Hkv) * 128, (const __nv_bfloat16*)bias, pos, slots, (const float2*)cos_sin,
-      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, Hq, Hkv, max_pos);
-  return LAUNCH_OK();
+  return launch_pdl(rope_kvwrite_splitk_kernel, dim3(grid_for(work, 256, 148 * 16)), dim3(256), (size_t)0, STREAM(stream),
+                    ws, splits, (long long)T * (Hq + 2 * Hkv) * 128, (const __nv_bfloat16*)bias, pos, slots,
+                    (const float2*)cos_sin, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T,
+                    Hq, Hkv, max_pos) == cudaSuccess ? 0 : -3;
 }

@@ -95,6 +95,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                 // operands and C may be produced / still read by the previous kernel in the stream
+  pdl_launch_dependents();    // the next kernel may run its prologue while this one works
 
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& kb0, int& kb1) {
     int split = tile % splits;
@@ -342,8 +344,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const PeerMaps& 
   int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
   int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1);
   int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, 192, L::TOTAL, stream>>>(ta, tb, pa, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return launch_pdl(kern, dim3(grid), dim3(192), (size_t)L::TOTAL, stream, ta, tb, pa, p) == cudaSuccess ? 0 : -3;
 }
 
 // out[m, n] = bf16(sum_s ws[s, m, n] + bias[n] + residual[m, n]); ws holds the fp32 partial products of a split-K GEMM.
