@@ -107,6 +107,7 @@ class RolloutEngine:
         self.blocks = BlockManager(self.num_pages)
         self.dummy_page = self.blocks.alloc()  # page 0 backs inactive rows
         self.kv = None
+        self.arena = None
         self._alloc_kv()
         B = max_num_seqs
         dev = self.device
@@ -147,22 +148,45 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ memory
     def _alloc_kv(self):
+        """KV cache [layers, 2, pages*128, kv_heads, 128] inside a VMM arena: its address survives sleep / wake."""
         cfg = self.cfg
-        self.kv = torch.zeros(cfg.num_hidden_layers, 2, self.num_pages * PAGE, cfg.num_key_value_heads, 128,
-                              dtype=torch.bfloat16, device=self.device)
+        shape = (cfg.num_hidden_layers, 2, self.num_pages * PAGE, cfg.num_key_value_heads, 128)
+        if getattr(self, "arena", None) is None:
+            try:
+                from .block_manager import VmmArena
+
+                nbytes = 2
+                for d in shape:
+                    nbytes *= d
+                self.arena = VmmArena(nbytes, self.device)
+            except Exception:  # noqa: BLE001  (driver without VMM support: plain allocation, graphs dropped on sleep)
+                self.arena = None
+        if self.arena is not None:
+            if not self.arena.mapped:
+                self.arena.map()
+            self.kv = self.arena.tensor(torch.bfloat16, shape)
+            self.kv.zero_()       # stale V rows are multiplied by zero probabilities: they must be finite
+        else:
+            self.kv = torch.zeros(*shape, dtype=torch.bfloat16, device=self.device)
 
     def sleep(self, level: int = 1):
-        """Release the KV cache (and captured graphs that point into it). Weights stay resident: trainer and rollout
-        share them on this GPU. Counterpart of vLLM sleep mode as used at openrlhf/trainer/ray/vllm_engine.py:138-153."""
-        self.graphs.clear()
-        self.kv = None
-        torch.cuda.empty_cache()
+        """Release the physical memory of the KV cache. Weights stay resident: trainer and rollout share them on this
+        GPU. With the VMM arena the cache keeps its address, so captured decode graphs stay valid across sleep / wake
+        (counterpart of vLLM sleep mode as used at openrlhf/trainer/ray/vllm_engine.py:138-153)."""
+        if self.sleeping:
+            return
+        if self.arena is not None:
+            self.arena.unmap()
+        else:
+            self.graphs.clear()
+            self.kv = None
+            torch.cuda.empty_cache()
         self.sleeping = True
 
     def wake_up(self, tags=None):
         if tags is not None and "kv_cache" not in tags:
             return  # weights are always resident
-        if self.kv is None:
+        if self.sleeping:
             self._alloc_kv()
         self.sleeping = False
 

@@ -74,3 +74,19 @@ def test_rollout_matches_trainer_logprobs_and_greedy():
 def test_rl_step_smoke():
     import __graft_entry__ as ge
     ge.smoke()
+
+
+def test_engine_sleep_wake_keeps_graphs_and_results():
+    from openrlhf_b200.rollout.engine import RolloutEngine, SamplingParams
+    cfg, m = _tiny()
+    eng = RolloutEngine(m, max_num_seqs=4, max_model_len=256, num_pages=16, seed=1)
+    p = [torch.randint(3, cfg.vocab_size, (9,)).tolist()]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    a = eng.generate(p, sp)[0].outputs[0].token_ids
+    free0 = torch.cuda.mem_get_info()[0]
+    n_graphs = len(eng.graphs)
+    eng.sleep()
+    assert eng.arena is None or torch.cuda.mem_get_info()[0] > free0
+    eng.wake_up()
+    b = eng.generate(p, sp)[0].outputs[0].token_ids
+    assert a == b and (eng.arena is None or len(eng.graphs) == n_graphs)
