@@ -1,0 +1,137 @@
+"""Kernel micro-benchmarks: ``python -m openrlhf_b200.bench_kernels --kernel gemm --m 8192 --n 8960 --k 1536``.
+
+Times one kernel with CUDA events (3 warm-up launches, L2 flushed between timed launches by writing a 256 MiB
+buffer) and prints achieved FLOP/s or bytes/s next to the measured peaks in MEASURED_PEAKS.json when that file is
+present. The same command line is what the ncu summaries under ``profiles/`` were captured with."""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "of measured"
+    except OSError:
+        return 6650.0, 1590.0, "of fallback"
+
+
+def _time(fn, iters: int, flush: bool = True) -> float:
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) * 1e-3)
+    return sorted(ts)[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_splitk", "decode_attn", "attn_fwd", "logprob",
+                                                         "rmsnorm", "adamw"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8960)
+    ap.add_argument("--k", type=int, default=1536)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"], help="nt: fwd, nn: dgrad, tn: wgrad")
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=1550)
+    ap.add_argument("--hq", type=int, default=12)
+    ap.add_argument("--hkv", type=int, default=2)
+    ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    from openrlhf_b200.ops import _lib
+    from openrlhf_b200.ops import functional as F
+    from openrlhf_b200.ops.attention import attn_fwd_tcgen05, paged_decode
+    from openrlhf_b200.ops.gemm import gemm, gemm_splitk
+
+    hbm, tf, tag = _peaks()
+    dev = "cuda"
+    if a.kernel in ("gemm", "gemm_splitk"):
+        M, N, K = a.m, a.n, a.k
+        a_mn, b_mn = a.layout == "tn", a.layout in ("nn", "tn")
+        A = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)
+        B = torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16)
+        if a.kernel == "gemm":
+            fn = lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn)
+        else:
+            fn = lambda: gemm_splitk(A, B, a.splits)
+        t = _time(fn, a.iters)
+        fl = 2.0 * M * N * K
+        byt = 2.0 * (M * K + N * K + M * N)
+        print(f"{a.kernel} M{M} N{N} K{K} {a.layout}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+              f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak), {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "decode_attn":
+        B_, Hq, Hkv, ctx = a.batch, a.hq, a.hkv, a.ctx
+        per = ctx // 128 + 1
+        kv = torch.randn(2, (B_ * per + 8) * 128, Hkv, 128, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B_ * per, device=dev, dtype=torch.int32).reshape(B_, per)
+        sl = torch.full((B_,), ctx, device=dev, dtype=torch.int32)
+        q = torch.randn(B_, Hq, 128, device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: paged_decode(q, kv[0], kv[1], bt, sl, 1 / math.sqrt(128), splits=a.splits), a.iters)
+        byt = B_ * ctx * 2 * Hkv * 128 * 2
+        print(f"decode_attn B{B_} Hq{Hq} Hkv{Hkv} ctx{ctx} splits{a.splits}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s "
+              f"({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "attn_fwd":
+        T, Hq, Hkv, L = a.m, a.hq, a.hkv, a.ctx
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device=dev, dtype=torch.bfloat16)
+        q = qkv[:, : Hq * 128].view(T, Hq, 128)
+        k = qkv[:, Hq * 128:(Hq + Hkv) * 128].view(T, Hkv, 128)
+        v = qkv[:, (Hq + Hkv) * 128:].view(T, Hkv, 128)
+        cu = torch.arange(0, T + 1, L, device=dev, dtype=torch.int32)
+        t = _time(lambda: attn_fwd_tcgen05(q, k, v, cu, 1 / math.sqrt(128)), a.iters)
+        fl = 4.0 * (T // L) * (L * (L + 128) / 2) * Hq * 128
+        print(f"attn_fwd T{T} seq{L} Hq{Hq} Hkv{Hkv}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+              f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
+    elif a.kernel == "logprob":
+        T, V, H = a.m, a.n, a.k
+        h = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+        w = (0.02 * torch.randn(V, H, device=dev)).to(torch.bfloat16)
+        y = torch.randint(0, V, (T,), device=dev)
+        with torch.no_grad():
+            t = _time(lambda: F.fused_logprob(h, w, y), a.iters)
+        fl = 2.0 * T * V * H
+        print(f"logprob T{T} V{V} H{H}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s ({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
+    elif a.kernel == "rmsnorm":
+        T, H = a.m, a.k
+        x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            t = _time(lambda: F.rmsnorm(x, w, 1e-6), a.iters)
+        byt = 4.0 * T * H
+        print(f"rmsnorm T{T} H{H}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "adamw":
+        import ctypes
+
+        n = a.m * a.k
+        ms, m1, v1, g = (torch.randn(n, device=dev) for _ in range(4))
+        pb = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        L = _lib.lib()
+        fn = lambda: L.b200_adamw(_lib.ptr(ms), _lib.ptr(m1), _lib.ptr(v1), _lib.ptr(g), _lib.ptr(pb),
+                                  ctypes.c_longlong(n), None, ctypes.c_float(1e-5), ctypes.c_float(0.9),
+                                  ctypes.c_float(0.95), ctypes.c_float(1e-8), ctypes.c_float(0.0), ctypes.c_int(1),
+                                  ctypes.c_int(1), _lib.stream_ptr())
+        t = _time(fn, a.iters)
+        byt = n * (4 * 4 + 3 * 4 + 4 + 2)
+        print(f"adamw n{n}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    _lib.check_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -30,12 +30,17 @@ struct DecodeParams {
 
 struct DecSmem {
   static constexpr int Q_OFF = 0;                         // 2 panels x 16 rows x 128 B
-  static constexpr int P_OFF = 4096;                      // 2 panels x 16 rows x 128 B
-  static constexpr int KV_OFF = 8192;                     // stages x (K 32 KB + V 32 KB)
+  static constexpr int P_OFF = 4096;                      // 2 buffers x (2 panels x 16 rows x 128 B)
+  static constexpr int KV_OFF = 12288;                    // stages x (K 32 KB + V 32 KB)
   static constexpr int BAR_OFF = KV_OFF + DEC_STAGES * 2 * KV_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 1024 + 1024;
 };
 
+// Pipeline: the MMA warp issues S(j+1) before it waits for P(j), so the score MMA of the next page runs while the
+// softmax warps work on the current one, and the P*V MMA of page j runs while they work on page j+1. S and P are
+// double-buffered (TMEM columns [0,16) / [16,32), shared-memory P buffers 0 / 1). The running output O (TMEM
+// columns [32,48)) is rescaled only when a head's maximum grew by more than 2^8 since the reference maximum was
+// last moved, which needs the previous P*V to have finished (pv_done); otherwise nothing waits on the tensor pipe.
 __global__ void __launch_bounds__(192, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const DecodeParams p) {
@@ -45,11 +50,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   uint64_t* kv_full = bars;                    // [STAGES]
   uint64_t* kv_empty = bars + DEC_STAGES;      // [STAGES]
   uint64_t* q_full = bars + 2 * DEC_STAGES;
-  uint64_t* s_full = q_full + 1;
-  uint64_t* p_full = q_full + 2;
-  uint64_t* o_full = q_full + 3;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 4);
-  float* red = reinterpret_cast<float*>(q_full + 6);  // [2][4][16] floats: per-warp partial max / sum
+  uint64_t* s_full = q_full + 1;               // [2]
+  uint64_t* p_full = q_full + 3;               // [2]
+  uint64_t* pv_done = q_full + 5;
+  uint64_t* o_full = q_full + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 7);
+  float* red = reinterpret_cast<float*>(q_full + 8);  // [2][4][16] floats: per-warp partial max (two parities)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -68,11 +74,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+    }
+    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     mbar_fence_init();
   }
+  // both P buffers start as zeros: rows of heads beyond G are never written and must stay finite
+  for (int i = threadIdx.x; i < 8192 / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(smem + DecSmem::P_OFF)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
   if (warp == 1) {
     tmem_alloc(tmem_slot, 64);
     tmem_relinquish();
@@ -81,10 +94,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;        // 16 columns
+  const uint32_t tmem_s = tmem_base;        // 2 x 16 columns
   const uint32_t tmem_o = tmem_base + 32;   // 16 columns
-  pdl_wait();
-  pdl_launch_dependents();
 
   if (n_tiles > 0) {
     if (warp == 0) {
@@ -115,35 +126,42 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         constexpr uint32_t idesc_s = make_idesc_bf16(128, NPAD, false, false);
         constexpr uint32_t idesc_o = make_idesc_bf16(128, NPAD, true, false);
         const uint32_t sq = smem_u32(smem + DecSmem::Q_OFF);
-        const uint32_t sp = smem_u32(smem + DecSmem::P_OFF);
+        const uint32_t kv_base = smem_u32(smem + DecSmem::KV_OFF);
         bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_FULL);
-        int stage = 0;
-        uint32_t phase = 0;
-        for (int i = 0; i < n_tiles && ok; ++i) {
-          if (!mbar_wait(&kv_full[stage], phase, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
+        // S^T(j) = K(j) * Q^T into S buffer j&1 : K-steps over hd (8 x 16); panel = k/4, 32 B per step in a panel
+        auto issue_s = [&](int j) -> bool {
+          const int stage = j % DEC_STAGES;
+          const uint32_t phase = (j / DEC_STAGES) & 1;
+          if (!mbar_wait(&kv_full[stage], phase, p.status, ERR_TIMEOUT_FULL)) return false;
           tc_fence_after();
-          const uint32_t sk = smem_u32(smem + DecSmem::KV_OFF + stage * 2 * KV_TILE_BYTES);
-          const uint32_t sv = sk + KV_TILE_BYTES;
-          // S^T = K * Q^T : K-steps over hd (8 x 16); panel = k/4, 32 B per step inside a panel
+          const uint32_t sk = kv_base + stage * 2 * KV_TILE_BYTES;
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
             const uint64_t ad = make_smem_desc_sw128(sk + (k >> 2) * (PAGE * 128) + (k & 3) * 32, 16, 1024);
             const uint64_t bd = make_smem_desc_sw128(sq + (k >> 2) * (NPAD * 128) + (k & 3) * 32, 16, 1024);
-            umma_bf16(tmem_s, ad, bd, idesc_s, k > 0 ? 1u : 0u);
+            umma_bf16(tmem_s + (j & 1) * NPAD, ad, bd, idesc_s, k > 0 ? 1u : 0u);
           }
-          umma_commit(s_full);
-          if (!mbar_wait(p_full, i & 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          umma_commit(&s_full[j & 1]);
+          return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+          if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after();
+          const int stage = j % DEC_STAGES;
+          const uint32_t sv = kv_base + stage * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
+          const uint32_t sp = smem_u32(smem + DecSmem::P_OFF + (j & 1) * 4096);
           // O^T += V^T * P^T : K-steps over kv (8 x 16 rows of 128 B); M chunks of 64 dims are 16 KB apart
 #pragma unroll
           for (int k = 0; k < PAGE / 16; ++k) {
             const uint64_t ad = make_smem_desc_sw128(sv + k * (16 * 128), PAGE * 128, 1024);
             const uint64_t bd = make_smem_desc_sw128(sp + (k >> 2) * (NPAD * 128) + (k & 3) * 32, 16, 1024);
-            umma_bf16(tmem_o, ad, bd, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_o, ad, bd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&kv_empty[stage]);
-          if (i == n_tiles - 1) umma_commit(o_full);
-          if (++stage == DEC_STAGES) { stage = 0; phase ^= 1; }
+          umma_commit(pv_done);
+          if (j == n_tiles - 1) umma_commit(o_full);
         }
       }
     } else {
@@ -151,92 +169,112 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;  // kv token inside the tile (S^T) and head-dim index (O^T)
       const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-      float m_run[NPAD], l_run[NPAD];
+      float m_ref[NPAD], l_part[NPAD];      // reference maximum (log2 domain) and this thread's share of the row sum
 #pragma unroll
-      for (int h = 0; h < NPAD; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
+      for (int h = 0; h < NPAD; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
       bool ok = true;
       for (int i = 0; i < n_tiles && ok; ++i) {
-        if (!mbar_wait(s_full, i & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (!mbar_wait(&s_full[i & 1], (i >> 1) & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
         uint32_t sr[NPAD];
-        tmem_ld_32x32b_x16(tmem_s + lane_addr, sr);
+        tmem_ld_32x32b_x16(tmem_s + (i & 1) * NPAD + lane_addr, sr);
         tmem_ld_wait();
         const bool valid = (tile0 + i) * PAGE + row < len;
-        float s[NPAD], tmax[NPAD];
+        float s[NPAD];
+        float* redp = red + (i & 1) * 64;
 #pragma unroll
         for (int h = 0; h < NPAD; ++h) {
-          s[h] = valid ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
-          tmax[h] = warp_max(s[h]);
-        }
-        if (lane == 0) {
-#pragma unroll
-          for (int h = 0; h < NPAD; ++h) red[quarter * NPAD + h] = tmax[h];
+          if (h < G) {
+            s[h] = valid ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
+            const float tm = warp_max(s[h]);
+            if (lane == 0) redp[quarter * NPAD + h] = tm;
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        float alpha[NPAD], pv[NPAD], psum[NPAD];
+        // every thread sees the same tile maxima, so the decision to move the reference maximum is block-uniform
+        float alpha[NPAD];
+        bool move = false;
 #pragma unroll
         for (int h = 0; h < NPAD; ++h) {
-          const float mt = fmaxf(fmaxf(red[h], red[NPAD + h]), fmaxf(red[2 * NPAD + h], red[3 * NPAD + h]));
-          const float mn = fmaxf(m_run[h], mt);
-          alpha[h] = exp2f(m_run[h] - mn);
-          m_run[h] = mn;
-          pv[h] = exp2f(s[h] - mn);
-          psum[h] = warp_sum(pv[h]);
+          alpha[h] = 1.f;
+          if (h < G) {
+            const float mt = fmaxf(fmaxf(redp[h], redp[NPAD + h]), fmaxf(redp[2 * NPAD + h], redp[3 * NPAD + h]));
+            if (mt > m_ref[h] + 8.f || m_ref[h] == -INFINITY) {
+              const float mn = fmaxf(mt, m_ref[h]);
+              alpha[h] = exp2f(m_ref[h] - mn);      // 0 on the first tile
+              m_ref[h] = mn;
+              move = true;
+            }
+          }
         }
-        if (lane == 0) {
+        if (move) {
 #pragma unroll
-          for (int h = 0; h < NPAD; ++h) red[64 + quarter * NPAD + h] = psum[h];
-        }
-        // rescale the running output (rows = head dims of this thread, columns = heads)
-        if (i > 0) {
-          uint32_t orr[NPAD];
-          tmem_ld_32x32b_x16(tmem_o + lane_addr, orr);
-          tmem_ld_wait();
+          for (int h = 0; h < NPAD; ++h) l_part[h] *= alpha[h];
+          if (i > 0) {
+            // the running output is being accumulated by P*V(i-1): wait for it, then rescale columns (= heads)
+            if (!mbar_wait(pv_done, (i - 1) & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t orr[NPAD];
+            tmem_ld_32x32b_x16(tmem_o + lane_addr, orr);
+            tmem_ld_wait();
 #pragma unroll
-          for (int h = 0; h < NPAD; ++h) orr[h] = __float_as_uint(__uint_as_float(orr[h]) * alpha[h]);
-          tmem_st_32x32b_x8(tmem_o + lane_addr, orr);
-          tmem_st_32x32b_x8(tmem_o + lane_addr + 8, orr + 8);
-          tmem_st_wait();
+            for (int h = 0; h < NPAD; ++h) orr[h] = __float_as_uint(__uint_as_float(orr[h]) * alpha[h]);
+            tmem_st_32x32b_x8(tmem_o + lane_addr, orr);
+            tmem_st_32x32b_x8(tmem_o + lane_addr + 8, orr + 8);
+            tmem_st_wait();
+          }
         }
         // P^T[h][token] as the K-major B operand: panel = token/64, row h of 128 B, 16-byte chunks swizzled by (h & 7)
         {
-          uint8_t* pbase = smem + DecSmem::P_OFF + (row >> 6) * (NPAD * 128);
+          uint8_t* pbase = smem + DecSmem::P_OFF + (i & 1) * 4096 + (row >> 6) * (NPAD * 128);
           const int tk = row & 63;
 #pragma unroll
           for (int h = 0; h < NPAD; ++h) {
-            const int off = h * 128 + ((((tk >> 3) ^ (h & 7)) << 4) | ((tk & 7) << 1));
-            *reinterpret_cast<__nv_bfloat16*>(pbase + off) = __float2bfloat16_rn(pv[h]);
+            if (h < G) {
+              const float pv = exp2f(s[h] - m_ref[h]);
+              l_part[h] += pv;
+              const int off = h * 128 + ((((tk >> 3) ^ (h & 7)) << 4) | ((tk & 7) << 1));
+              *reinterpret_cast<__nv_bfloat16*>(pbase + off) = __float2bfloat16_rn(pv);
+            }
           }
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-        for (int h = 0; h < NPAD; ++h)
-          l_run[h] = l_run[h] * alpha[h] + red[64 + h] + red[64 + NPAD + h] + red[64 + 2 * NPAD + h] + red[64 + 3 * NPAD + h];
-        if (lane == 0) mbar_arrive(p_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[i & 1]);
       }
       if (ok && mbar_wait(o_full, 0, p.status, ERR_TIMEOUT_TMEM_FULL)) {
         tc_fence_after();
+        // row sums: one block-wide reduction at the end instead of one per tile
+        float* lred = red;   // reuse: [4][16]
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int h = 0; h < NPAD; ++h) {
+          if (h < G) {
+            const float t = warp_sum(l_part[h]);
+            if (lane == 0) lred[quarter * NPAD + h] = t;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         uint32_t orr[NPAD];
         tmem_ld_32x32b_x16(tmem_o + lane_addr, orr);
         tmem_ld_wait();
-        if (p.splits == 1) {
 #pragma unroll
-          for (int h = 0; h < NPAD; ++h)
-            if (h < G)
-              p.out[((size_t)b * p.Hq + kvh * G + h) * HD + row] = __float2bfloat16_rn(__uint_as_float(orr[h]) / l_run[h]);
-        } else {
-#pragma unroll
-          for (int h = 0; h < NPAD; ++h)
-            if (h < G) {
+        for (int h = 0; h < NPAD; ++h) {
+          if (h < G) {
+            const float l = lred[h] + lred[NPAD + h] + lred[2 * NPAD + h] + lred[3 * NPAD + h];
+            const float o = __uint_as_float(orr[h]) / l;
+            if (p.splits == 1) {
+              p.out[((size_t)b * p.Hq + kvh * G + h) * HD + row] = __float2bfloat16_rn(o);
+            } else {
               const size_t idx = ((size_t)b * p.Hq + kvh * G + h) * p.splits + split;
-              p.part_o[idx * HD + row] = __uint_as_float(orr[h]) / l_run[h];
+              p.part_o[idx * HD + row] = o;
               if (row == 0) {
-                p.part_ml[idx * 2] = m_run[h];
-                p.part_ml[idx * 2 + 1] = l_run[h];
+                p.part_ml[idx * 2] = m_ref[h];
+                p.part_ml[idx * 2 + 1] = l;
               }
             }
+          }
         }
       }
     }
@@ -254,6 +292,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   }
 
   __syncwarp();
+  // this grid can be larger than one wave: successors are released only now, so that their CTAs do not take SMs
+  // away from the CTAs of this grid that have not started yet
+  pdl_launch_dependents();
   if (p.status != nullptr && *(volatile int*)p.status != 0) {
     uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
