@@ -23,7 +23,33 @@ def _peaks():
         return 6650.0, 1590.0, "of fallback"
 
 
-def _time(fn, iters: int, flush: bool = True) -> float:
+FLUSH = True
+GRAPH = 0
+
+
+def _time(fn, iters: int, flush: bool | None = None) -> float:
+    flush = FLUSH if flush is None else flush
+    if GRAPH > 0:
+        # back-to-back launches inside one CUDA graph: per-launch device time without host launch latency and with
+        # warm instruction / descriptor caches (the situation inside the captured decode loop)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(GRAPH):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) * 1e-3 / GRAPH
     scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(3):
         fn()
@@ -55,7 +81,12 @@ def main():
     ap.add_argument("--hkv", type=int, default=2)
     ap.add_argument("--splits", type=int, default=1)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--graph", type=int, default=0, help="time N back-to-back launches inside one CUDA graph")
+    ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed launches")
     a = ap.parse_args()
+    global FLUSH, GRAPH
+    FLUSH = not a.no_flush
+    GRAPH = a.graph
     from openrlhf_b200.ops import _lib
     from openrlhf_b200.ops import functional as F
     from openrlhf_b200.ops.attention import attn_fwd_tcgen05, paged_decode

@@ -5,7 +5,7 @@
 //     S^T[kv,16]  = K_page[kv,hd] * Q^T[hd,16]        (A = K, K-major;   B = Q, K-major)
 //     O^T[hd,16] += V_page^T[hd,kv] * P^T[kv,16]      (A = V, MN-major;  B = P, K-major)
 // so no tensor-core work is spent on padding rows, each softmax thread owns one kv token (16 values), and the kernel
-// is bound by the KV bytes streamed through a 3-stage TMA ring. Takes the place of vLLM's paged decode attention in
+// is bound by the KV bytes it streams; two CTAs are resident per SM so that one CTA's loads overlap the other's math. Takes the place of vLLM's paged decode attention in
 // the reference's rollout path (openrlhf/trainer/ray/vllm_engine.py:155-179 drives vLLM's engine).
 #include "ptx.cuh"
 
@@ -14,7 +14,7 @@ namespace b200 {
 constexpr int PAGE = 128;   // tokens per KV page == kv tile
 constexpr int HD = 128;     // head dim
 constexpr int NPAD = 16;    // query heads per kv head, padded
-constexpr int DEC_STAGES = 3;
+constexpr int DEC_STAGES = 1;   // one K and one V buffer per CTA; two CTAs share an SM and interleave their loads
 constexpr int KV_TILE_BYTES = PAGE * HD * 2;  // 32 KB for K, same for V
 
 struct DecodeParams {
@@ -31,8 +31,9 @@ struct DecodeParams {
 struct DecSmem {
   static constexpr int Q_OFF = 0;                         // 2 panels x 16 rows x 128 B
   static constexpr int P_OFF = 4096;                      // 2 buffers x (2 panels x 16 rows x 128 B)
-  static constexpr int KV_OFF = 12288;                    // stages x (K 32 KB + V 32 KB)
-  static constexpr int BAR_OFF = KV_OFF + DEC_STAGES * 2 * KV_TILE_BYTES;
+  static constexpr int K_OFF = 12288;                     // K page, 32 KB
+  static constexpr int V_OFF = K_OFF + KV_TILE_BYTES;     // V page, 32 KB
+  static constexpr int BAR_OFF = V_OFF + KV_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 1024 + 1024;
 };
 
@@ -41,15 +42,17 @@ struct DecSmem {
 // double-buffered (TMEM columns [0,16) / [16,32), shared-memory P buffers 0 / 1). The running output O (TMEM
 // columns [32,48)) is rescaled only when a head's maximum grew by more than 2^8 since the reference maximum was
 // last moved, which needs the previous P*V to have finished (pv_done); otherwise nothing waits on the tensor pipe.
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DecSmem::BAR_OFF);
-  uint64_t* kv_full = bars;                    // [STAGES]
-  uint64_t* kv_empty = bars + DEC_STAGES;      // [STAGES]
-  uint64_t* q_full = bars + 2 * DEC_STAGES;
+  uint64_t* k_full = bars;        // K and V have their own full / empty pairs: the next K page is fetched while the
+  uint64_t* k_empty = bars + 1;   // softmax and the P*V product of the current page are still running
+  uint64_t* v_full = bars + 2;
+  uint64_t* v_empty = bars + 3;
+  uint64_t* q_full = bars + 4;
   uint64_t* s_full = q_full + 1;               // [2]
   uint64_t* p_full = q_full + 3;               // [2]
   uint64_t* pv_done = q_full + 5;
@@ -69,10 +72,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int n_tiles = max(tile1 - tile0, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
-    }
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -106,19 +109,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         mbar_expect_tx(q_full, 2 * NPAD * 128);
         tma_load_2d(smem + DecSmem::Q_OFF, &tma_q, q_full, 0, b * p.Hq + kvh * G);
         tma_load_2d(smem + DecSmem::Q_OFF + NPAD * 128, &tma_q, q_full, 64, b * p.Hq + kvh * G);
-        int stage = 0;
+        uint8_t* sk = smem + DecSmem::K_OFF;
+        uint8_t* sv = smem + DecSmem::V_OFF;
         uint32_t phase = 0;
-        for (int t = tile0; t < tile1; ++t) {
-          if (!mbar_wait(&kv_empty[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+        for (int t = tile0; t < tile1; ++t, phase ^= 1) {
           const int page = p.block_table[(size_t)b * p.max_pages + t];
-          uint8_t* sk = smem + DecSmem::KV_OFF + stage * 2 * KV_TILE_BYTES;
-          uint8_t* sv = sk + KV_TILE_BYTES;
-          mbar_expect_tx(&kv_full[stage], 2 * KV_TILE_BYTES);
-          tma_load_2d(sk, &tma_k, &kv_full[stage], kvh * HD, page * PAGE);
-          tma_load_2d(sk + PAGE * 128, &tma_k, &kv_full[stage], kvh * HD + 64, page * PAGE);
-          tma_load_2d(sv, &tma_v, &kv_full[stage], kvh * HD, page * PAGE);
-          tma_load_2d(sv + PAGE * 128, &tma_v, &kv_full[stage], kvh * HD + 64, page * PAGE);
-          if (++stage == DEC_STAGES) { stage = 0; phase ^= 1; }
+          if (!mbar_wait(k_empty, phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(k_full, KV_TILE_BYTES);
+          tma_load_2d(sk, &tma_k, k_full, kvh * HD, page * PAGE);
+          tma_load_2d(sk + PAGE * 128, &tma_k, k_full, kvh * HD + 64, page * PAGE);
+          if (!mbar_wait(v_empty, phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(v_full, KV_TILE_BYTES);
+          tma_load_2d(sv, &tma_v, v_full, kvh * HD, page * PAGE);
+          tma_load_2d(sv + PAGE * 128, &tma_v, v_full, kvh * HD + 64, page * PAGE);
         }
       }
     } else if (warp == 1) {
@@ -126,15 +129,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         constexpr uint32_t idesc_s = make_idesc_bf16(128, NPAD, false, false);
         constexpr uint32_t idesc_o = make_idesc_bf16(128, NPAD, true, false);
         const uint32_t sq = smem_u32(smem + DecSmem::Q_OFF);
-        const uint32_t kv_base = smem_u32(smem + DecSmem::KV_OFF);
+        const uint32_t sk = smem_u32(smem + DecSmem::K_OFF);
+        const uint32_t sv = smem_u32(smem + DecSmem::V_OFF);
         bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_FULL);
         // S^T(j) = K(j) * Q^T into S buffer j&1 : K-steps over hd (8 x 16); panel = k/4, 32 B per step in a panel
         auto issue_s = [&](int j) -> bool {
-          const int stage = j % DEC_STAGES;
-          const uint32_t phase = (j / DEC_STAGES) & 1;
-          if (!mbar_wait(&kv_full[stage], phase, p.status, ERR_TIMEOUT_FULL)) return false;
+          if (!mbar_wait(k_full, j & 1, p.status, ERR_TIMEOUT_FULL)) return false;
           tc_fence_after();
-          const uint32_t sk = kv_base + stage * 2 * KV_TILE_BYTES;
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
             const uint64_t ad = make_smem_desc_sw128(sk + (k >> 2) * (PAGE * 128) + (k & 3) * 32, 16, 1024);
@@ -142,15 +143,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             umma_bf16(tmem_s + (j & 1) * NPAD, ad, bd, idesc_s, k > 0 ? 1u : 0u);
           }
           umma_commit(&s_full[j & 1]);
+          umma_commit(k_empty);          // the K buffer may be refilled as soon as these MMAs have read it
           return true;
         };
         if (ok) ok = issue_s(0);
         for (int j = 0; j < n_tiles && ok; ++j) {
           if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
           if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          if (!mbar_wait(v_full, j & 1, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const int stage = j % DEC_STAGES;
-          const uint32_t sv = kv_base + stage * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
           const uint32_t sp = smem_u32(smem + DecSmem::P_OFF + (j & 1) * 4096);
           // O^T += V^T * P^T : K-steps over kv (8 x 16 rows of 128 B); M chunks of 64 dims are 16 KB apart
 #pragma unroll
@@ -159,7 +160,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             const uint64_t bd = make_smem_desc_sw128(sp + (k >> 2) * (NPAD * 128) + (k & 3) * 32, 16, 1024);
             umma_bf16(tmem_o, ad, bd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&kv_empty[stage]);
+          umma_commit(v_empty);
           umma_commit(pv_done);
           if (j == n_tiles - 1) umma_commit(o_full);
         }
