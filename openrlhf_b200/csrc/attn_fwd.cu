@@ -1,24 +1,27 @@
 // Causal attention forward over a packed (varlen) token stream on tcgen05: used for training / log-prob forwards and
-// for rollout prefill. GQA, head_dim 128, one CTA per (128-row query tile of one sequence, query head).
+// for rollout prefill. GQA, head_dim 128.
 //
-//   S[128q,128kv] = Q K^T     (A = Q tile,  K-major;  B = K tile, K-major)   accumulator in TMEM columns [0,128)
-//   O[128q,128d] += P V       (A = P (smem), K-major; B = V tile, MN-major)  accumulator in TMEM columns [128,256)
+// One CTA works on TWO query streams that share the same K/V tiles, so that the tensor core runs one stream's MMAs
+// while the other stream's softmax is in flight:
+//   * pair_heads = 1 (even GQA group): heads 2x and 2x+1 of one kv-head on the same 128 query rows;
+//   * pair_heads = 0: one head on the query rows q0..q0+127 and q0+128..q0+255 of one sequence.
 //
-// warp 0: TMA producer (Q once, then K/V tiles through a 2-stage ring); warp 1: MMA issuer; warps 2-5: softmax, one
-// query row per thread, online max/sum in the log2 domain with a lazily updated reference maximum (O is rescaled in
-// TMEM only when the running maximum grew by more than 2^8), P written back to shared memory in the 128-byte-swizzled
-// K-major layout the second MMA reads. Outputs: O (bf16) and the log-sum-exp per (head, token) for the backward pass.
+//   S_s[128q,128kv] = Q_s K^T   (A = Q tile, smem K-major; B = K tile, smem K-major)  TMEM columns [128 s, 128 s + 128)
+//   P_s (bf16) overwrites columns [128 s, 128 s + 64) of its own S tile (two values per 32-bit column)
+//   O_s[128q,128d] += P_s V     (A = P in TMEM; B = V tile, smem MN-major)            TMEM columns [256 + 128 s, +128)
+//
+// warp 0: TMA producer (Q tiles once, K and V through separate 2-stage rings); warp 1: MMA issuer, order
+// PV_0(j), S_0(j+1), PV_1(j), S_1(j+1); warps 2-5 / 6-9: softmax of stream 0 / 1, one query row per thread, online
+// softmax in the log2 domain with a lazily moved reference maximum (O is rescaled in TMEM only when the running
+// maximum grew by more than 2^8). Outputs: O (bf16) and the log-sum-exp per (head, token) for the backward pass.
 // Takes the place of flash-attn 2's varlen forward that the reference reaches through HF Transformers
 // (openrlhf/models/actor.py:152 sets attn_implementation="flash_attention_2").
 #include "ptx.cuh"
 
 namespace b200 {
 
-constexpr int AT_BM = 128;   // query rows per tile
-constexpr int AT_BN = 128;   // kv rows per tile
 constexpr int AT_HD = 128;
-constexpr int AT_STAGES = 2;
-constexpr int AT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: Q, K, V and P tiles all have this size
+constexpr int AT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: Q, K and V tiles all have this size
 
 struct AttnFwdParams {
   const int* cu_seqlens;   // [B+1]
@@ -28,85 +31,102 @@ struct AttnFwdParams {
   float* lse;              // [Hq, T] natural-log LSE
   int n_seqs, T, Hq, Hkv, ldo;
   int q_col0, k_col0, v_col0;   // column of head 0 inside the q / k / v matrices the tensor maps describe
+  int n_tiles, pair_heads;
   float scale_log2;
   int* status;
 };
 
 struct AtSmem {
-  static constexpr int Q_OFF = 0;
-  static constexpr int P_OFF = AT_TILE_BYTES;
-  static constexpr int KV_OFF = 2 * AT_TILE_BYTES;
-  static constexpr int BAR_OFF = KV_OFF + AT_STAGES * 2 * AT_TILE_BYTES;
+  static constexpr int Q_OFF = 0;                          // 2 query tiles
+  static constexpr int K_OFF = 2 * AT_TILE_BYTES;          // 2 stages
+  static constexpr int V_OFF = 4 * AT_TILE_BYTES;          // 2 stages
+  static constexpr int BAR_OFF = 6 * AT_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                 const __grid_constant__ CUtensorMap tma_v, const AttnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AtSmem::BAR_OFF);
-  uint64_t* kv_full = bars;
-  uint64_t* kv_empty = bars + AT_STAGES;
-  uint64_t* q_full = bars + 2 * AT_STAGES;
-  uint64_t* s_full = q_full + 1;
-  uint64_t* p_full = q_full + 2;
-  uint64_t* o_full = q_full + 3;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 4);
+  uint64_t* k_full = bars;          // [2]
+  uint64_t* k_empty = bars + 2;     // [2]
+  uint64_t* v_full = bars + 4;      // [2]
+  uint64_t* v_empty = bars + 6;     // [2]
+  uint64_t* q_full = bars + 8;
+  uint64_t* s_full = bars + 9;      // [2] per stream
+  uint64_t* p_full = bars + 11;     // [2] per stream
+  uint64_t* o_full = bars + 13;     // [2] per stream
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = p.tile_seq[blockIdx.x];
-  if (seq < 0 || seq >= p.n_seqs) return;          // padding tile: whole CTA leaves before touching TMEM
-  const int head = blockIdx.y;
-  const int kvh = head / (p.Hq / p.Hkv);
+  const int t = p.n_tiles - 1 - (int)blockIdx.y;    // later (longer) tiles of a sequence start first
+  const int seq = p.tile_seq[t];
+  if (seq < 0 || seq >= p.n_seqs) return;           // padding tile: whole CTA leaves before touching TMEM
   const int row_base = p.cu_seqlens[seq];
   const int len = p.cu_seqlens[seq + 1] - row_base;
-  const int q0 = p.tile_q0[blockIdx.x];
-  const int kv_end = min(len, q0 + AT_BM);          // causal: keys up to the last query row of the tile
-  const int n_tiles = (kv_end + AT_BN - 1) / AT_BN;
+  const int tq0 = p.tile_q0[t];
+  const int head0 = p.pair_heads ? 2 * (int)blockIdx.x : (int)blockIdx.x;
+  const int head1 = p.pair_heads ? head0 + 1 : head0;
+  const int q0_0 = tq0, q0_1 = p.pair_heads ? tq0 : tq0 + 128;
+  const int kvh = head0 / (p.Hq / p.Hkv);
+  // causal: keys up to the last query row of the stream's tile
+  const int nt0 = q0_0 < len ? (min(len, q0_0 + 128) + 127) / 128 : 0;
+  const int nt1 = q0_1 < len ? (min(len, q0_1 + 128) + 127) / 128 : 0;
+  const int n = max(nt0, nt1);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < AT_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&o_full[s], 1);
     }
     mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tma_q);
       tma_prefetch_desc(&tma_k);
       tma_prefetch_desc(&tma_v);
-      mbar_expect_tx(q_full, AT_TILE_BYTES);
-      tma_load_2d(smem + AtSmem::Q_OFF, &tma_q, q_full, p.q_col0 + head * AT_HD, row_base + q0);
-      tma_load_2d(smem + AtSmem::Q_OFF + 16384, &tma_q, q_full, p.q_col0 + head * AT_HD + 64, row_base + q0);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
-        uint8_t* sk = smem + AtSmem::KV_OFF + stage * 2 * AT_TILE_BYTES;
-        uint8_t* sv = sk + AT_TILE_BYTES;
-        const int r = row_base + j * AT_BN;
-        mbar_expect_tx(&kv_full[stage], 2 * AT_TILE_BYTES);
-        tma_load_2d(sk, &tma_k, &kv_full[stage], p.k_col0 + kvh * AT_HD, r);
-        tma_load_2d(sk + 16384, &tma_k, &kv_full[stage], p.k_col0 + kvh * AT_HD + 64, r);
-        tma_load_2d(sv, &tma_v, &kv_full[stage], p.v_col0 + kvh * AT_HD, r);
-        tma_load_2d(sv + 16384, &tma_v, &kv_full[stage], p.v_col0 + kvh * AT_HD + 64, r);
-        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      mbar_expect_tx(q_full, ((nt0 > 0) + (nt1 > 0)) * AT_TILE_BYTES);
+      if (nt0 > 0) {
+        tma_load_2d(smem + AtSmem::Q_OFF, &tma_q, q_full, p.q_col0 + head0 * AT_HD, row_base + q0_0);
+        tma_load_2d(smem + AtSmem::Q_OFF + 16384, &tma_q, q_full, p.q_col0 + head0 * AT_HD + 64, row_base + q0_0);
+      }
+      if (nt1 > 0) {
+        uint8_t* sq1 = smem + AtSmem::Q_OFF + AT_TILE_BYTES;
+        tma_load_2d(sq1, &tma_q, q_full, p.q_col0 + head1 * AT_HD, row_base + q0_1);
+        tma_load_2d(sq1 + 16384, &tma_q, q_full, p.q_col0 + head1 * AT_HD + 64, row_base + q0_1);
+      }
+      for (int j = 0; j < n; ++j) {
+        const int stage = j & 1;
+        const uint32_t phase = (j >> 1) & 1;
+        const int r = row_base + j * 128;
+        uint8_t* sk = smem + AtSmem::K_OFF + stage * AT_TILE_BYTES;
+        uint8_t* sv = smem + AtSmem::V_OFF + stage * AT_TILE_BYTES;
+        if (!mbar_wait(&k_empty[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&k_full[stage], AT_TILE_BYTES);
+        tma_load_2d(sk, &tma_k, &k_full[stage], p.k_col0 + kvh * AT_HD, r);
+        tma_load_2d(sk + 16384, &tma_k, &k_full[stage], p.k_col0 + kvh * AT_HD + 64, r);
+        if (!mbar_wait(&v_empty[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&v_full[stage], AT_TILE_BYTES);
+        tma_load_2d(sv, &tma_v, &v_full[stage], p.v_col0 + kvh * AT_HD, r);
+        tma_load_2d(sv + 16384, &tma_v, &v_full[stage], p.v_col0 + kvh * AT_HD + 64, r);
       }
     }
   } else if (warp == 1) {
@@ -114,138 +134,150 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, false, true);
       const uint32_t sq = smem_u32(smem + AtSmem::Q_OFF);
-      const uint32_t sp = smem_u32(smem + AtSmem::P_OFF);
+      const uint32_t sk0 = smem_u32(smem + AtSmem::K_OFF);
+      const uint32_t sv0 = smem_u32(smem + AtSmem::V_OFF);
       bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_FULL);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait(&kv_full[stage], phase, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + AtSmem::KV_OFF + stage * 2 * AT_TILE_BYTES);
-        const uint32_t sv = sk + AT_TILE_BYTES;
+      auto issue_s = [&](int s, int j) {
+        const uint32_t sk = sk0 + (j & 1) * AT_TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k) {
-          const uint64_t ad = make_smem_desc_sw128(sq + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t ad = make_smem_desc_sw128(sq + s * AT_TILE_BYTES + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sk + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          umma_bf16(tmem_s, ad, bd, idesc_s, k > 0 ? 1u : 0u);
+          umma_bf16(tmem_base + s * 128, ad, bd, idesc_s, k > 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        if (!mbar_wait(p_full, j & 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        umma_commit(&s_full[s]);
+      };
+      auto issue_pv = [&](int s, int j) -> bool {
+        if (!mbar_wait(&p_full[s], j & 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) return false;
         tc_fence_after();
+        const uint32_t sv = sv0 + (j & 1) * AT_TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < AT_BN / 16; ++k) {
-          const uint64_t ad = make_smem_desc_sw128(sp + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+        for (int k = 0; k < 128 / 16; ++k) {
           const uint64_t bd = make_smem_desc_sw128(sv + k * 2048, 16384, 1024);
-          umma_bf16(tmem_o, ad, bd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_base + 256 + s * 128, tmem_base + s * 128 + k * 8, bd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[stage]);
-        if (j == n_tiles - 1) umma_commit(o_full);
-        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+        return true;
+      };
+      if (ok && n > 0) ok = mbar_wait(&k_full[0], 0, p.status, ERR_TIMEOUT_FULL);
+      if (ok && n > 0) {
+        tc_fence_after();
+        if (nt0 > 0) issue_s(0, 0);
+        if (nt1 > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (j < nt0) {
+          if (!issue_pv(0, j)) { ok = false; break; }
+          if (j == nt0 - 1) umma_commit(&o_full[0]);
+        }
+        if (j + 1 < n) {
+          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+        }
+        if (j + 1 < nt0) issue_s(0, j + 1);
+        if (j < nt1) {
+          if (!issue_pv(1, j)) { ok = false; break; }
+          if (j == nt1 - 1) umma_commit(&o_full[1]);
+        }
+        umma_commit(&v_empty[j & 1]);
+        if (j + 1 < nt1) issue_s(1, j + 1);
+        if (j + 1 < n) umma_commit(&k_empty[(j + 1) & 1]);
       }
     }
   } else {
-    const int quarter = warp & 3;
+    // ---------------------------------------------------------------- softmax of stream s, one query row per thread
+    const int s = (warp - 2) >> 2;
+    const int quarter = warp & 3;                   // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;              // query row inside the tile
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    const int q_pos = q0 + r;
+    const int nts = s ? nt1 : nt0;
+    const int q0s = s ? q0_1 : q0_0;
+    const int head = s ? head1 : head0;
+    const int q_pos = q0s + r;
+    const uint32_t tm_s = tmem_base + s * 128 + lane_addr;
+    const uint32_t tm_o = tmem_base + 256 + s * 128 + lane_addr;
     float m_ref = -INFINITY;                        // reference maximum used in the exponent (log2 domain)
     float l_run = 0.f;
-    uint8_t* prow = smem + AtSmem::P_OFF + r * 128;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(s_full, j & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+    for (int j = 0; j < nts && ok; ++j) {
+      // S(j) complete also means PV(j-1) of this stream is complete: MMAs finish in issue order
+      if (!mbar_wait(&s_full[s], j & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int kv0 = j * AT_BN;
-      const bool need_mask = (kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > len);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool valid = !need_mask || (kv <= q_pos && kv < len);
-          if (valid) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
+      uint32_t v[128];
+      tmem_ld_32x32b_x32(tm_s, v);
+      tmem_ld_32x32b_x32(tm_s + 32, v + 32);
+      tmem_ld_32x32b_x32(tm_s + 64, v + 64);
+      tmem_ld_32x32b_x32(tm_s + 96, v + 96);
+      tmem_ld_wait();
+      const int kv0 = j * 128;
+      if (kv0 + 127 > q0s) {                        // diagonal tile: causal mask (keys past the sequence end are
+#pragma unroll                                      // above every valid row's diagonal, so this covers them too)
+        for (int i = 0; i < 128; ++i)
+          if (kv0 + i > q_pos) v[i] = 0xff800000u;
       }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
       mx *= p.scale_log2;
-      // lazily move the reference maximum: only when it grew by more than 8 (factor 256), warp-uniform decision
-      float m_new = m_ref;
+      // lazily move the reference maximum: only when it grew by more than 8 (factor 256)
       const bool grow = mx > m_ref + 8.f || m_ref == -INFINITY;
-      if (grow) m_new = fmaxf(mx, m_ref);
-      const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);   // m_ref=-inf -> 0
-      if (__any_sync(0xffffffffu, grow) && j > 0) {
+      const float m_new = grow ? fmaxf(mx, m_ref) : m_ref;
+      const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);   // m_ref = -inf -> 0
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tm_o + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) tmem_st_32x32b_x8(tmem_o + lane_addr + c * 32 + i, v + i);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x16(tm_o + c * 32, o);
+          tmem_st_32x32b_x16(tm_o + c * 32 + 16, o + 16);
         }
-        tmem_st_wait();
       }
       l_run *= alpha;
       m_ref = m_new;
-      // pass 2: p = 2^(s*scale - m_ref), row sum, bf16 P tile into swizzled shared memory
+      // p = 2^(s*scale - m_ref); bf16 pairs go back into the first 64 columns of this stream's S tile
       float lsum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        float pv[32];
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool valid = !need_mask || (kv <= q_pos && kv < len);
-          const float e = valid ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_ref) : 0.f;
-          pv[i] = e;
-          lsum += e;
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = exp2f(fmaf(__uint_as_float(v[c * 32 + 2 * i]), p.scale_log2, -m_ref));
+          const float e1 = exp2f(fmaf(__uint_as_float(v[c * 32 + 2 * i + 1]), p.scale_log2, -m_ref));
+          lsum += e0 + e1;
+          pk[i] = pack_bf16x2(e0, e1);
         }
-        // columns c*32 .. c*32+31 -> panel (c >> 1), 16-byte chunks (c & 1) * 4 + q, swizzled by (r & 7)
-        uint8_t* pp = prow + (c >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 o;
-          o.x = pack_bf16x2(pv[q * 8 + 0], pv[q * 8 + 1]);
-          o.y = pack_bf16x2(pv[q * 8 + 2], pv[q * 8 + 3]);
-          o.z = pack_bf16x2(pv[q * 8 + 4], pv[q * 8 + 5]);
-          o.w = pack_bf16x2(pv[q * 8 + 6], pv[q * 8 + 7]);
-          const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-          *reinterpret_cast<uint4*>(pp + chunk * 16) = o;
-        }
+        tmem_st_32x32b_x16(tm_s + c * 16, pk);
       }
       l_run += lsum;
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[s]);
     }
-    if (ok && mbar_wait(o_full, 0, p.status, ERR_TIMEOUT_TMEM_FULL)) {
+    if (ok && nts > 0 && mbar_wait(&o_full[s], 0, p.status, ERR_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool row_ok = q_pos < len;
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = p.out + (size_t)(row_base + q_pos) * p.ldo + head * AT_HD;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tm_o + c * 32, o);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]) * inv_l, __uint_as_float(v[q * 8 + 1]) * inv_l);
-            o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]) * inv_l, __uint_as_float(v[q * 8 + 3]) * inv_l);
-            o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]) * inv_l, __uint_as_float(v[q * 8 + 5]) * inv_l);
-            o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]) * inv_l, __uint_as_float(v[q * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv_l, __uint_as_float(o[q * 8 + 1]) * inv_l);
+            w.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv_l, __uint_as_float(o[q * 8 + 3]) * inv_l);
+            w.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv_l, __uint_as_float(o[q * 8 + 5]) * inv_l);
+            w.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv_l, __uint_as_float(o[q * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = w;
           }
         }
       }
@@ -256,6 +288,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
   __syncwarp();
   if (p.status != nullptr && *(volatile int*)p.status != 0) {
+    // a wait gave up somewhere: give copies in flight time to land before the shared memory is released
     uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
@@ -263,7 +296,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -274,15 +307,18 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 using namespace b200;
 
-// q / k / v: row-major matrices with T rows; *_cols = number of columns the tensor map may address, *_ld = row stride,
-// *_col0 = column where head 0 starts (so q, k, v may be three views of one fused qkv buffer, or separate tensors).
+// q / k / v: row-major matrices with T rows; *_ld = row stride, *_col0 = column where head 0 starts (so q, k, v may be
+// three views of one fused qkv buffer, or separate tensors). tile_seq / tile_q0 list query tiles of `tile_rows` rows:
+// 128 when the GQA group is even (two heads per CTA), 256 otherwise (two 128-row halves of one head per CTA).
 extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld, int q_col0,
                              int k_col0, int v_col0, const int* cu_seqlens, const int* tile_seq, const int* tile_q0,
-                             int n_tiles, void* out, int ldo, float* lse, int n_seqs, int T, int Hq, int Hkv,
-                             float scale, int* status, void* stream_) {
+                             int n_tiles, int tile_rows, void* out, int ldo, float* lse, int n_seqs, int T, int Hq,
+                             int Hkv, float scale, int* status, void* stream_) {
   if (n_tiles <= 0 || T <= 0) return 0;
   if (Hq % Hkv || (q_ld % 8) || (k_ld % 8) || (v_ld % 8) || (ldo % 8) || (q_col0 % 8) || (k_col0 % 8) || (v_col0 % 8))
     return -10;
+  const int pair_heads = ((Hq / Hkv) % 2 == 0) ? 1 : 0;
+  if (tile_rows != (pair_heads ? 128 : 256) || n_tiles > 65535) return -10;
   CUtensorMap tq, tk, tv;
   int r = make_tmap_bf16_2d(&tq, q, T, q_ld, q_ld, 128, 64);
   if (r) return r;
@@ -299,9 +335,9 @@ extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, int q_
   AttnFwdParams p;
   p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.n_seqs = n_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
-  p.ldo = ldo; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.ldo = ldo; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0; p.n_tiles = n_tiles; p.pair_heads = pair_heads;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  dim3 grid(n_tiles, Hq);
-  attn_fwd_kernel<<<grid, 192, AtSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
+  dim3 grid(pair_heads ? Hq / 2 : Hq, n_tiles);
+  attn_fwd_kernel<<<grid, 320, AtSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import weakref
 import os
 
 import torch
@@ -45,17 +46,34 @@ def _pick_varlen_impl(q, k, v, cu_seqlens, max_seqlen, scale):
     _varlen_impl = tv
 
 
-def _query_tiles(cu_seqlens: torch.Tensor, T: int, n_seqs: int):
-    """Device-side list of 128-row query tiles: (tile_seq [n], tile_q0 [n]); n = T//128 + n_seqs is an upper bound,
-    surplus entries carry tile_seq = n_seqs (the kernel skips them). No host synchronisation."""
-    n = T // 128 + n_seqs
+_tile_cache: dict = {}
+
+
+def _query_tiles_cached(cu_seqlens: torch.Tensor, T: int, n_seqs: int, rows: int):
+    """The tile list depends only on cu_seqlens, which every layer of a forward pass shares: keep the last few,
+    keyed by tensor identity and in-place version (a weak reference guards against a recycled id)."""
+    key = (id(cu_seqlens), cu_seqlens._version, T, rows)
+    hit = _tile_cache.get(key)
+    if hit is not None and hit[0]() is cu_seqlens:
+        return hit[1]
+    if len(_tile_cache) >= 8:
+        _tile_cache.clear()
+    val = _query_tiles(cu_seqlens, T, n_seqs, rows)
+    _tile_cache[key] = (weakref.ref(cu_seqlens), val)
+    return val
+
+
+def _query_tiles(cu_seqlens: torch.Tensor, T: int, n_seqs: int, rows: int = 128):
+    """Device-side list of `rows`-row query tiles: (tile_seq [n], tile_q0 [n]); n = T//rows + n_seqs is an upper
+    bound, surplus entries carry tile_seq = n_seqs (the kernel skips them). No host synchronisation."""
+    n = T // rows + n_seqs
     lens = (cu_seqlens[1:] - cu_seqlens[:-1]).long()
-    per = (lens + 127) // 128
+    per = (lens + rows - 1) // rows
     ends = torch.cumsum(per, 0)
     t = torch.arange(n, device=cu_seqlens.device)
     seq = torch.searchsorted(ends, t, right=True)
     starts = ends - per
-    q0 = (t - starts[seq.clamp_max(n_seqs - 1)]) * 128
+    q0 = (t - starts[seq.clamp_max(n_seqs - 1)]) * rows
     return seq.int().contiguous(), q0.int().contiguous(), n
 
 
@@ -67,13 +85,14 @@ def attn_fwd_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     assert D == 128 and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D
     assert k.stride(1) == D and v.stride(1) == D and k.stride(2) == 1 and v.stride(2) == 1
     n_seqs = cu_seqlens.numel() - 1
-    tile_seq, tile_q0, n = _query_tiles(cu_seqlens, T, n_seqs)
+    rows = 128 if (Hq // Hkv) % 2 == 0 else 256     # two heads per CTA, or two 128-row halves of one head
+    tile_seq, tile_q0, n = _query_tiles_cached(cu_seqlens, T, n_seqs, rows)
     out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
     rc = _lib.lib().b200_attn_fwd(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.c_int(q.stride(0)), ctypes.c_int(k.stride(0)),
         ctypes.c_int(v.stride(0)), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0), _lib.ptr(cu_seqlens),
-        _lib.ptr(tile_seq), _lib.ptr(tile_q0), ctypes.c_int(n), _lib.ptr(out), ctypes.c_int(Hq * D), _lib.ptr(lse),
+        _lib.ptr(tile_seq), _lib.ptr(tile_q0), ctypes.c_int(n), ctypes.c_int(rows), _lib.ptr(out), ctypes.c_int(Hq * D), _lib.ptr(lse),
         ctypes.c_int(n_seqs), ctypes.c_int(T), ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_float(scale),
         _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
     _lib.check_rc(rc, "attn_fwd")

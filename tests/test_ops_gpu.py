@@ -177,7 +177,8 @@ def test_rl_kernels_match_reference():
     _close(l1, l2, rtol=1e-3, atol=1e-5); _close(v.grad, v2.grad, rtol=1e-3, atol=1e-6)
 
 
-@pytest.mark.parametrize("Hq,Hkv,lens", [(4, 2, [1, 127, 128, 129, 300]), (12, 2, [513, 40]), (8, 8, [1024])])
+@pytest.mark.parametrize("Hq,Hkv,lens", [(4, 2, [1, 127, 128, 129, 300]), (12, 2, [513, 40]), (8, 8, [1024]),
+                                         (7, 1, [700, 129, 5, 256])])
 def test_attn_fwd_tcgen05(Hq, Hkv, lens):
     from openrlhf_b200.ops import _lib, reference as R
     from openrlhf_b200.ops.attention import attn_fwd_tcgen05
