@@ -69,7 +69,7 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_splitk", "decode_attn", "attn_fwd", "logprob",
+    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_splitk", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
                                                          "rmsnorm", "adamw"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
@@ -89,7 +89,7 @@ def main():
     GRAPH = a.graph
     from openrlhf_b200.ops import _lib
     from openrlhf_b200.ops import functional as F
-    from openrlhf_b200.ops.attention import attn_fwd_tcgen05, paged_decode
+    from openrlhf_b200.ops.attention import attn_bwd_tcgen05, attn_fwd_tcgen05, paged_decode
     from openrlhf_b200.ops.gemm import gemm, gemm_splitk
 
     hbm, tf, tag = _peaks()
@@ -130,6 +130,19 @@ def main():
         fl = 4.0 * (T // L) * (L * (L + 128) / 2) * Hq * 128
         print(f"attn_fwd T{T} seq{L} Hq{Hq} Hkv{Hkv}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
               f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
+    elif a.kernel == "attn_bwd":
+        T, Hq, Hkv, L = a.m, a.hq, a.hkv, a.ctx
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device=dev, dtype=torch.bfloat16)
+        q = qkv[:, : Hq * 128].view(T, Hq, 128)
+        k = qkv[:, Hq * 128:(Hq + Hkv) * 128].view(T, Hkv, 128)
+        v = qkv[:, (Hq + Hkv) * 128:].view(T, Hkv, 128)
+        cu = torch.arange(0, T + 1, L, device=dev, dtype=torch.int32)
+        out, lse = attn_fwd_tcgen05(q, k, v, cu, 1 / math.sqrt(128))
+        dout = torch.randn_like(out)
+        t = _time(lambda: attn_bwd_tcgen05(q, k, v, out, dout, lse, cu, 1 / math.sqrt(128)), a.iters)
+        fl = 10.0 * (T // L) * (L * (L + 128) / 2) * Hq * 128
+        print(f"attn_bwd T{T} seq{L} Hq{Hq} Hkv{Hkv}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+              f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak; includes delta, zeroing and the fp32->bf16 pass)")
     elif a.kernel == "logprob":
         T, V, H = a.m, a.n, a.k
         h = torch.randn(T, H, device=dev, dtype=torch.bfloat16)

@@ -155,6 +155,11 @@ class TransformerLM(nn.Module):
             qn = F.rmsnorm(qk[:, :Hq].reshape(-1, D), self.p(pre + "q_norm.weight"), cfg.rms_norm_eps).view(T, Hq * D)
             kn = F.rmsnorm(qk[:, Hq:].reshape(-1, D), self.p(pre + "k_norm.weight"), cfg.rms_norm_eps).view(T, Hkv * D)
             qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * D:]], dim=1)
+        if attn_fn is None and qkv.is_cuda and D == 128 and qkv.dtype == torch.bfloat16:
+            from ..ops.attention import rope_attention
+
+            a = rope_attention(qkv, pos, self.rope(qkv.device), cu_seqlens, Hq, Hkv, 1.0 / math.sqrt(D))
+            return self._lin(i, "o", a, None, h)
         qkv = F.rope(qkv, pos, self.rope(qkv.device), Hq + Hkv, D)
         q = qkv[:, : Hq * D].view(T, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)

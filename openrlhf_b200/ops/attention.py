@@ -99,46 +99,105 @@ def attn_fwd_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     return out, lse
 
 
+def attn_bwd_tcgen05(q, k, v, out, dout, lse, cu_seqlens, scale, pos=None, rope_table=None):
+    """tcgen05 causal varlen backward. q [T,Hq,128], k/v [T,Hkv,128] (the tensors the forward saw: rotated), out /
+    dout [T,Hq,128], lse [Hq,T]. Returns dqkv bf16 [T, (Hq+2*Hkv)*128] = [dq | dk | dv]; when pos / rope_table are
+    given, dq and dk are rotated back (gradient with respect to the un-rotated projections)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and out.is_contiguous()
+    dout = dout if (dout.stride(2) == 1 and dout.stride(1) == D and dout.stride(0) % 8 == 0) else dout.contiguous()
+    n_seqs = cu_seqlens.numel() - 1
+    tile_seq, tile_k0, n = _query_tiles_cached(cu_seqlens, T, n_seqs, 128)
+    W = (Hq + 2 * Hkv) * D
+    delta = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    acc = torch.empty(T, W, dtype=torch.float32, device=q.device)
+    dqkv = torch.empty(T, W, dtype=torch.bfloat16, device=q.device)
+    rc = _lib.lib().b200_attn_bwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ctypes.c_int(q.stride(0)), ctypes.c_int(k.stride(0)),
+        ctypes.c_int(v.stride(0)), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0), _lib.ptr(out),
+        ctypes.c_int(Hq * D), _lib.ptr(dout), ctypes.c_int(dout.stride(0)), _lib.ptr(lse), _lib.ptr(cu_seqlens),
+        _lib.ptr(tile_seq), _lib.ptr(tile_k0), ctypes.c_int(n), _lib.ptr(delta), _lib.ptr(acc), _lib.ptr(dqkv),
+        _lib.ptr(pos), _lib.ptr(rope_table), ctypes.c_int(rope_table.shape[0] if rope_table is not None else 0),
+        ctypes.c_int(n_seqs), ctypes.c_int(T), ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_float(scale),
+        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "attn_bwd")
+    return dqkv
+
+
 class _AttnVarlen(torch.autograd.Function):
-    """Forward on this repository's tcgen05 kernel; backward through a library varlen flash-attention backward fed
-    with that forward's output and log-sum-exp (or, if that entry point is unusable, by re-running the library
-    forward under autograd)."""
+    """Forward and backward on this repository's tcgen05 kernels."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
         out, lse = attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)
         ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
-        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+        ctx.scale = scale
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, cu = ctx.saved_tensors
-        global _fa_bwd_ok
-        if _fa_bwd_ok is not False:
-            try:
-                from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
-
-                dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-                qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
-                dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
-                _flash_attn_varlen_backward(dout.contiguous(), qc, kc, vc, out, lse, dq, dk, dv, cu, cu,
-                                            ctx.max_seqlen, ctx.max_seqlen, 0.0, ctx.scale, True, -1, -1, 0.0, None,
-                                            False, None)
-                _fa_bwd_ok = True
-                return dq, dk, dv, None, None, None
-            except Exception:  # noqa: BLE001
-                if _fa_bwd_ok is True:
-                    raise
-                _fa_bwd_ok = False
-        with torch.enable_grad():
-            qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
-            o = _library_varlen(qd, kd, vd, cu, ctx.max_seqlen, ctx.scale)
-            dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), dout)
+        T, Hq, D = q.shape
+        Hkv = k.shape[1]
+        dqkv = attn_bwd_tcgen05(q, k, v, out, dout, lse, cu, ctx.scale)
+        dq = dqkv[:, : Hq * D].view(T, Hq, D)
+        dk = dqkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+        dv = dqkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
         return dq, dk, dv, None, None, None
 
 
-_fa_bwd_ok = None
+class _RopeAttn(torch.autograd.Function):
+    """Rotary embedding + causal varlen attention on the fused projection output qkv [T, (Hq+2*Hkv)*128]. The rotation
+    is applied in place (nothing upstream keeps the projection output for its own backward); the backward returns one
+    dqkv tensor in the same fused layout, so no per-slice gradient buffers are assembled."""
+
+    @staticmethod
+    def forward(ctx, qkv, pos, table, cu_seqlens, Hq, Hkv, scale):
+        from .functional import _rope_inplace
+
+        T, D = qkv.shape[0], 128
+        if qkv._is_view() or qkv.is_leaf or not qkv.is_contiguous():
+            qkv = qkv.clone()
+        else:
+            ctx.mark_dirty(qkv)
+        _rope_inplace(qkv, pos, table, Hq + Hkv, D, 1.0)
+        q = qkv[:, : Hq * D].view(T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        out, lse = attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens, pos, table)
+        ctx.dims = (Hq, Hkv, scale)
+        return out.view(T, Hq * D), qkv
+
+    @staticmethod
+    def backward(ctx, dout, _dqkv_unused):
+        qkv, out, lse, cu, pos, table = ctx.saved_tensors
+        Hq, Hkv, scale = ctx.dims
+        T, D = qkv.shape[0], 128
+        q = qkv[:, : Hq * D].view(T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        dqkv = attn_bwd_tcgen05(q, k, v, out, dout.view(T, Hq, D), lse, cu, scale, pos, table)
+        return dqkv, None, None, None, None, None, None
+
+
+def rope_attention(qkv: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, cu_seqlens: torch.Tensor, Hq: int,
+                   Hkv: int, scale: float) -> torch.Tensor:
+    """Fused rotary embedding + packed causal GQA attention (head_dim 128, bf16, CUDA). Returns [T, Hq*128]."""
+    if torch.is_grad_enabled() and qkv.requires_grad:
+        return _RopeAttn.apply(qkv, pos, table, cu_seqlens, Hq, Hkv, scale)[0]
+    from .functional import _rope_inplace
+
+    T, D = qkv.shape[0], 128
+    qkv = qkv if (qkv.is_contiguous() and not qkv.requires_grad) else qkv.detach().clone()
+    _rope_inplace(qkv, pos, table, Hq + Hkv, D, 1.0)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    return attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)[0].view(T, Hq * D)
+
+
 USE_OWN_FWD = os.environ.get("OPENRLHF_B200_ATTN_FWD", "1") == "1"
 
 
