@@ -34,7 +34,10 @@ struct AttnBwdParams {
   float* dq_acc;            // fp32, zero-initialised: row stride acc_ld, head h at column h*128
   float* dk_acc;            // same row stride, kv-head h at column h*128
   float* dv_acc;
-  int acc_ld;
+  int acc_ld;               // row stride of dq_acc
+  int dkv_ld;               // row stride of dk_acc / dv_acc
+  int q_row_off, q_rows;    // context parallel: q / dO / lse / delta / dq_acc hold the rows [q_row_off, q_row_off +
+                            // q_rows) of the packed stream; K, V, dk_acc, dv_acc and cu_seqlens index it globally
   int n_seqs, T, Hq, Hkv;
   int q_col0, k_col0, v_col0;
   float scale, scale_log2;
@@ -94,7 +97,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int k0 = p.tile_k0[blockIdx.y];
   if (k0 >= len) return;
   const int jt = k0 >> 7;
-  const int n = (len + 127) / 128 - jt;            // query tiles i = jt .. jt + n - 1
+  // query tiles i = i_lo .. i_lo + n - 1: at or below the diagonal, and among the rows this rank holds
+  const int i_lo = max(jt, (max(0, p.q_row_off - row_base) + 127) >> 7);
+  const int i_hi = min((len + 127) >> 7, (p.q_row_off + p.q_rows - row_base + 127) >> 7);
+  const int n = i_hi - i_lo;
+  if (n <= 0) return;
+  const int q_base = row_base - p.q_row_off;       // local row of the document's first token
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -136,7 +144,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       for (int it = 0; it < n; ++it) {
         const int st = it & 1;
         if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
-        const int r = row_base + (jt + it) * 128;
+        const int r = q_base + (i_lo + it) * 128;
         uint8_t* sq = smem + AbSmem::Q_OFF + st * AB_TILE;
         uint8_t* sdo = smem + AbSmem::DO_OFF + st * AB_TILE;
         mbar_expect_tx(&qdo_full[st], 2 * AB_TILE);
@@ -220,7 +228,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!mbar_wait(&stat_full[st], (it >> 1) & 1, p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
       if (!mbar_wait(s_full, it & 1, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const bool diag = (it == 0);               // query tile == key tile: keep q >= k only
+      const bool diag = (i_lo + it == jt);       // query tile == key tile: keep q >= k only
       uint32_t pk[64];                           // P^T row as bf16 pairs
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -281,7 +289,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (ok && mbar_wait(dkv_full, 0, p.status, ERR_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const int kv = k0 + r;
-      float* dst = p.dv_acc + (size_t)(row_base + kv) * p.acc_ld + kvh * 128;
+      float* dst = p.dv_acc + (size_t)(row_base + kv) * p.dkv_ld + kvh * 128;
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t v[32];
@@ -301,10 +309,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     auto stage_stats = [&](int it) {
-      const int q_pos = (jt + it) * 128 + r;
+      const int q_pos = (i_lo + it) * 128 + r;
       float l2 = INFINITY, d = 0.f;              // past the sequence end: P becomes exp2(-inf) = 0
       if (q_pos < len) {
-        const size_t idx = (size_t)head * p.T + row_base + q_pos;
+        const size_t idx = (size_t)head * p.q_rows + q_base + q_pos;
         l2 = p.lse[idx] * 1.4426950408889634f;
         d = p.delta[idx];
       }
@@ -322,8 +330,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_after();
       // lane = query row; 16-byte vector reductions (measured faster than scalar reductions that a warp issues over
       // 128 contiguous bytes: the L2 reduction rate follows the instruction count, not the sector count)
-      const int q_pos = (jt + it) * 128 + r;
-      float* dst = p.dq_acc + (size_t)(row_base + q_pos) * p.acc_ld + head * 128;
+      const int q_pos = (i_lo + it) * 128 + r;
+      float* dst = p.dq_acc + (size_t)(q_base + q_pos) * p.acc_ld + head * 128;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t v[64];
@@ -349,7 +357,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (ok && mbar_wait(dkv_full, 0, p.status, ERR_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const int kv = k0 + r;
-      float* dst = p.dk_acc + (size_t)(row_base + kv) * p.acc_ld + kvh * 128;
+      float* dst = p.dk_acc + (size_t)(row_base + kv) * p.dkv_ld + kvh * 128;
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t v[32];
@@ -440,6 +448,59 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 using namespace b200;
 
+static int launch_delta(const void* out, int ldo, const void* dout, int lddo, float* delta, int rows, int Hq,
+                        cudaStream_t stream) {
+  const long long warps = (long long)rows * Hq;
+  const int blocks = (int)std::min<long long>((warps * 32 + 255) / 256, 148 * 16);
+  attn_bwd_delta_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                    reinterpret_cast<const __nv_bfloat16*>(dout), delta, rows, Hq, ldo,
+                                                    lddo);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+static int launch_finalize(const float* acc, void* dqkv, const int* pos, const void* cos_sin, int max_pos, int rows,
+                           int Hq, int Hkv, cudaStream_t stream) {
+  const long long work = (long long)rows * (Hq + 2 * Hkv) * 16;
+  const int blocks = (int)std::min<long long>((work + 255) / 256, 148 * 16);
+  attn_bwd_finalize_kernel<<<blocks, 256, 0, stream>>>(acc, reinterpret_cast<__nv_bfloat16*>(dqkv), pos,
+                                                       reinterpret_cast<const float2*>(cos_sin), rows, Hq + 2 * Hkv,
+                                                       (pos != nullptr && cos_sin != nullptr) ? Hq + Hkv : 0, max_pos);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+static int launch_main(const void* q, int q_rows, const void* k, const void* v, int kv_rows, int q_ld, int k_ld, int v_ld,
+                       int q_col0, int k_col0, int v_col0, const void* dout, int lddo, const float* lse,
+                       const float* delta, const int* cu_seqlens, const int* tile_seq, const int* tile_k0, int n_tiles,
+                       float* dq_acc, int dq_ld, float* dk_acc, float* dv_acc, int dkv_ld, int q_row_off, int n_seqs,
+                       int Hq, int Hkv, float scale, int* status, cudaStream_t stream) {
+  if (Hq % Hkv || (q_ld % 8) || (k_ld % 8) || (v_ld % 8) || (lddo % 8) || (q_col0 % 8) || (k_col0 % 8) || (v_col0 % 8) ||
+      n_tiles > 65535)
+    return -10;
+  CUtensorMap tq, tk, tv, tdo;
+  int r = make_tmap_bf16_2d(&tq, q, q_rows, q_ld, q_ld, 128, 64);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tk, k, kv_rows, k_ld, k_ld, 128, 64);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tv, v, kv_rows, v_ld, v_ld, 128, 64);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tdo, dout, q_rows, lddo, lddo, 128, 64);
+  if (r) return r;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AbSmem::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  AttnBwdParams p;
+  p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_k0 = tile_k0; p.lse = lse; p.delta = delta;
+  p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dv_acc = dv_acc; p.acc_ld = dq_ld; p.dkv_ld = dkv_ld;
+  p.q_row_off = q_row_off; p.q_rows = q_rows;
+  p.n_seqs = n_seqs; p.T = q_rows; p.Hq = Hq; p.Hkv = Hkv; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  attn_bwd_kernel<<<dim3(Hq, n_tiles), 320, AbSmem::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 // Backward of b200_attn_fwd. q / k / v as there (already rotated); out / dout [T, Hq*128] with row strides ldo / lddo;
 // lse [Hq, T]. Workspaces: delta fp32 [Hq, T]; acc fp32 [T, (Hq + 2 Hkv) * 128] (zeroed here). Result: dqkv bf16
 // [T, (Hq + 2 Hkv) * 128] = [dq heads | dk heads | dv heads]; with pos / cos_sin given, dq and dk are rotated back so
@@ -450,47 +511,46 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, int q_
                              int n_tiles, float* delta, float* acc, void* dqkv, const int* pos, const void* cos_sin,
                              int max_pos, int n_seqs, int T, int Hq, int Hkv, float scale, int* status, void* stream_) {
   if (n_tiles <= 0 || T <= 0) return 0;
-  if (Hq % Hkv || (q_ld % 8) || (k_ld % 8) || (v_ld % 8) || (ldo % 8) || (lddo % 8) || (q_col0 % 8) || (k_col0 % 8) ||
-      (v_col0 % 8) || n_tiles > 65535)
-    return -10;
+  if ((ldo % 8) || (lddo % 8)) return -10;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  CUtensorMap tq, tk, tv, tdo;
-  int r = make_tmap_bf16_2d(&tq, q, T, q_ld, q_ld, 128, 64);
-  if (r) return r;
-  r = make_tmap_bf16_2d(&tk, k, T, k_ld, k_ld, 128, 64);
-  if (r) return r;
-  r = make_tmap_bf16_2d(&tv, v, T, v_ld, v_ld, 128, 64);
-  if (r) return r;
-  r = make_tmap_bf16_2d(&tdo, dout, T, lddo, lddo, 128, 64);
-  if (r) return r;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AbSmem::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
   const int W = (Hq + 2 * Hkv) * 128;
   if (cudaMemsetAsync(acc, 0, (size_t)T * W * sizeof(float), stream) != cudaSuccess) return -3;
-  {
-    const long long warps = (long long)T * Hq;
-    const int blocks = (int)std::min<long long>((warps * 32 + 255) / 256, 148 * 16);
-    attn_bwd_delta_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(out),
-                                                      reinterpret_cast<const __nv_bfloat16*>(dout), delta, T, Hq, ldo,
-                                                      lddo);
-  }
-  AttnBwdParams p;
-  p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_k0 = tile_k0; p.lse = lse; p.delta = delta;
-  p.dq_acc = acc; p.dk_acc = acc + Hq * 128; p.dv_acc = acc + (Hq + Hkv) * 128; p.acc_ld = W;
-  p.n_seqs = n_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
-  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  attn_bwd_kernel<<<dim3(Hq, n_tiles), 320, AbSmem::TOTAL, stream>>>(tq, tk, tv, tdo, p);
-  if (cudaGetLastError() != cudaSuccess) return -3;
-  {
-    const long long work = (long long)T * (Hq + 2 * Hkv) * 16;
-    const int blocks = (int)std::min<long long>((work + 255) / 256, 148 * 16);
-    attn_bwd_finalize_kernel<<<blocks, 256, 0, stream>>>(acc, reinterpret_cast<__nv_bfloat16*>(dqkv), pos,
-                                                         reinterpret_cast<const float2*>(cos_sin), T, Hq + 2 * Hkv,
-                                                         (pos != nullptr && cos_sin != nullptr) ? Hq + Hkv : 0, max_pos);
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  int r = launch_delta(out, ldo, dout, lddo, delta, T, Hq, stream);
+  if (r) return r;
+  r = launch_main(q, T, k, v, T, q_ld, k_ld, v_ld, q_col0, k_col0, v_col0, dout, lddo, lse, delta, cu_seqlens, tile_seq,
+                  tile_k0, n_tiles, acc, W, acc + Hq * 128, acc + (Hq + Hkv) * 128, W, 0, n_seqs, Hq, Hkv, scale, status,
+                  stream);
+  if (r) return r;
+  return launch_finalize(acc, dqkv, pos, cos_sin, max_pos, T, Hq, Hkv, stream);
+}
+
+// Context-parallel backward, first half: this rank's query rows against the gathered K/V (kv_g, as left by
+// b200_attn_fwd_cp). dq goes into acc_local [T_loc, W] (columns of the q heads; the whole buffer is zeroed here); dk /
+// dv partial sums go into this rank's dkv_g [T_total, 2*Hkv*128] fp32 at global rows (rows [kv_tile_lo*128,
+// (rank+1)*T_loc) are zeroed here). After a barrier, b200_cp_dkv_reduce sums the peers' partials for the local rows
+// into acc_local's k / v columns and b200_attn_bwd_finalize produces the bf16 dqkv.
+extern "C" int b200_attn_bwd_cp(const void* qkv_local, const void* kv_g, int world, int rank, int T_loc, int kv_tile_lo,
+                                const void* out, const void* dout, int lddo, const float* lse, const int* cu_seqlens,
+                                const int* tile_seq, const int* tile_k0, int n_tiles, float* delta, float* acc_local,
+                                float* dkv_g, int n_seqs, int Hq, int Hkv, float scale, int* status, void* stream_) {
+  if (n_tiles <= 0 || T_loc <= 0) return 0;
+  if (T_loc % 128 || (lddo % 8)) return -10;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int W = (Hq + 2 * Hkv) * 128, kv_cols = 2 * Hkv * 128;
+  if (cudaMemsetAsync(acc_local, 0, (size_t)T_loc * W * sizeof(float), stream) != cudaSuccess) return -3;
+  const size_t row_lo = (size_t)kv_tile_lo * 128, row_hi = (size_t)(rank + 1) * T_loc;
+  if (cudaMemsetAsync(dkv_g + row_lo * kv_cols, 0, (row_hi - row_lo) * kv_cols * sizeof(float), stream) != cudaSuccess)
+    return -3;
+  int r = launch_delta(out, Hq * 128, dout, lddo, delta, T_loc, Hq, stream);
+  if (r) return r;
+  const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(kv_g);
+  return launch_main(qkv_local, T_loc, kv, kv + Hkv * 128, world * T_loc, W, kv_cols, kv_cols, 0, 0, 0, dout, lddo, lse,
+                     delta, cu_seqlens, tile_seq, tile_k0, n_tiles, acc_local, W, dkv_g, dkv_g + Hkv * 128, kv_cols,
+                     rank * T_loc, n_seqs, Hq, Hkv, scale, status, stream);
+}
+
+extern "C" int b200_attn_bwd_finalize(const float* acc, void* dqkv, const int* pos, const void* cos_sin, int max_pos,
+                                      int rows, int Hq, int Hkv, void* stream_) {
+  if (rows <= 0) return 0;
+  return launch_finalize(acc, dqkv, pos, cos_sin, max_pos, rows, Hq, Hkv, reinterpret_cast<cudaStream_t>(stream_));
 }

@@ -16,6 +16,8 @@
 // maximum grew by more than 2^8). Outputs: O (bf16) and the log-sum-exp per (head, token) for the backward pass.
 // Takes the place of flash-attn 2's varlen forward that the reference reaches through HF Transformers
 // (openrlhf/models/actor.py:152 sets attn_implementation="flash_attention_2").
+#include <cstring>
+
 #include "ptx.cuh"
 
 namespace b200 {
@@ -32,8 +34,23 @@ struct AttnFwdParams {
   int n_seqs, T, Hq, Hkv, ldo;
   int q_col0, k_col0, v_col0;   // column of head 0 inside the q / k / v matrices the tensor maps describe
   int n_tiles, pair_heads;
+  int q_row_off, q_rows;   // context parallel: q / out / lse hold the rows [q_row_off, q_row_off + q_rows) of the
+                           // packed stream that cu_seqlens and the K/V tensor maps index globally (0, T otherwise)
+  const int* kv_flags;     // context parallel: kv_flags[row / 128] == kv_epoch once that K/V tile has been gathered
+  int kv_epoch;
   float scale_log2;
   int* status;
+};
+
+// Context-parallel gather role: the first n_copy_y rows of the grid copy the K/V rows [tile_lo*128, tile_hi*128) of
+// the packed stream from their owners' fused qkv buffers (peer memory, plain loads) into this GPU's gathered K/V
+// buffer and publish one flag per 128-row tile, so that every remote byte crosses NVLink once and the attention CTAs
+// of the same launch start on a tile as soon as it has landed.
+struct CpGather {
+  const __nv_bfloat16* peer_qkv[8];   // each rank's [rows_per_rank, src_ld] buffer
+  __nv_bfloat16* kv_g;                // [T_total, kv_cols]
+  int* flags;
+  int n_copy_y, tile_lo, tile_hi, rows_per_rank, src_ld, src_col0, kv_cols, epoch;
 };
 
 struct AtSmem {
@@ -46,7 +63,30 @@ struct AtSmem {
 
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                const __grid_constant__ CUtensorMap tma_v, const AttnFwdParams p) {
+                const __grid_constant__ CUtensorMap tma_v, const AttnFwdParams p, const CpGather cp) {
+  if ((int)blockIdx.y < cp.n_copy_y) {
+    // ------------------------------------------------------------ gather CTAs (lowest block indices: scheduled first)
+    const int n_cta = cp.n_copy_y * gridDim.x;
+    const int vec_per_row = cp.kv_cols >> 3;
+    for (int tile = cp.tile_lo + blockIdx.y * gridDim.x + blockIdx.x; tile < cp.tile_hi; tile += n_cta) {
+      const int row0 = tile * 128;
+      const int owner = row0 / cp.rows_per_rank;
+      const __nv_bfloat16* src = cp.peer_qkv[owner] + (size_t)(row0 - owner * cp.rows_per_rank) * cp.src_ld + cp.src_col0;
+      __nv_bfloat16* dst = cp.kv_g + (size_t)row0 * cp.kv_cols;
+      for (int i = threadIdx.x; i < 128 * vec_per_row; i += blockDim.x) {
+        const int r = i / vec_per_row, c = i % vec_per_row;
+        reinterpret_cast<uint4*>(dst + (size_t)r * cp.kv_cols)[c] =
+            reinterpret_cast<const uint4*>(src + (size_t)r * cp.src_ld)[c];
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // the tile is read back by TMA (async proxy)
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(cp.flags + tile), "r"(cp.epoch) : "memory");
+      }
+    }
+    return;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AtSmem::BAR_OFF);
@@ -61,7 +101,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = p.n_tiles - 1 - (int)blockIdx.y;    // later (longer) tiles of a sequence start first
+  const int t = p.n_tiles - 1 - ((int)blockIdx.y - cp.n_copy_y);   // later (longer) tiles of a sequence start first
   const int seq = p.tile_seq[t];
   if (seq < 0 || seq >= p.n_seqs) return;           // padding tile: whole CTA leaves before touching TMEM
   const int row_base = p.cu_seqlens[seq];
@@ -72,9 +112,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int q0_0 = tq0, q0_1 = p.pair_heads ? tq0 : tq0 + 128;
   const int kvh = head0 / (p.Hq / p.Hkv);
   // causal: keys up to the last query row of the stream's tile
-  const int nt0 = q0_0 < len ? (min(len, q0_0 + 128) + 127) / 128 : 0;
-  const int nt1 = q0_1 < len ? (min(len, q0_1 + 128) + 127) / 128 : 0;
+  const int lr0 = row_base + q0_0 - p.q_row_off, lr1 = row_base + q0_1 - p.q_row_off;   // rows inside q / out / lse
+  const int nt0 = (q0_0 < len && lr0 >= 0 && lr0 < p.q_rows) ? (min(len, q0_0 + 128) + 127) / 128 : 0;
+  const int nt1 = (q0_1 < len && lr1 >= 0 && lr1 < p.q_rows) ? (min(len, q0_1 + 128) + 127) / 128 : 0;
   const int n = max(nt0, nt1);
+  if (n == 0) return;                               // context parallel: neither stream belongs to this rank
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -105,13 +147,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tma_prefetch_desc(&tma_v);
       mbar_expect_tx(q_full, ((nt0 > 0) + (nt1 > 0)) * AT_TILE_BYTES);
       if (nt0 > 0) {
-        tma_load_2d(smem + AtSmem::Q_OFF, &tma_q, q_full, p.q_col0 + head0 * AT_HD, row_base + q0_0);
-        tma_load_2d(smem + AtSmem::Q_OFF + 16384, &tma_q, q_full, p.q_col0 + head0 * AT_HD + 64, row_base + q0_0);
+        tma_load_2d(smem + AtSmem::Q_OFF, &tma_q, q_full, p.q_col0 + head0 * AT_HD, lr0);
+        tma_load_2d(smem + AtSmem::Q_OFF + 16384, &tma_q, q_full, p.q_col0 + head0 * AT_HD + 64, lr0);
       }
       if (nt1 > 0) {
         uint8_t* sq1 = smem + AtSmem::Q_OFF + AT_TILE_BYTES;
-        tma_load_2d(sq1, &tma_q, q_full, p.q_col0 + head1 * AT_HD, row_base + q0_1);
-        tma_load_2d(sq1 + 16384, &tma_q, q_full, p.q_col0 + head1 * AT_HD + 64, row_base + q0_1);
+        tma_load_2d(sq1, &tma_q, q_full, p.q_col0 + head1 * AT_HD, lr1);
+        tma_load_2d(sq1 + 16384, &tma_q, q_full, p.q_col0 + head1 * AT_HD + 64, lr1);
       }
       for (int j = 0; j < n; ++j) {
         const int stage = j & 1;
@@ -120,6 +162,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         uint8_t* sk = smem + AtSmem::K_OFF + stage * AT_TILE_BYTES;
         uint8_t* sv = smem + AtSmem::V_OFF + stage * AT_TILE_BYTES;
         if (!mbar_wait(&k_empty[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) break;
+        if (p.kv_flags != nullptr) {                // context parallel: wait (bounded) until the tile was gathered
+          const int* f = p.kv_flags + (r >> 7);
+          const uint64_t t0 = globaltimer_ns();
+          int seen;
+          bool landed = true;
+          while (true) {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+            if (seen == p.kv_epoch) break;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { landed = false; break; }
+            __nanosleep(200);
+          }
+          if (!landed) {
+            if (p.status != nullptr) atomicCAS(p.status, 0, ERR_TIMEOUT_FULL);
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         mbar_expect_tx(&k_full[stage], AT_TILE_BYTES);
         tma_load_2d(sk, &tma_k, &k_full[stage], p.k_col0 + kvh * AT_HD, r);
         tma_load_2d(sk + 16384, &tma_k, &k_full[stage], p.k_col0 + kvh * AT_HD + 64, r);
@@ -263,7 +322,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_after();
       const bool row_ok = q_pos < len;
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = p.out + (size_t)(row_base + q_pos) * p.ldo + head * AT_HD;
+      const int lrow = row_base + q_pos - p.q_row_off;
+      __nv_bfloat16* orow = p.out + (size_t)lrow * p.ldo + head * AT_HD;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -282,7 +342,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       if (row_ok && p.lse != nullptr)
-        p.lse[(size_t)head * p.T + row_base + q_pos] = (m_ref + log2f(l_run)) * 0.6931471805599453f;
+        p.lse[(size_t)head * p.q_rows + lrow] = (m_ref + log2f(l_run)) * 0.6931471805599453f;
     }
   }
 
@@ -307,24 +367,22 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 
 using namespace b200;
 
-// q / k / v: row-major matrices with T rows; *_ld = row stride, *_col0 = column where head 0 starts (so q, k, v may be
-// three views of one fused qkv buffer, or separate tensors). tile_seq / tile_q0 list query tiles of `tile_rows` rows:
-// 128 when the GQA group is even (two heads per CTA), 256 otherwise (two 128-row halves of one head per CTA).
-extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld, int q_col0,
-                             int k_col0, int v_col0, const int* cu_seqlens, const int* tile_seq, const int* tile_q0,
-                             int n_tiles, int tile_rows, void* out, int ldo, float* lse, int n_seqs, int T, int Hq,
-                             int Hkv, float scale, int* status, void* stream_) {
-  if (n_tiles <= 0 || T <= 0) return 0;
+static int launch_attn_fwd(const void* q, int q_rows, const void* k, const void* v, int kv_rows, int q_ld, int k_ld,
+                           int v_ld, int q_col0, int k_col0, int v_col0, const int* cu_seqlens, const int* tile_seq,
+                           const int* tile_q0, int n_tiles, int tile_rows, void* out, int ldo, float* lse, int n_seqs,
+                           int Hq, int Hkv, float scale, int q_row_off, const CpGather& cp, int* status,
+                           void* stream_) {
+  if (n_tiles <= 0 || q_rows <= 0) return 0;
   if (Hq % Hkv || (q_ld % 8) || (k_ld % 8) || (v_ld % 8) || (ldo % 8) || (q_col0 % 8) || (k_col0 % 8) || (v_col0 % 8))
     return -10;
   const int pair_heads = ((Hq / Hkv) % 2 == 0) ? 1 : 0;
-  if (tile_rows != (pair_heads ? 128 : 256) || n_tiles > 65535) return -10;
+  if (tile_rows != (pair_heads ? 128 : 256) || n_tiles + cp.n_copy_y > 65535) return -10;
   CUtensorMap tq, tk, tv;
-  int r = make_tmap_bf16_2d(&tq, q, T, q_ld, q_ld, 128, 64);
+  int r = make_tmap_bf16_2d(&tq, q, q_rows, q_ld, q_ld, 128, 64);
   if (r) return r;
-  r = make_tmap_bf16_2d(&tk, k, T, k_ld, k_ld, 128, 64);
+  r = make_tmap_bf16_2d(&tk, k, kv_rows, k_ld, k_ld, 128, 64);
   if (r) return r;
-  r = make_tmap_bf16_2d(&tv, v, T, v_ld, v_ld, 128, 64);
+  r = make_tmap_bf16_2d(&tv, v, kv_rows, v_ld, v_ld, 128, 64);
   if (r) return r;
   static bool configured = false;
   if (!configured) {
@@ -334,10 +392,48 @@ extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, int q_
   }
   AttnFwdParams p;
   p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
-  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.n_seqs = n_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.n_seqs = n_seqs; p.T = q_rows; p.Hq = Hq; p.Hkv = Hkv;
   p.ldo = ldo; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0; p.n_tiles = n_tiles; p.pair_heads = pair_heads;
+  p.q_row_off = q_row_off; p.q_rows = q_rows; p.kv_flags = cp.n_copy_y > 0 ? cp.flags : nullptr; p.kv_epoch = cp.epoch;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  dim3 grid(pair_heads ? Hq / 2 : Hq, n_tiles);
-  attn_fwd_kernel<<<grid, 320, AtSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
+  dim3 grid(pair_heads ? Hq / 2 : Hq, n_tiles + cp.n_copy_y);
+  attn_fwd_kernel<<<grid, 320, AtSmem::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// q / k / v: row-major matrices with T rows; *_ld = row stride, *_col0 = column where head 0 starts (so q, k, v may be
+// three views of one fused qkv buffer, or separate tensors). tile_seq / tile_q0 list query tiles of `tile_rows` rows:
+// 128 when the GQA group is even (two heads per CTA), 256 otherwise (two 128-row halves of one head per CTA).
+extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld, int q_col0,
+                             int k_col0, int v_col0, const int* cu_seqlens, const int* tile_seq, const int* tile_q0,
+                             int n_tiles, int tile_rows, void* out, int ldo, float* lse, int n_seqs, int T, int Hq,
+                             int Hkv, float scale, int* status, void* stream_) {
+  CpGather cp;
+  memset(&cp, 0, sizeof(cp));
+  return launch_attn_fwd(q, T, k, v, T, q_ld, k_ld, v_ld, q_col0, k_col0, v_col0, cu_seqlens, tile_seq, tile_q0, n_tiles,
+                         tile_rows, out, ldo, lse, n_seqs, Hq, Hkv, scale, 0, cp, status, stream_);
+}
+
+// Context-parallel forward. This rank holds rows [rank*T_loc, (rank+1)*T_loc) of the packed stream in qkv_local
+// [T_loc, W] (fused layout q | k | v, already rotated; every rank's buffer is reachable through peer_qkv). Documents
+// start on multiples of 128 rows, so no K/V tile straddles two ranks. The launch gathers the K/V rows
+// [kv_tile_lo*128, (rank+1)*T_loc) into kv_g [T_total, 2*Hkv*128] with n_copy_y rows of gather CTAs and runs the
+// attention of the local query rows against it; cu_seqlens and the tile list index the global stream. All ranks must
+// have passed a barrier after writing their qkv buffers, and must pass another before those buffers are rewritten.
+extern "C" int b200_attn_fwd_cp(const void* qkv_local, const void* const* peer_qkv, int world, int rank, int T_loc,
+                                void* kv_g, int* flags, int epoch, int kv_tile_lo, int n_copy_y, const int* cu_seqlens,
+                                const int* tile_seq, const int* tile_q0, int n_tiles, int tile_rows, void* out,
+                                float* lse, int n_seqs, int Hq, int Hkv, float scale, int* status, void* stream_) {
+  if (world < 1 || world > 8 || T_loc % 128 || n_copy_y < 1) return -10;
+  const int W = (Hq + 2 * Hkv) * 128, kv_cols = 2 * Hkv * 128;
+  CpGather cp;
+  memset(&cp, 0, sizeof(cp));
+  for (int i = 0; i < world; ++i) cp.peer_qkv[i] = reinterpret_cast<const __nv_bfloat16*>(peer_qkv[i]);
+  cp.kv_g = reinterpret_cast<__nv_bfloat16*>(kv_g); cp.flags = flags; cp.n_copy_y = n_copy_y; cp.tile_lo = kv_tile_lo;
+  cp.tile_hi = (rank + 1) * T_loc / 128; cp.rows_per_rank = T_loc; cp.src_ld = W; cp.src_col0 = Hq * 128;
+  cp.kv_cols = kv_cols; cp.epoch = epoch;
+  const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(kv_g);
+  return launch_attn_fwd(qkv_local, T_loc, kv, kv + Hkv * 128, world * T_loc, W, kv_cols, kv_cols, 0, 0, 0, cu_seqlens,
+                         tile_seq, tile_q0, n_tiles, tile_rows, out, Hq * 128, lse, n_seqs, Hq, Hkv, scale,
+                         rank * T_loc, cp, status, stream_);
 }
