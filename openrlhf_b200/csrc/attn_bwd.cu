@@ -526,8 +526,8 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, int q_
 
 // Context-parallel backward, first half: this rank's query rows against the gathered K/V (kv_g, as left by
 // b200_attn_fwd_cp). dq goes into acc_local [T_loc, W] (columns of the q heads; the whole buffer is zeroed here); dk /
-// dv partial sums go into this rank's dkv_g [T_total, 2*Hkv*128] fp32 at global rows (rows [kv_tile_lo*128,
-// (rank+1)*T_loc) are zeroed here). After a barrier, b200_cp_dkv_reduce sums the peers' partials for the local rows
+// dv partial sums go into this rank's dkv_g [T_total, 2*Hkv*128] fp32 at global rows (rows [0, (rank+1)*T_loc) are
+// zeroed here). After a barrier, b200_cp_dkv_reduce sums the peers' partials for the local rows
 // into acc_local's k / v columns and b200_attn_bwd_finalize produces the bf16 dqkv.
 extern "C" int b200_attn_bwd_cp(const void* qkv_local, const void* kv_g, int world, int rank, int T_loc, int kv_tile_lo,
                                 const void* out, const void* dout, int lddo, const float* lse, const int* cu_seqlens,
@@ -538,7 +538,8 @@ extern "C" int b200_attn_bwd_cp(const void* qkv_local, const void* kv_g, int wor
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const int W = (Hq + 2 * Hkv) * 128, kv_cols = 2 * Hkv * 128;
   if (cudaMemsetAsync(acc_local, 0, (size_t)T_loc * W * sizeof(float), stream) != cudaSuccess) return -3;
-  const size_t row_lo = (size_t)kv_tile_lo * 128, row_hi = (size_t)(rank + 1) * T_loc;
+  (void)kv_tile_lo;   // every row a peer may read back has to be defined, not only the rows this rank adds to
+  const size_t row_lo = 0, row_hi = (size_t)(rank + 1) * T_loc;
   if (cudaMemsetAsync(dkv_g + row_lo * kv_cols, 0, (row_hi - row_lo) * kv_cols * sizeof(float), stream) != cudaSuccess)
     return -3;
   int r = launch_delta(out, Hq * 128, dout, lddo, delta, T_loc, Hq, stream);

@@ -186,6 +186,29 @@ reshard_copy_kernel(const ReshardEntry* __restrict__ plan, PeerTable srcs, __nv_
   }
 }
 
+
+// Context-parallel attention backward, second half: every rank holds partial dK / dV sums for ALL rows of the packed
+// stream it attended to (dkv_g [T_total, cols] fp32). The owner of rows [rank*rows_per_rank, +rows_per_rank) pulls the
+// partials of the ranks >= its own (causal attention: earlier ranks never see its keys) over NVLink, adds them and
+// writes the sum into its local accumulator (row stride out_ld, first column out_col0). One pass, every byte crosses
+// the link once.
+__global__ void __launch_bounds__(256)
+cp_dkv_reduce_kernel(PeerTable parts, int world, int rank, int rows_per_rank, int cols, float* __restrict__ out,
+                     int out_ld, int out_col0) {
+  const int vec_per_row = cols >> 2;
+  const long long total = (long long)rows_per_rank * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row);
+    const size_t src = ((size_t)rank * rows_per_rank + r) * cols + (size_t)c * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int pr = rank; pr < world; ++pr) {
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(parts.ptr[pr]) + src);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)r * out_ld + out_col0 + c * 4) = acc;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -237,5 +260,13 @@ extern "C" int b200_reshard_copy(const void* plan_dev, int n_entries, const void
   dim3 grid(n_entries, 8);
   reshard_copy_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const ReshardEntry*>(plan_dev), make_table(src_ptrs, world), reinterpret_cast<__nv_bfloat16*>(dst));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_cp_dkv_reduce(const void* const* part_ptrs, int world, int rank, int rows_per_rank, int cols,
+                                  float* out, int out_ld, int out_col0, void* stream) {
+  if (world > MAX_PEERS || (cols & 3) || (out_ld & 3) || (out_col0 & 3)) return -10;
+  cp_dkv_reduce_kernel<<<148 * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_table(part_ptrs, world), world, rank, rows_per_rank, cols, out, out_ld, out_col0);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

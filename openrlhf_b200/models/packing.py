@@ -55,3 +55,41 @@ def pack_lists(seqs: list[torch.Tensor], device=None) -> PackedBatch:
     T = int(lens.max())
     idx = torch.cat([torch.arange(int(n)) + i * T for i, n in enumerate(lens)]).to(device)
     return PackedBatch(ids, labels, pos, cu.to(device), T, idx, len(seqs), T)
+
+
+def pack_lists_cp(seqs: list[torch.Tensor], world: int, pad_id: int = 0, device=None):
+    """Pack documents for context parallelism: every document is padded at its end to a multiple of 128 tokens (the
+    pad tokens attend to the document but nothing attends to them), and a trailing pad document rounds the stream up
+    to a multiple of 128*world rows, so that each rank's chunk is a whole number of 128-row tiles and no tile
+    straddles two ranks. Returns (PackedBatch over the global stream, valid [T] bool: real tokens).
+
+    The reference pads the packed stream to a multiple of the ring size and slices it per rank
+    (openrlhf/models/ring_attn_utils.py:101-141)."""
+    device = device or seqs[0].device
+    docs, valid = [], []
+    for s in seqs:
+        n = len(s)
+        padn = (-n) % 128
+        docs.append(torch.cat([s.to(device).long(), torch.full((padn,), pad_id, dtype=torch.long, device=device)]))
+        valid.append(torch.cat([torch.ones(n, dtype=torch.bool), torch.zeros(padn, dtype=torch.bool)]))
+    total = sum(len(d) for d in docs)
+    tail = (-total) % (128 * world)
+    if tail:
+        docs.append(torch.full((tail,), pad_id, dtype=torch.long, device=device))
+        valid.append(torch.zeros(tail, dtype=torch.bool))
+    pb = pack_lists(docs, device=device)
+    v = torch.cat(valid).to(device)
+    # the last real token of a document has no next token inside it
+    ends = torch.tensor([0] + [len(d) for d in docs]).cumsum(0)
+    for i, s in enumerate(seqs):
+        v[int(ends[i]) + len(s) - 1] = False
+    return pb, v
+
+
+def cp_slice(pb: PackedBatch, rank: int, world: int):
+    """This rank's rows of a batch packed by pack_lists_cp: (input_ids, labels, position_ids) of T/world rows each;
+    cu_seqlens stays global."""
+    T = pb.input_ids.numel()
+    assert T % (128 * world) == 0
+    lo, hi = rank * (T // world), (rank + 1) * (T // world)
+    return pb.input_ids[lo:hi], pb.labels[lo:hi], pb.position_ids[lo:hi].contiguous()

@@ -95,6 +95,7 @@ class TransformerLM(nn.Module):
             self._params[s.name] = p
             self.register_parameter(s.name.replace(".", "__"), p)
         self.gradient_checkpointing = False
+        self.cp = None   # parallel.cp.CPContext: attention over a context-parallel group (inputs are this rank's rows)
         self.lora = None                      # optional LoraAdapters (models/lora.py)
         self.max_pos = min(cfg.max_position_embeddings, 1 << 17)
         if seed is not None:
@@ -155,6 +156,9 @@ class TransformerLM(nn.Module):
             qn = F.rmsnorm(qk[:, :Hq].reshape(-1, D), self.p(pre + "q_norm.weight"), cfg.rms_norm_eps).view(T, Hq * D)
             kn = F.rmsnorm(qk[:, Hq:].reshape(-1, D), self.p(pre + "k_norm.weight"), cfg.rms_norm_eps).view(T, Hkv * D)
             qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * D:]], dim=1)
+        if self.cp is not None and attn_fn is None:
+            a = self.cp.attention(qkv, pos, self.rope(qkv.device), cu_seqlens, 1.0 / math.sqrt(D))
+            return self._lin(i, "o", a, None, h)
         if attn_fn is None and qkv.is_cuda and D == 128 and qkv.dtype == torch.bfloat16:
             from ..ops.attention import rope_attention
 

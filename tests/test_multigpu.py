@@ -27,3 +27,8 @@ def test_symm_optimizer_step_matches_nccl():
 def test_fused_tp_gemms():
     out = _run("tp_gemm.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "tp_gemm ok" in out
+
+
+def test_context_parallel_attention():
+    out = _run("cp_attention.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "CP_ATTENTION_OK" in out
