@@ -73,6 +73,12 @@ class Actor(nn.Module):
         if attention_mask is None:
             attention_mask = torch.ones_like(sequences)
         pb = pack_padded(sequences, attention_mask)
+        if context_parallel is None and ring_attn_group is not None and sequences.is_cuda:
+            if getattr(self, "_cp", None) is None or self._cp.group is not ring_attn_group:
+                from ..parallel.cp import ContextParallel
+
+                self._cp = ContextParallel(ring_attn_group)
+            context_parallel = self._cp
         logp_t, ent_t, aux = self.forward_packed(pb, return_entropy, context_parallel)
         log_probs = unpack_to_padded(logp_t, pb)[:, :-1]
         out = ActorOutput(aux_loss=aux)

@@ -173,3 +173,66 @@ class _CPAttn(torch.autograd.Function):
                                       ctypes.c_int(Hkv), _lib.stream_ptr())
         _lib.check_rc(rc, "attn_bwd_finalize")
         return dqkv, None, None, None, None, None, None
+
+
+class _GatherTokens(torch.autograd.Function):
+    """All-gather of a per-token vector across the context-parallel group. Every rank then computes the same loss on
+    the gathered vector, so the sum over ranks of the slice gradients (what an autograd-aware all-gather would
+    reduce-scatter; openrlhf/models/ring_attn_utils.py:177-181) is ``size`` times the local slice gradient."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        out = torch.empty(world * x.numel(), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        world, rank = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        n = g.numel() // world
+        return g[rank * n:(rank + 1) * n] * world, None
+
+
+class ContextParallel:
+    """Model-level glue: takes the packed batch every rank of the group holds, re-packs it with 128-aligned documents,
+    runs this rank's rows through the model with context-parallel attention and returns per-token results in the
+    original packed order (Actor.forward_packed calls forward_logprobs)."""
+
+    def __init__(self, group):
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._ctx: dict = {}
+
+    def _context(self, T_loc, cfg, device) -> CPContext:
+        key = (T_loc, cfg.num_attention_heads, cfg.num_key_value_heads)
+        c = self._ctx.get(key)
+        if c is None:
+            if len(self._ctx) >= 2:       # symmetric buffers are sized per chunk length: keep only recent shapes
+                self._ctx.clear()
+            c = CPContext(self.group, T_loc, cfg.num_attention_heads, cfg.num_key_value_heads, device)
+            self._ctx[key] = c
+        return c
+
+    def forward_logprobs(self, model, pb, temperature: float = 1.0, return_entropy: bool = False):
+        from ..models.packing import cp_slice, pack_lists_cp
+
+        cu = pb.cu_seqlens.tolist()
+        seqs = [pb.input_ids[a:b] for a, b in zip(cu[:-1], cu[1:])]
+        pb_cp, _ = pack_lists_cp(seqs, self.size, device=pb.input_ids.device)
+        ids, labels, pos = cp_slice(pb_cp, self.rank, self.size)
+        ctx = self._context(ids.numel(), model.cfg, ids.device)
+        model.cp = ctx
+        try:
+            h, aux = model(ids, pos, pb_cp.cu_seqlens, pb_cp.max_seqlen)
+        finally:
+            model.cp = None
+        logp, ent = model.logprobs(h, labels, temperature, return_entropy)
+        cu_cp = pb_cp.cu_seqlens.tolist()
+        idx = torch.cat([torch.arange(b - a) + c for a, b, c in zip(cu[:-1], cu[1:], cu_cp[:-1])]).to(ids.device)
+        logp = _GatherTokens.apply(logp, self.group)[idx]
+        if ent is not None:
+            ent = _GatherTokens.apply(ent, self.group)[idx]
+        return logp, ent, aux

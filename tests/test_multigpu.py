@@ -32,3 +32,8 @@ def test_fused_tp_gemms():
 def test_context_parallel_attention():
     out = _run("cp_attention.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "CP_ATTENTION_OK" in out
+
+
+def test_context_parallel_model():
+    out = _run("cp_model.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "CP_MODEL_OK" in out
