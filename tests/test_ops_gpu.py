@@ -254,3 +254,29 @@ def test_rope_attention_fused_matches_reference():
     ref.backward(g.float())
     _close(out, ref, rtol=3e-2, atol=3e-2)
     assert _rel_err(x.grad, xr.grad) < 2e-2, _rel_err(x.grad, xr.grad)
+
+
+@pytest.mark.parametrize("tp,src_world", [(1, 1), (2, 1), (2, 4)])
+def test_reshard_plan_kernel(tp, src_world):
+    """Weight-sync copy plan executed by the CUDA kernel (sources = local buffers standing in for peer shards)
+    against the PyTorch executor of the same plan."""
+    from openrlhf_b200.models.config import PRESETS
+    from openrlhf_b200.models.transformer import build_param_specs
+    from openrlhf_b200.parallel.reshard import ReshardPlan, build_plan, run_plan_reference
+    cfg = PRESETS["tiny-qwen2"]
+    specs = build_param_specs(cfg)
+    size = specs[-1].offset + (specs[-1].numel + 127) // 128 * 128
+    flat = torch.randn(size, device="cuda").to(torch.bfloat16)
+    shard, srcs = None, [flat]
+    if src_world > 1:
+        shard = (size + src_world * 256 - 1) // (src_world * 256) * 256
+        padded = torch.cat([flat, torch.zeros(shard * src_world - size, device="cuda", dtype=torch.bfloat16)])
+        srcs = [padded[r * shard:(r + 1) * shard].clone() for r in range(src_world)]
+    for tp_rank in range(tp):
+        entries, dsize = build_plan(cfg, tp_rank, tp, src_world, shard)
+        want = torch.zeros(dsize, dtype=torch.bfloat16)
+        run_plan_reference(entries, [s.cpu() for s in srcs], want)
+        got = torch.zeros(dsize, device="cuda", dtype=torch.bfloat16)
+        ReshardPlan(entries, "cuda").run([s.data_ptr() for s in srcs], got)
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu(), want)
