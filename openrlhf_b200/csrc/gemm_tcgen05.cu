@@ -10,6 +10,8 @@
 // which covers forward (Y = X W^T), dgrad (dX = dY W) and wgrad (dW = dY^T X) of a linear layer without
 // materialising a transpose. Replaces the cuBLAS calls behind nn.Linear in the reference
 // (openrlhf/models/actor.py:149-157 instantiates HF models whose projections are nn.Linear).
+#include <cstring>
+
 #include "ptx.cuh"
 
 namespace b200 {
@@ -35,6 +37,15 @@ struct GemmParams {
   int n_peer_c;         //   them with red.add over NVLink (row-parallel linear: GEMM + all-reduce in one kernel)
   int ag_world;         // >0: A is row-sharded over ag_world ranks (all-gather fused into the A-tile loads)
   int ag_rows;          //   rows held by each rank (multiple of 128)
+  // grouped (mixture-of-experts) extensions
+  int group_mode;            // 0 plain; 1: every 128-row M tile belongs to one group and multiplies that group's B
+                             // (rows of A / C sorted by group, each group padded to a multiple of 128 rows);
+                             // 2: one output matrix per group, K runs over that group's rows (weight gradients)
+  const int* tile_group;     // mode 1: [m tiles] group of each tile, < 0 = unused padding tile
+  int group_b_rows;          // mode 1: rows of the stacked B matrix per group (N if B is [G*N, K], K if B is [G*K, N])
+  const int* group_offsets;  // mode 2: [G+1] first row of each group in the K dimension (multiples of 64)
+  int n_groups;              // mode 2
+  long long group_c_stride;  // mode 2: elements between consecutive groups' outputs
 };
 
 // Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
@@ -73,7 +84,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int kb_total = (p.K + BK - 1) / BK;
   const int splits = p.k_splits > 1 ? p.k_splits : 1;
   const int kb_per_split = (kb_total + splits - 1) / splits;
-  const int num_tiles = m_blocks * n_blocks * splits;
+  const int num_tiles = m_blocks * n_blocks * splits * (p.group_mode == 2 ? p.n_groups : 1);
   constexpr int GROUP_M = 16;
 
   if (threadIdx.x == 0) {
@@ -98,7 +109,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   pdl_wait();                 // operands and C may be produced / still read by the previous kernel in the stream
   pdl_launch_dependents();    // the next kernel may run its prologue while this one works
 
-  auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& kb0, int& kb1, int& grp) {
+    grp = 0;
+    if (p.group_mode == 2) {             // one output per group; K range = that group's rows
+      const int per = m_blocks * n_blocks;
+      grp = tile / per;
+      const int t = tile % per;
+      m_blk = t % m_blocks;
+      n_blk = t / m_blocks;
+      kb0 = p.group_offsets[grp] / BK;
+      kb1 = p.group_offsets[grp + 1] / BK;
+      return;
+    }
     int split = tile % splits;
     int t = tile / splits;
     int per_group = GROUP_M * n_blocks;
@@ -110,6 +132,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     n_blk = r / gsz;
     kb0 = split * kb_per_split;
     kb1 = min(kb_total, kb0 + kb_per_split);
+    if (p.group_mode == 1) {
+      grp = p.tile_group[m_blk];
+      if (grp < 0) kb1 = kb0;            // padding tile: no work for any role
+    }
   };
 
   if (warp == 0) {
@@ -121,8 +147,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m_blk, n_blk, kb0, kb1;
-        tile_coords(tile, m_blk, n_blk, kb0, kb1);
+        int m_blk, n_blk, kb0, kb1, grp;
+        tile_coords(tile, m_blk, n_blk, kb0, kb1, grp);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -141,12 +167,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int c = 0; c < BM / 64; ++c)
               tma_load_2d(sa + c * (BK * 128), &tma_a, &full_bar[stage], m_blk * BM + c * 64, kb * BK);
           }
+          const int brow = p.group_mode == 1 ? grp * p.group_b_rows : 0;   // this group's block of the stacked B
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, n_blk * BN);
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, brow + n_blk * BN);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (BK * 128), &tma_b, &full_bar[stage], n_blk * BN + c * 64, kb * BK);
+              tma_load_2d(sb + c * (BK * 128), &tma_b, &full_bar[stage], n_blk * BN + c * 64, brow + kb * BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -161,8 +188,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        int m_blk, n_blk, kb0, kb1;
-        tile_coords(tile, m_blk, n_blk, kb0, kb1);
+        int m_blk, n_blk, kb0, kb1, grp;
+        tile_coords(tile, m_blk, n_blk, kb0, kb1, grp);
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
@@ -194,8 +221,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      int m_blk, n_blk, kb0, kb1;
-      tile_coords(tile, m_blk, n_blk, kb0, kb1);
+      int m_blk, n_blk, kb0, kb1, grp;
+      tile_coords(tile, m_blk, n_blk, kb0, kb1, grp);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -212,7 +239,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int col0 = n_blk * BN + c * 32;
         if (row_ok && has_work && col0 < p.N) {
           if (p.out_f32) {
-            float* crow = reinterpret_cast<float*>(p.C) + (size_t)(tile % splits) * p.split_stride +
+            float* crow = reinterpret_cast<float*>(p.C) +
+                          (p.group_mode == 2 ? (size_t)grp * p.group_c_stride : (size_t)(tile % splits) * p.split_stride) +
                           (size_t)row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -342,7 +370,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const PeerMaps& 
     configured = true;
   }
   int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
-  int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1);
+  int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1) * (p.group_mode == 2 ? p.n_groups : 1);
   int grid = tiles < sms ? tiles : sms;
   return launch_pdl(kern, dim3(grid), dim3(192), (size_t)L::TOTAL, stream, ta, tb, pa, p) == cudaSuccess ? 0 : -3;
 }
@@ -425,6 +453,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   else r = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, 64);
   if (r) return r;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.C = C;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -468,6 +497,7 @@ extern "C" int b200_gemm_bf16_tp(const void* A, const void* const* a_shards, con
   CUtensorMap ta, tb;
   PeerMaps pm = {};
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = nullptr;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.k_splits = 1; p.split_stride = 0; p.alpha = 1.f; p.status = status;
@@ -495,4 +525,58 @@ extern "C" int b200_gemm_bf16_tp(const void* A, const void* const* a_shards, con
   if (bn == 256) return launch<256, false, false>(ta, tb, pm, p, g_sm_count, stream);
   if (bn == 128) return launch<128, false, false>(ta, tb, pm, p, g_sm_count, stream);
   return launch<64, false, false>(ta, tb, pm, p, g_sm_count, stream);
+}
+
+
+// Grouped GEMMs for mixture-of-experts layers (rows sorted by expert, every expert padded to a multiple of 128 rows).
+//   mode 1: C[P, N] = A[P, K] * B_g^T, g = tile_group[row / 128]; B is the experts' weights stacked along rows:
+//           b_mn = 0: [G*N, K] (forward), b_mn = 1: [G*K, N] (input gradient; here "K" is the weight's output dim).
+//   mode 2: C_g[M, N] (+)= A[rows of g, M]^T * B[rows of g, N] (weight gradients; fp32 output, one matrix per group,
+//           group_offsets[G+1] = padded row offsets, multiples of 128).
+extern "C" int b200_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                      int ldc, int b_mn, int mode, const int* tile_group, int group_b_rows,
+                                      const int* group_offsets, int n_groups, long long group_c_stride, int accumulate,
+                                      int bn, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || n_groups <= 0) return 0;
+  if (mode != 1 && mode != 2) return -10;
+  const int out_f32 = mode == 2;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_f32 ? 4 : 8)) || (N % (out_f32 ? 4 : 8))) return -10;
+  if (mode == 1 && (M % 128)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -12;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (bn != 64 && bn != 128 && bn != 256) bn = N >= 1024 ? 256 : (N >= 512 ? 128 : 64);
+  CUtensorMap ta, tb;
+  int r;
+  const int a_mn = mode == 2;
+  if (mode == 2) b_mn = 1;
+  if (!a_mn) r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
+  else r = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, 64);
+  if (r) return r;
+  if (mode == 1) {
+    if (!b_mn) r = make_tmap_bf16_2d(&tb, B, (uint64_t)n_groups * group_b_rows, K, ldb, bn, BK);
+    else r = make_tmap_bf16_2d(&tb, B, (uint64_t)n_groups * group_b_rows, N, ldb, BK, 64);
+  } else {
+    r = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, 64);
+  }
+  if (r) return r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_f32 = out_f32; p.accumulate = out_f32 ? accumulate : 0;
+  p.k_splits = 1; p.alpha = 1.f; p.status = status;
+  p.group_mode = mode; p.tile_group = tile_group; p.group_b_rows = group_b_rows; p.group_offsets = group_offsets;
+  p.n_groups = n_groups; p.group_c_stride = group_c_stride;
+  static PeerMaps no_peers;
+#define B200_DISPATCH(BN_)                                                                            \
+  if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, no_peers, p, g_sm_count, stream);     \
+  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, no_peers, p, g_sm_count, stream);       \
+  return launch<BN_, true, true>(ta, tb, no_peers, p, g_sm_count, stream);
+  if (bn == 256) { B200_DISPATCH(256) }
+  if (bn == 128) { B200_DISPATCH(128) }
+  B200_DISPATCH(64)
+#undef B200_DISPATCH
 }

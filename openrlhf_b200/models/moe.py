@@ -7,6 +7,8 @@ each expert runs on its contiguous slice of rows, so expert GEMMs see dense [row
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import functional as F
@@ -66,11 +68,88 @@ def load_balancing_loss(probs: torch.Tensor, idx: torch.Tensor, num_experts: int
     return num_experts * (f * P).sum()
 
 
+class _GroupedLinear(torch.autograd.Function):
+    """y[rows of e] = x[rows of e] @ W[e].T for all experts in one grouped tcgen05 GEMM (rows sorted by expert, each
+    expert padded to a multiple of 128 rows). Backward: one grouped GEMM for the input gradient, one grouped
+    weight-gradient GEMM accumulating in fp32 into W.main_grad."""
+
+    @staticmethod
+    def forward(ctx, x, W, tile_group, offsets):
+        from ..ops.gemm import gemm_grouped_rows
+
+        ctx.save_for_backward(x, tile_group, offsets)
+        ctx.W = W
+        return gemm_grouped_rows(x, W.detach(), tile_group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm_grouped_rows, gemm_grouped_wgrad
+
+        x, tile_group, offsets = ctx.saved_tensors
+        W = ctx.W
+        dy = dy.contiguous()
+        dx = gemm_grouped_rows(dy, W.detach(), tile_group, b_mn=True)
+        mg = getattr(W, "main_grad", None)
+        if mg is not None:
+            gemm_grouped_wgrad(dy, x, offsets, mg, accumulate=True)
+            return dx, None, None, None
+        dW = torch.zeros(W.shape, dtype=torch.float32, device=W.device)
+        gemm_grouped_wgrad(dy, x, offsets, dW, accumulate=False)
+        return dx, dW.to(W.dtype), None, None
+
+
+def permute_plan(idx: torch.Tensor, num_experts: int):
+    """Device-side (no host synchronisation) plan that sorts the T*k routed rows by expert and pads every expert to a
+    multiple of 128 rows. Returns (tok [T*k] source token of each sorted row, dest [T*k] row in the padded buffer,
+    order [T*k] position in the flattened (token, slot) list, tile_group int32 [P/128], offsets int32 [E+1], P)."""
+    T, k = idx.shape
+    E = num_experts
+    flat_e = idx.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    sorted_e = flat_e[order]
+    counts = torch.bincount(flat_e, minlength=E)
+    padded = (counts + 127) // 128 * 128
+    ends = torch.cumsum(padded, 0)
+    starts = ends - padded
+    dense_starts = torch.cumsum(counts, 0) - counts
+    rank_in_e = torch.arange(T * k, device=idx.device) - dense_starts[sorted_e]
+    dest = starts[sorted_e] + rank_in_e
+    P = (T * k + E * 127 + 127) // 128 * 128          # static upper bound: no device->host read
+    tiles = torch.arange(P // 128, device=idx.device) * 128
+    tg = torch.searchsorted(ends, tiles, right=True)
+    tile_group = torch.where(tg < E, tg, torch.full_like(tg, -1)).to(torch.int32)
+    # a tile past the last used row of its expert cannot exist (experts are padded to whole tiles); tiles past the
+    # last expert's end are marked unused above
+    offsets = torch.cat([starts[:1] * 0, ends]).to(torch.int32)
+    return order // k, dest, order, tile_group, offsets, P
+
+
+def moe_forward_grouped(x, router_w, gate_up, down, top_k: int, norm_topk: bool):
+    """Grouped-GEMM MoE block (CUDA, bf16): router -> sort rows by expert -> gate_up -> SwiGLU -> down -> weighted
+    combine. Same results as moe_forward (the per-expert loop) up to bf16 rounding."""
+    T, H = x.shape
+    E = gate_up.shape[0]
+    w, idx, probs = router_topk(x, router_w, top_k, norm_topk)
+    aux = load_balancing_loss(probs, idx, E)
+    tok, dest, order, tile_group, offsets, P = permute_plan(idx, E)
+    xs = torch.zeros(P, H, dtype=x.dtype, device=x.device).index_copy(0, dest, x[tok])
+    gu = _GroupedLinear.apply(xs, gate_up, tile_group, offsets)
+    a = F.swiglu(gu)
+    ys = _GroupedLinear.apply(a, down, tile_group, offsets)
+    wk = w.reshape(-1)[order].to(ys.dtype)[:, None]
+    y = torch.zeros_like(x)
+    y.index_add_(0, tok, ys[dest] * wk)
+    return y, aux
+
+
 def moe_forward(x, router_w, gate_up, down, top_k: int, norm_topk: bool, expert_range: tuple[int, int] | None = None):
     """x [T,H] -> (y [T,H], aux_loss). `expert_range` restricts computation to local experts (expert parallelism:
     rows routed to other ranks are handled by the caller's dispatch/combine)."""
     T, H = x.shape
     E = gate_up.shape[0]
+    if (x.is_cuda and expert_range is None and x.dtype == torch.bfloat16 and H % 64 == 0
+            and gate_up.shape[1] % 128 == 0 and os.environ.get("OPENRLHF_B200_MOE_LOOP", "0") != "1"):
+        return moe_forward_grouped(x, router_w, gate_up, down, top_k, norm_topk)
     w, idx, probs = router_topk(x, router_w, top_k, norm_topk)
     aux = load_balancing_loss(probs, idx, E)
     flat_e = idx.reshape(-1)

@@ -114,3 +114,46 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, bias: torch.Tenso
                                        _lib.stream_ptr())
     _lib.check_rc(rc, "splitk_reduce")
     return out
+
+
+# ---------------------------------------------------------------------------------------------- grouped (MoE) GEMMs
+def gemm_grouped_rows(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, b_mn: bool = False,
+                      bn: int = 0) -> torch.Tensor:
+    """Rows of ``a`` [P, K] are sorted by group and every group is padded to a multiple of 128 rows; tile_group int32
+    [P/128] names the group of each 128-row tile (< 0: padding tile, left untouched in the output).
+
+    b_mn=False: ``w`` is [G, N, K]; out[rows of g] = a[rows of g] @ w[g].T        (expert forward)
+    b_mn=True : ``w`` is [G, K, N]; out[rows of g] = a[rows of g] @ w[g]          (expert input gradient)
+    """
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+    P, K = a.shape
+    G = w.shape[0]
+    N = w.shape[2] if b_mn else w.shape[1]
+    assert (w.shape[1] if b_mn else w.shape[2]) == K and P % 128 == 0 and tile_group.numel() == P // 128
+    out = torch.zeros(P, N, dtype=torch.bfloat16, device=a.device)
+    rc = _lib.lib().b200_gemm_bf16_grouped(
+        _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), ctypes.c_int(P), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(K),
+        ctypes.c_int(w.shape[2]), ctypes.c_int(N), ctypes.c_int(1 if b_mn else 0), ctypes.c_int(1), _lib.ptr(tile_group),
+        ctypes.c_int(w.shape[1]), None, ctypes.c_int(G), ctypes.c_longlong(0), ctypes.c_int(0), ctypes.c_int(bn),
+        _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gemm_grouped_rows")
+    return out
+
+
+def gemm_grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, group_offsets: torch.Tensor, out: torch.Tensor,
+                       accumulate: bool = True, bn: int = 0) -> torch.Tensor:
+    """out[g] (+)= dy[rows of g].T @ x[rows of g] for every group; dy [P, M], x [P, N] sorted / padded as above,
+    group_offsets int32 [G+1] padded row offsets, out fp32 [G, M, N]."""
+    assert dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and dy.is_contiguous() and x.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    P, M = dy.shape
+    N = x.shape[1]
+    G = out.shape[0]
+    assert out.shape[1] == M and out.shape[2] == N and group_offsets.numel() == G + 1
+    rc = _lib.lib().b200_gemm_bf16_grouped(
+        _lib.ptr(dy), _lib.ptr(x), _lib.ptr(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(P), ctypes.c_int(M),
+        ctypes.c_int(N), ctypes.c_int(N), ctypes.c_int(1), ctypes.c_int(2), None, ctypes.c_int(0),
+        _lib.ptr(group_offsets), ctypes.c_int(G), ctypes.c_longlong(M * N), ctypes.c_int(1 if accumulate else 0),
+        ctypes.c_int(bn), _lib.ptr(_lib.status_word(dy.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gemm_grouped_wgrad")
+    return out
