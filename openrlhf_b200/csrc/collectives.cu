@@ -12,6 +12,8 @@
 // (engine.backward / engine.step at openrlhf/utils/deepspeed/deepspeed.py:177-194) and the per-parameter
 // gather + broadcast weight sync of openrlhf/trainer/ray/ppo_actor.py:408-489.
 // No TMA is involved here: all remote traffic is plain ld/st/multimem issued by the consuming or producing thread.
+#include <algorithm>
+
 #include "ptx.cuh"
 
 namespace b200 {
@@ -209,6 +211,100 @@ cp_dkv_reduce_kernel(PeerTable parts, int world, int rank, int rows_per_rank, in
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- expert parallelism
+// Dispatch: routed row i = (token i / k, slot i % k) goes to row dest_row[i] of the receive buffer of rank
+// dest_rank[i] (peer stores, 16 bytes per lane), optionally scaled (backward of the weighted combine). One warp per row.
+__global__ void __launch_bounds__(256)
+ep_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest_rank,
+                  const int* __restrict__ dest_row, const float* __restrict__ scale, PeerTable bufs, int rows, int k,
+                  int H) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vec = H >> 3;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < rows; i += warps) {
+    const int r = dest_rank[i];
+    if (r < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.ptr[r]) + (size_t)dest_row[i] * H);
+    const float sc = scale != nullptr ? scale[i] : 1.f;
+    for (int c = lane; c < vec; c += 32) {
+      uint4 v = src[c];
+      if (scale != nullptr) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 f = __bfloat1622float2(h[q]);
+          h[q] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+      }
+      dst[c] = v;
+    }
+  }
+}
+
+// Combine: out[t] = sum_slot w[t,slot] * buf[dest_rank[t,slot]][dest_row[t,slot]] (peer loads, fp32 accumulation; the
+// pull makes the sum order fixed, so the result is deterministic). Optionally also keeps the pulled rows
+// (rows_out [T*k, H]) and, given dy [T, H], writes dots[t,slot] = <dy[t], row> (the gradient of the routing weight).
+__global__ void __launch_bounds__(256)
+ep_gather_kernel(PeerTable bufs, const int* __restrict__ dest_rank, const int* __restrict__ dest_row,
+                 const float* __restrict__ w, __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ rows_out,
+                 const __nv_bfloat16* __restrict__ dy, float* __restrict__ dots, int T, int k, int H) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int vec = H >> 3;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    for (int c = lane; c < vec; c += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < k; ++s) {
+        const int i = t * k + s;
+        const int r = dest_rank[i];
+        if (r < 0) continue;
+        const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.ptr[r]) +
+                                                       (size_t)dest_row[i] * H)[c];
+        if (rows_out != nullptr) reinterpret_cast<uint4*>(rows_out + (size_t)i * H)[c] = v;
+        const float ws = w != nullptr ? w[i] : 1.f;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 f = __bfloat1622float2(h[q]);
+          acc[2 * q] += ws * f.x;
+          acc[2 * q + 1] += ws * f.y;
+        }
+      }
+      if (out != nullptr) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(out + (size_t)t * H)[c] = o;
+      }
+    }
+    if (dots != nullptr) {
+      for (int s = 0; s < k; ++s) {
+        const int i = t * k + s;
+        const int r = dest_rank[i];
+        float d = 0.f;
+        if (r >= 0) {
+          const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(bufs.ptr[r]) + (size_t)dest_row[i] * H;
+          for (int c = lane; c < vec; c += 32) {
+            const uint4 a = reinterpret_cast<const uint4*>(row)[c];
+            const uint4 b = reinterpret_cast<const uint4*>(dy + (size_t)t * H)[c];
+            const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float2 fa = __bfloat1622float2(ha[q]), fb = __bfloat1622float2(hb[q]);
+              d += fa.x * fb.x + fa.y * fb.y;
+            }
+          }
+        }
+        d = warp_sum(d);
+        if (lane == 0) dots[i] = d;
+      }
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -268,5 +364,27 @@ extern "C" int b200_cp_dkv_reduce(const void* const* part_ptrs, int world, int r
   if (world > MAX_PEERS || (cols & 3) || (out_ld & 3) || (out_col0 & 3)) return -10;
   cp_dkv_reduce_kernel<<<148 * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       make_table(part_ptrs, world), world, rank, rows_per_rank, cols, out, out_ld, out_col0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_ep_scatter(const void* x, const int* dest_rank, const int* dest_row, const float* scale,
+                               const void* const* buf_ptrs, int world, int rows, int k, int H, void* stream) {
+  if (world > MAX_PEERS || (H & 7) || k < 1) return -10;
+  if (rows <= 0) return 0;
+  const int blocks = (int)std::min<long long>(((long long)rows * 32 + 255) / 256, 148 * 8);
+  ep_scatter_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), dest_rank, dest_row, scale, make_table(buf_ptrs, world), rows, k, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_ep_gather(const void* const* buf_ptrs, int world, const int* dest_rank, const int* dest_row,
+                              const float* w, void* out, void* rows_out, const void* dy, float* dots, int T, int k,
+                              int H, void* stream) {
+  if (world > MAX_PEERS || (H & 7) || k < 1) return -10;
+  if (T <= 0) return 0;
+  const int blocks = (int)std::min<long long>(((long long)T * 32 + 255) / 256, 148 * 8);
+  ep_gather_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_table(buf_ptrs, world), dest_rank, dest_row, w, reinterpret_cast<__nv_bfloat16*>(out),
+      reinterpret_cast<__nv_bfloat16*>(rows_out), reinterpret_cast<const __nv_bfloat16*>(dy), dots, T, k, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

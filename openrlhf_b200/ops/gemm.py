@@ -118,7 +118,7 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, splits: int, bias: torch.Tenso
 
 # ---------------------------------------------------------------------------------------------- grouped (MoE) GEMMs
 def gemm_grouped_rows(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, b_mn: bool = False,
-                      bn: int = 0) -> torch.Tensor:
+                      bn: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Rows of ``a`` [P, K] are sorted by group and every group is padded to a multiple of 128 rows; tile_group int32
     [P/128] names the group of each 128-row tile (< 0: padding tile, left untouched in the output).
 
@@ -130,7 +130,10 @@ def gemm_grouped_rows(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor
     G = w.shape[0]
     N = w.shape[2] if b_mn else w.shape[1]
     assert (w.shape[1] if b_mn else w.shape[2]) == K and P % 128 == 0 and tile_group.numel() == P // 128
-    out = torch.zeros(P, N, dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.zeros(P, N, dtype=torch.bfloat16, device=a.device)
+    else:
+        assert out.shape == (P, N) and out.is_contiguous() and out.dtype == torch.bfloat16
     rc = _lib.lib().b200_gemm_bf16_grouped(
         _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), ctypes.c_int(P), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(K),
         ctypes.c_int(w.shape[2]), ctypes.c_int(N), ctypes.c_int(1 if b_mn else 0), ctypes.c_int(1), _lib.ptr(tile_group),

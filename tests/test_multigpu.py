@@ -37,3 +37,8 @@ def test_context_parallel_attention():
 def test_context_parallel_model():
     out = _run("cp_model.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "CP_MODEL_OK" in out
+
+
+def test_expert_parallel_moe():
+    out = _run("ep_moe.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "EP_MOE_OK" in out
