@@ -48,6 +48,28 @@ class _ExpertLinear(torch.autograd.Function):
         return dx, dW.to(W.dtype), None
 
 
+class _ExpertSlice(torch.autograd.Function):
+    """W[lo:hi] as a tensor whose weight gradient lands in W.main_grad[lo:hi] (or in a dense zero-padded grad)."""
+
+    @staticmethod
+    def forward(ctx, W, lo, hi):
+        ctx.W, ctx.lo, ctx.hi = W, lo, hi
+        ctx.set_materialize_grads(False)
+        out = W.detach()[lo:hi]
+        mg = getattr(W, "main_grad", None)
+        if mg is not None:
+            out.main_grad = mg[lo:hi]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        if g is None or getattr(ctx.W, "main_grad", None) is not None:
+            return None, None, None
+        full = torch.zeros_like(ctx.W)
+        full[ctx.lo:ctx.hi] = g
+        return full, None, None
+
+
 def router_topk(x, router_w, top_k: int, norm_topk: bool):
     """Returns (weights [T,k] fp32, experts [T,k] int64, probs [T,E] fp32)."""
     logits = F.linear(x, router_w).float()
@@ -142,11 +164,20 @@ def moe_forward_grouped(x, router_w, gate_up, down, top_k: int, norm_topk: bool)
     return y, aux
 
 
-def moe_forward(x, router_w, gate_up, down, top_k: int, norm_topk: bool, expert_range: tuple[int, int] | None = None):
+def moe_forward(x, router_w, gate_up, down, top_k: int, norm_topk: bool, expert_range: tuple[int, int] | None = None,
+                ep=None):
     """x [T,H] -> (y [T,H], aux_loss). `expert_range` restricts computation to local experts (expert parallelism:
     rows routed to other ranks are handled by the caller's dispatch/combine)."""
     T, H = x.shape
     E = gate_up.shape[0]
+    if ep is not None and x.is_cuda:
+        # expert parallel: this rank computes only its slice of the experts; every rank still holds all expert
+        # weights (the slices other ranks own get zero gradient here and their values through the optimizer's
+        # parameter all-gather), so the ZeRO engine needs no expert-specific handling
+        w, idx, probs = router_topk(x, router_w, top_k, norm_topk)
+        aux = load_balancing_loss(probs, idx, E)
+        lo, hi = ep.rank * ep.E_loc, (ep.rank + 1) * ep.E_loc
+        return ep.moe(x, w, idx, _ExpertSlice.apply(gate_up, lo, hi), _ExpertSlice.apply(down, lo, hi)), aux
     if (x.is_cuda and expert_range is None and x.dtype == torch.bfloat16 and H % 64 == 0
             and gate_up.shape[1] % 128 == 0 and os.environ.get("OPENRLHF_B200_MOE_LOOP", "0") != "1"):
         return moe_forward_grouped(x, router_w, gate_up, down, top_k, norm_topk)

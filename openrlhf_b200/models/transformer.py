@@ -95,6 +95,7 @@ class TransformerLM(nn.Module):
             self._params[s.name] = p
             self.register_parameter(s.name.replace(".", "__"), p)
         self.gradient_checkpointing = False
+        self.ep = None   # parallel.ep.EPContext: MoE layers run expert-parallel over its group
         self.cp = None   # parallel.cp.CPContext: attention over a context-parallel group (inputs are this rank's rows)
         self.lora = None                      # optional LoraAdapters (models/lora.py)
         self.max_pos = min(cfg.max_position_embeddings, 1 << 17)
@@ -182,7 +183,7 @@ class TransformerLM(nn.Module):
             from .moe import moe_forward
 
             y, aux = moe_forward(x, self.p(pre + "router.weight"), self.p(pre + "experts.gate_up"),
-                                 self.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob)
+                                 self.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob, ep=self.ep)
             return h + y, aux
         gu = self._lin(i, "gate_up", x)
         a = F.swiglu(gu)

@@ -42,3 +42,8 @@ def test_context_parallel_model():
 def test_expert_parallel_moe():
     out = _run("ep_moe.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "EP_MOE_OK" in out
+
+
+def test_expert_parallel_model():
+    out = _run("ep_model.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "EP_MODEL_OK" in out
