@@ -182,10 +182,20 @@ class Strategy:
                 lm = _inner_lm(module)
                 sched = LRScheduler(cfg.get("lr", 1e-6), cfg.get("max_steps", 1000), cfg.get("lr_warmup_ratio", 0.03),
                                     cfg.get("min_lr_ratio", 0.1), cfg.get("lr_scheduler", "cosine_with_min_lr"))
-                eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
-                                 eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
-                                 max_norm=self.max_norm, zero_stage=self.stage, group=self.mesh.group("dp"),
-                                 scheduler=sched, use_symm=cfg.get("use_symm"))
+                if cfg.get("optim", "adam") == "muon":
+                    from ..parallel.muon import MuonEngine
+
+                    mu = cfg.get("muon") or {}
+                    eng = MuonEngine(lm, muon_lr=mu.get("lr", 0.02), momentum=mu.get("momentum", 0.95),
+                                     adam_lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
+                                     eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
+                                     max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched,
+                                     ns_steps=mu.get("ns_steps", 5), nesterov=mu.get("nesterov", True))
+                else:
+                    eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
+                                     eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
+                                     max_norm=self.max_norm, zero_stage=self.stage, group=self.mesh.group("dp"),
+                                     scheduler=sched, use_symm=cfg.get("use_symm"))
                 out.append(_Prepared(module, eng))
             else:
                 if arg is not None:
