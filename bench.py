@@ -109,7 +109,11 @@ def main():
     torch.cuda.set_device(local)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        import datetime
+
+        # a rank that fails must not leave the others waiting for NCCL's default 10 minutes
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"),
+                                timeout=datetime.timedelta(seconds=int(os.environ.get("BENCH_NCCL_TIMEOUT_S", "240"))))
     from openrlhf_b200.ops import _lib
     from openrlhf_b200.trainer.hybrid_engine import HybridRLWorker, default_rl_args
 
@@ -140,9 +144,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def note(msg):
+        if os.environ.get("BENCH_VERBOSE", "0") == "1":
+            print(f"[bench rank {rank}] {time.strftime('%H:%M:%S')} {msg}", file=sys.stderr, flush=True)
+
+    note("worker built")
     it = iter(host_prompts)
-    for _ in range(args.warmup):
+    for i in range(args.warmup):
         worker.rl_step(next(it))
+        note(f"warm-up step {i} done")
     # ---- device-timed region: prompts pre-staged on the device
     staged = [next(it).to(f"cuda:{local}") for _ in range(args.steps)]
     barrier()

@@ -80,6 +80,7 @@ def main():
     ap.add_argument("--hq", type=int, default=12)
     ap.add_argument("--hkv", type=int, default=2)
     ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--bn", type=int, default=0, help="GEMM tile width (0: heuristic)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--graph", type=int, default=0, help="time N back-to-back launches inside one CUDA graph")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed launches")
@@ -100,13 +101,13 @@ def main():
         A = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)
         B = torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16)
         if a.kernel == "gemm":
-            fn = lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn)
+            fn = lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn, bn=a.bn)
         else:
-            fn = lambda: gemm_splitk(A, B, a.splits)
+            fn = lambda: gemm_splitk(A, B, a.splits, bn=a.bn)
         t = _time(fn, a.iters)
         fl = 2.0 * M * N * K
         byt = 2.0 * (M * K + N * K + M * N)
-        print(f"{a.kernel} M{M} N{N} K{K} {a.layout}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+        print(f"{a.kernel} M{M} N{N} K{K} {a.layout} bn{a.bn} splits{a.splits}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
               f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak), {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
     elif a.kernel == "decode_attn":
         B_, Hq, Hkv, ctx = a.batch, a.hq, a.hkv, a.ctx

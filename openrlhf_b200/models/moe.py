@@ -70,9 +70,48 @@ class _ExpertSlice(torch.autograd.Function):
         return full, None, None
 
 
+class _RouteFn(torch.autograd.Function):
+    """Fused router kernel (softmax + top-k + renormalisation); the backward pass is a handful of [T, E] PyTorch ops."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, norm_topk):
+        import ctypes
+
+        from ..ops import _lib
+
+        T, E = logits.shape
+        logits = logits.contiguous()
+        probs = torch.empty_like(logits)
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        idx = torch.empty(T, top_k, dtype=torch.int64, device=logits.device)
+        rc = _lib.lib().b200_moe_route(_lib.ptr(logits), ctypes.c_int(T), ctypes.c_int(E), ctypes.c_int(top_k),
+                                       ctypes.c_int(int(norm_topk)), _lib.ptr(probs), _lib.ptr(w), _lib.ptr(idx), None,
+                                       None, _lib.stream_ptr())
+        _lib.check_rc(rc, "moe_route")
+        ctx.save_for_backward(probs, w, idx)
+        ctx.norm = norm_topk
+        ctx.mark_non_differentiable(idx)
+        return w, idx, probs
+
+    @staticmethod
+    def backward(ctx, dw, _didx, dprobs):
+        probs, w, idx = ctx.saved_tensors
+        g = dprobs.clone() if dprobs is not None else torch.zeros_like(probs)
+        if dw is not None:
+            if ctx.norm:
+                s = probs.gather(1, idx).sum(-1, keepdim=True)
+                dsel = (dw - (dw * w).sum(-1, keepdim=True)) / s
+            else:
+                dsel = dw
+            g.scatter_add_(1, idx, dsel)
+        return probs * (g - (g * probs).sum(-1, keepdim=True)), None, None
+
+
 def router_topk(x, router_w, top_k: int, norm_topk: bool):
     """Returns (weights [T,k] fp32, experts [T,k] int64, probs [T,E] fp32)."""
     logits = F.linear(x, router_w).float()
+    if logits.is_cuda and logits.shape[1] <= 256 and top_k <= 32:
+        return _RouteFn.apply(logits, top_k, norm_topk)
     probs = torch.softmax(logits, dim=-1)
     w, idx = probs.topk(top_k, dim=-1)
     if norm_topk:

@@ -56,7 +56,7 @@ class CPContext:
         self.flag_epoch = 0
         self.bar_epoch = 0
         self.parity = 0
-        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "20"))
+        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "60"))
         self._lo_cache: dict = {}
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)

@@ -53,7 +53,7 @@ class EPContext:
         self._hs = symm_mem.rendezvous(self.pad, self.group)
         self.pad_ptrs = _ptr_array(self._hs.buffer_ptrs)
         self.bar_epoch = 0
-        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "20"))
+        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "60"))
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 

@@ -59,7 +59,7 @@ class SymmBuffers:
             self.mc_param = int(self._hp.multicast_ptr)
             self.mc_grad = int(self._hg.multicast_ptr) if self._hg is not None else 0
         self.epoch = 0
-        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "20"))
+        self.wait_limit_s = float(os.environ.get("OPENRLHF_B200_WAIT_LIMIT_S", "60"))
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
@@ -80,6 +80,12 @@ class SymmBuffers:
         if getattr(eng, "_reduced", None) is None:
             eng._reduced = torch.empty(n, dtype=torch.float32, device=self.device)
         eng.scalars.zero_()
+        # ranks reach the optimizer step with whatever skew generation and the backward passes left them; a 4-byte NCCL
+        # all-reduce absorbs it (NCCL waits without a deadline of its own), so that the bounded device-side barrier
+        # below only ever sees microseconds of skew and its limit can stay a failure detector
+        if getattr(self, "_skew", None) is None:
+            self._skew = torch.zeros(1, dtype=torch.float32, device=self.device)
+        dist.all_reduce(self._skew, group=self.group)
         self.barrier(0)
         rc = L.b200_zero_reduce(self.grad_ptrs, ctypes.c_void_p(self.mc_grad), ctypes.c_int(self.world),
                                 ctypes.c_longlong(lo), ctypes.c_longlong(n), ctypes.c_float(1.0 / self.world),

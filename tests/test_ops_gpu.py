@@ -307,3 +307,25 @@ def test_moe_grouped_matches_expert_loop(T, H, I, E, k):
     assert abs(aux.item() - aux2.item()) < 1e-4
     for name, a, b in zip(("dx", "dgate_up", "ddown"), got, ref):
         assert rel(a, b) < 3e-2, (name, rel(a, b))
+
+
+@pytest.mark.parametrize("T,E,k,norm", [(257, 8, 2, True), (1000, 128, 8, True), (64, 60, 4, False)])
+def test_moe_router_kernel(T, E, k, norm):
+    """Fused router (softmax, top-k, renorm) and its backward against PyTorch fp32."""
+    from openrlhf_b200.models.moe import _RouteFn
+    torch.manual_seed(0)
+    logits = torch.randn(T, E, device="cuda", requires_grad=True)
+    w, idx, probs = _RouteFn.apply(logits, k, norm)
+    ref_l = logits.detach().clone().requires_grad_()
+    rp = torch.softmax(ref_l, -1)
+    rw, ridx = rp.topk(k, -1)
+    if norm:
+        rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    _close(probs, rp, rtol=1e-4, atol=1e-6)
+    _close(w.gather(1, idx.argsort(-1)), rw.gather(1, ridx.argsort(-1)), rtol=1e-4, atol=1e-6)
+    gw, gp = torch.randn_like(w), torch.randn_like(probs)
+    # same pairing of weights and upstream gradients on both sides: order by expert index
+    (w.gather(1, idx.argsort(-1)) * gw).sum().add((probs * gp).sum()).backward()
+    (rw.gather(1, ridx.argsort(-1)) * gw).sum().add((rp * gp).sum()).backward()
+    _close(logits.grad, ref_l.grad, rtol=1e-3, atol=1e-5)
