@@ -88,7 +88,12 @@ def save_pretrained(model: TransformerLM, path: str, tokenizer=None, extra_confi
                     rank: int = 0, world: int = 1, max_shard_bytes: int = MAX_SHARD_BYTES) -> None:
     """Write HF safetensors shards. With world > 1 every rank writes the shards whose index is congruent to its rank
     (all ranks hold the full bf16 parameters), rank 0 writes the index, config and tokenizer."""
-    from safetensors.torch import save_file
+    from ..utils.st_io import available as _native_st, save_file as _native_save
+
+    if _native_st():
+        save_file = _native_save          # parallel native writer, same file format
+    else:
+        from safetensors.torch import save_file
 
     os.makedirs(path, exist_ok=True)
     shards: list[list[tuple[str, torch.Tensor]]] = [[]]

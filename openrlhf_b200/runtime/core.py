@@ -131,8 +131,29 @@ def _heartbeat(conn, interval: float, stop: threading.Event):
             return
 
 
-def _worker_main(cls_spec, init_args, init_kwargs, env: dict, req, rep, hb, hb_interval: float):
+class _ViaRing:
+    """Pipe marker: the payload of this reply travels through the worker's shared-memory ring."""
+
+
+def _tensor_bytes(obj) -> int:
+    import torch
+
+    if isinstance(obj, torch.Tensor):
+        return obj.numel() * obj.element_size()
+    if isinstance(obj, dict):
+        return sum(_tensor_bytes(v) for v in obj.values())
+    if isinstance(obj, (list, tuple)):
+        return sum(_tensor_bytes(v) for v in obj)
+    return 0
+
+
+def _worker_main(cls_spec, init_args, init_kwargs, env: dict, req, rep, hb, hb_interval: float, ring_name=None):
     os.environ.update({k: str(v) for k, v in env.items()})
+    ring = None
+    if ring_name:
+        from .shm import ShmChannel
+
+        ring = ShmChannel.attach(ring_name)
     stop = threading.Event()
     threading.Thread(target=_heartbeat, args=(hb, hb_interval, stop), daemon=True).start()
     try:
@@ -149,6 +170,11 @@ def _worker_main(cls_spec, init_args, init_kwargs, env: dict, req, rep, hb, hb_i
     def reply(call_id, ok, payload):
         with send_lock:
             try:
+                # large tensor payloads go through the native shared-memory ring (one memcpy, no pickling of the
+                # bytes); the pipe only carries a marker, so ring messages and markers stay in the same order
+                if ring is not None and ok and 65536 <= _tensor_bytes(payload) < ring.capacity // 2:
+                    ring.send(payload, timeout=120.0)
+                    payload = _ViaRing()
                 rep.send((call_id, ok, payload))
             except (OSError, BrokenPipeError):
                 pass
@@ -205,8 +231,14 @@ class WorkerHandle:
     """Proxy of one worker process. ``handle.call("method", ...)`` returns a Future."""
 
     def __init__(self, cls_spec, args=(), kwargs=None, env: dict | None = None, heartbeat_interval: float = 1.0,
-                 heartbeat_timeout: float = 30.0, start_timeout: float = 600.0, name: str = "worker"):
+                 heartbeat_timeout: float = 30.0, start_timeout: float = 600.0, name: str = "worker",
+                 shm_bytes: int = 0):
         ctx = mp.get_context("spawn")
+        self._ring = None
+        if shm_bytes > 0:
+            from .shm import ShmChannel
+
+            self._ring = ShmChannel(capacity=shm_bytes)
         self._req_r, self._req_w = ctx.Pipe(duplex=False)
         self._rep_r, self._rep_w = ctx.Pipe(duplex=False)
         self._hb_r, self._hb_w = ctx.Pipe(duplex=False)
@@ -219,7 +251,7 @@ class WorkerHandle:
         self._dead: str | None = None
         self.proc = ctx.Process(target=_worker_main, daemon=True,
                                 args=(cls_spec, args, kwargs or {}, env or {}, self._req_r, self._rep_w, self._hb_w,
-                                      heartbeat_interval))
+                                      heartbeat_interval, self._ring.name if self._ring is not None else None))
         self.proc.start()
         self._started = Future()
         threading.Thread(target=self._pump, daemon=True).start()
@@ -237,6 +269,8 @@ class WorkerHandle:
                     self.last_heartbeat = self._hb_r.recv()
                 if self._rep_r.poll(0.05):
                     call_id, ok, payload = self._rep_r.recv()
+                    if isinstance(payload, _ViaRing):
+                        payload = self._ring.recv(timeout=120.0)
                     if call_id == -1:
                         self.last_heartbeat = time.time()
                         if ok:

@@ -77,7 +77,12 @@ def rotate(save_dir: str, tag: str | None, max_num: int = 3, max_mem: float = 10
 
 def save_sharded(engine, save_dir: str, tag: str, client_state: dict | None = None, save_latest: bool = True,
                  rank: int = 0, world: int = 1) -> str:
-    from safetensors.torch import save_file
+    from .st_io import available as _native_st, save_file as _native_save
+
+    if _native_st():
+        save_file = _native_save          # parallel native writer, same file format
+    else:
+        from safetensors.torch import save_file
 
     d = os.path.join(save_dir, tag)
     os.makedirs(d, exist_ok=True)

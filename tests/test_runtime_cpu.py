@@ -71,3 +71,25 @@ def test_failure_detection_exit_and_stall():
         assert h2.alive() and f.result(20) == "woke"
     finally:
         h2.shutdown()
+
+
+def test_large_reply_travels_through_shared_memory_ring():
+    """A worker created with shm_bytes > 0 returns big tensors through the native ring; small ones use the pipe."""
+    import torch
+    from openrlhf_b200.runtime.core import WorkerHandle
+    from openrlhf_b200.utils import st_io
+    if not st_io.available():
+        pytest.skip("native library not built")
+    h = WorkerHandle("openrlhf_b200.runtime.testing.EchoWorker", kwargs={"tag": "ring"}, shm_bytes=8 << 20)
+    try:
+        h.wait_started()
+        big = torch.randn(512, 1024)                      # 2 MiB reply
+        out = h.call("add", big, 2.0).result(60)
+        assert torch.equal(out, big + 2.0)
+        small = torch.ones(4)
+        assert torch.equal(h.call("add", small, 1.0).result(60), small + 1.0)
+        outs = [h.call("add", big, float(i)) for i in range(6)]   # several in flight: order of markers = order in the ring
+        for i, f in enumerate(outs):
+            assert torch.equal(f.result(60), big + float(i))
+    finally:
+        h.shutdown()
