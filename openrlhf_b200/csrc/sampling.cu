@@ -203,8 +203,7 @@ logprob_bwd_rows_kernel(__nv_bfloat16* __restrict__ logits, int T, int V, int ld
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(idx / nvec), v = (int)(idx % nvec);
-    long long y = labels[t];
-    y = y < 0 ? 0 : (y >= V ? V - 1 : y);
+    const long long y = labels[t];      // outside [0, V): no one-hot term in this row (vocabulary-parallel shards)
     __nv_bfloat16* row = logits + (size_t)t * ld;
     const float lse = lse_in[t];
     const float g = dlogp[t] * inv_t;

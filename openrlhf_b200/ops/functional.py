@@ -294,6 +294,118 @@ def fused_logprob(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, temper
     return _FusedLogprob.apply(h.contiguous(), w, labels.contiguous().long(), float(temperature), want_entropy, chunk)
 
 
+# ---------------------------------------------------------------------------------------------- vocabulary-parallel LM head
+def _vp_combine(stats: torch.Tensor):
+    """stats [n, T, 4] per vocabulary shard: (tempered lse, label logit / temperature or 0, untempered lse, untempered
+    E[z]). Returns (logp [T], entropy [T], global tempered lse [T])."""
+    lse_g = torch.logsumexp(stats[..., 0], dim=0)
+    logp = stats[..., 1].sum(0) - lse_g
+    lse1_g = torch.logsumexp(stats[..., 2], dim=0)
+    w = torch.exp(stats[..., 2] - lse1_g)
+    ent = lse1_g - (w * stats[..., 3]).sum(0)
+    return logp, ent, lse_g
+
+
+class _VocabParallelLogprob(torch.autograd.Function):
+    """Fused log-prob over an lm_head whose rows (vocabulary) are split across a group: every rank streams its own
+    V/n columns of the logits, 16 bytes of statistics per token and rank are exchanged, and the backward pass needs one
+    all-reduce of dh. No rank ever holds [T, V] logits."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, vocab_start, group, temperature, want_entropy, chunk):
+        import torch.distributed as dist
+
+        T, Vl = h.shape[0], w.shape[0]
+        lab = labels.long() - vocab_start
+        inr = (lab >= 0) & (lab < Vl)
+        stats = torch.zeros(T, 4, dtype=torch.float32, device=h.device)
+        if h.is_cuda:
+            logp = torch.empty(T, dtype=torch.float32, device=h.device)
+            lse = torch.empty_like(logp)
+            ent = torch.empty_like(logp)
+            lse1 = torch.empty_like(logp)
+            scratch = torch.empty_like(logp)
+            for s in range(0, T, chunk):
+                e = min(T, s + chunk)
+                logits = gemm(h[s:e], w)
+                args = (_lib.ptr(logits), _c_int(1), _c_int(e - s), _c_int(Vl), _c_int(logits.stride(0)), _lib.ptr(lab[s:e]))
+                _lib.check_rc(_L().b200_logprob_rows(*args, _c_f(temperature), _lib.ptr(logp[s:e]),
+                                                    _lib.ptr(ent[s:e]) if want_entropy else None, _lib.ptr(lse[s:e]),
+                                                    _lib.stream_ptr()), "logprob_rows")
+                if want_entropy:
+                    if temperature == 1.0:
+                        lse1[s:e] = lse[s:e]
+                    else:
+                        _lib.check_rc(_L().b200_logprob_rows(*args, _c_f(1.0), _lib.ptr(scratch[s:e]), None,
+                                                            _lib.ptr(lse1[s:e]), _lib.stream_ptr()), "logprob_rows")
+            stats[:, 0] = lse
+            stats[:, 1] = torch.where(inr, logp + lse, torch.zeros_like(logp))
+            if want_entropy:
+                stats[:, 2], stats[:, 3] = lse1, lse1 - ent
+        else:
+            z = h.float() @ w.float().t()
+            stats[:, 0] = torch.logsumexp(z / temperature, -1)
+            stats[:, 1] = torch.where(inr, z.gather(1, lab.clamp(0, Vl - 1)[:, None]).squeeze(1) / temperature,
+                                      torch.zeros(T))
+            stats[:, 2] = torch.logsumexp(z, -1)
+            stats[:, 3] = (torch.softmax(z, -1) * z).sum(-1)
+        n = dist.get_world_size(group)
+        allst = torch.empty(n * T, 4, dtype=torch.float32, device=h.device)
+        dist.all_gather_into_tensor(allst, stats, group=group)
+        logp_g, ent_g, lse_g = _vp_combine(allst.view(n, T, 4))
+        ctx.save_for_backward(h, w, lab, lse_g)
+        ctx.group, ctx.temperature, ctx.chunk, ctx.w_ref = group, temperature, chunk, w
+        if want_entropy:
+            ctx.mark_non_differentiable(ent_g)
+            return logp_g, ent_g
+        return logp_g, None
+
+    @staticmethod
+    def backward(ctx, dlogp, _dent):
+        import torch.distributed as dist
+
+        h, w, lab, lse_g = ctx.saved_tensors
+        T, Vl = h.shape[0], w.shape[0]
+        inv_t = 1.0 / ctx.temperature
+        dlogp = dlogp.float().contiguous()
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        if h.is_cuda:
+            dh = torch.empty_like(h)
+            dw_buf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            for s in range(0, T, ctx.chunk):
+                e = min(T, s + ctx.chunk)
+                logits = gemm(h[s:e], w)
+                rc = _L().b200_logprob_bwd_rows(_lib.ptr(logits), _c_int(e - s), _c_int(Vl), _c_int(logits.stride(0)),
+                                                _lib.ptr(lab[s:e]), _lib.ptr(lse_g[s:e]), _lib.ptr(dlogp[s:e]),
+                                                _c_f(inv_t), _lib.stream_ptr())
+                _lib.check_rc(rc, "logprob_bwd_rows")
+                gemm(logits, w, b_mn=True, out=dh[s:e])
+                gemm(logits, h[s:e], a_mn=True, b_mn=True, out=dw_buf, accumulate=True)
+            dw = None if mg is not None else dw_buf.to(w.dtype)
+        else:
+            z = h.float() @ w.float().t()
+            p = torch.exp(z * inv_t - lse_g[:, None])
+            onehot = torch.zeros_like(p)
+            inr = (lab >= 0) & (lab < Vl)
+            onehot[inr, lab[inr]] = 1.0
+            dz = dlogp[:, None] * inv_t * (onehot - p)
+            dh = (dz @ w.float()).to(h.dtype)
+            dw = (dz.t() @ h.float()).to(w.dtype)
+            if mg is not None:
+                mg.add_(dw.float())
+                dw = None
+        dist.all_reduce(dh, group=ctx.group)      # every vocabulary shard contributes to dh
+        return dh, dw, None, None, None, None, None, None
+
+
+def vocab_parallel_logprob(h: torch.Tensor, w_local: torch.Tensor, labels: torch.Tensor, vocab_start: int, group,
+                           temperature: float = 1.0, want_entropy: bool = False, chunk: int = 4096):
+    """fused_logprob with the lm_head rows [vocab_start, vocab_start + w_local.shape[0]) on this rank. All ranks of
+    `group` pass the same h and labels; returns the same (logp, entropy) on every rank."""
+    return _VocabParallelLogprob.apply(h.contiguous(), w_local, labels.contiguous(), int(vocab_start), group,
+                                       float(temperature), want_entropy, chunk)
+
+
 # ---------------------------------------------------------------------------------------------- value head
 def value_head(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """[T,H] x [1,H] -> [T] fp32 (tiny GEMV; fp32 accumulate)."""

@@ -47,3 +47,8 @@ def test_expert_parallel_moe():
 def test_expert_parallel_model():
     out = _run("ep_model.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "EP_MODEL_OK" in out
+
+
+def test_vocab_parallel_logprob():
+    out = _run("vocab_parallel.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "VOCAB_PARALLEL_OK" in out
