@@ -74,9 +74,12 @@ def _select(t: torch.Tensor, sel):
 
 
 def iter_hf_tensors(model: TransformerLM) -> Iterator[tuple[str, torch.Tensor]]:
+    z3 = getattr(model, "z3", None)
+    full = z3.gather_full() if z3 is not None else None     # ZeRO-3: parameters are sharded, gather the logical buffer
     for spec, p in model.named_specs():
+        t = p.detach() if full is None else full[spec.offset:spec.offset + spec.numel].view(spec.shape)
         for hf_name, sel in hf_names_for(model.cfg, spec.name):
-            yield hf_name, _select(p.detach(), sel)
+            yield hf_name, _select(t, sel)
 
 
 def hf_state_dict(model: TransformerLM) -> dict[str, torch.Tensor]:

@@ -203,12 +203,19 @@ class TransformerLM(nn.Module):
         Returns (hidden [T,H] after the final norm, aux_loss scalar: sum of the MoE load-balancing terms)."""
         h = F.embedding(input_ids, self.p("embed.weight"))
         aux_total = h.new_zeros((), dtype=torch.float32)
+        z3 = getattr(self, "z3", None)      # parallel.zero3.Zero3Engine: layer parameters live in two shared slots
         for i in range(self.cfg.num_hidden_layers):
+            if z3 is not None:
+                z3.before_layer_forward(i)
+                if h.requires_grad and torch.is_grad_enabled():
+                    h.register_hook(z3.post_backward_hook(i))      # fires once layer i's backward is complete
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
                 h, aux = torch.utils.checkpoint.checkpoint(self._layer, i, h, position_ids, cu_seqlens, max_seqlen,
                                                            attn_fn, use_reentrant=False)
             else:
                 h, aux = self._layer(i, h, position_ids, cu_seqlens, max_seqlen, attn_fn)
+            if z3 is not None and h.requires_grad and torch.is_grad_enabled():
+                h.register_hook(z3.pre_backward_hook(i))           # fires before layer i's backward starts
             aux_total = aux_total + aux
         h = F.rmsnorm(h, self.p("norm.weight"), self.cfg.rms_norm_eps)
         return h, aux_total

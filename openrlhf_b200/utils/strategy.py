@@ -191,6 +191,12 @@ class Strategy:
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
                                      max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched,
                                      ns_steps=mu.get("ns_steps", 5), nesterov=mu.get("nesterov", True))
+                elif self.stage == 3 and self.world_size > 1 and self.ring_attn_size == 1 and getattr(lm, "lora", None) is None:
+                    from ..parallel.zero3 import Zero3Engine
+
+                    eng = Zero3Engine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
+                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
+                                      max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched)
                 else:
                     eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),

@@ -52,3 +52,8 @@ def test_expert_parallel_model():
 def test_vocab_parallel_logprob():
     out = _run("vocab_parallel.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "VOCAB_PARALLEL_OK" in out
+
+
+def test_zero3_matches_zero2():
+    out = _run("zero3_vs_zero2.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "ZERO3_OK" in out
