@@ -40,9 +40,11 @@ def _round(n: int, m: int) -> int:
 class Zero3Engine:
     def __init__(self, model: TransformerLM, lr: float = 1e-6, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.0, max_norm: float = 1.0, group=None, scheduler: LRScheduler | None = None):
-        self.model, self.group = model, group
-        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
-        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.model = model
+        initialised = dist.is_available() and dist.is_initialized()
+        self.group = group if group is not None else (dist.group.WORLD if initialised else None)
+        self.world = dist.get_world_size(self.group) if initialised else 1
+        self.rank = dist.get_rank(self.group) if self.world > 1 else 0
         self.device = model.flat.device
         self.on_gpu = self.device.type == "cuda"
         self.lr, self.betas, self.eps, self.wd, self.max_norm, self.scheduler = lr, betas, eps, weight_decay, max_norm, scheduler
