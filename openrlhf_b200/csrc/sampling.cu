@@ -1,5 +1,5 @@
-// Token sampler for the rollout engine: temperature, top-k, top-p, Gumbel-max draw and the log-prob of the drawn
-// token under the processed distribution, one CTA per sequence, Philox streams keyed by (seed, sequence, step).
+// Token sampler for the rollout engine: temperature, top-k, top-p, an inverse-CDF draw (one Philox uniform per
+// (seed, sequence, step)) and the log-prob of the drawn token under the processed distribution, one CTA per sequence.
 // Stands in for vLLM's sampler as configured by the reference (SamplingParams with temperature / top_p / top_k and
 // logprobs of the sampled token: openrlhf/trainer/ppo_utils/samples_generator.py:203-211,
 // openrlhf/trainer/ray/vllm_engine.py:295-300 selects "processed_logprobs").
@@ -47,6 +47,32 @@ __device__ __forceinline__ float block_reduce_max(float v, float* red) {
   return t;
 }
 
+// e[k] = exp((z[j+k] - mx) * inv_t) if that value passes the keep threshold and j + k < end, else 0. j is a multiple
+// of 8; one 16-byte load when the row is bf16 and 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void load8_kept_exp(const T* z, int j, int end, float mx, float inv_t, float thr, bool vec,
+                                               float* e) {
+  float x[8];
+  if (vec && j + 8 <= end) {
+    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(z) + j);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = __bfloat1622float2(h[q]);
+      x[2 * q] = f.x;
+      x[2 * q + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x[k] = (j + k < end) ? load_logit(z, j + k) : -INFINITY;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float v = (x[k] - mx) * inv_t;
+    e[k] = (j + k < end && v >= thr) ? __expf(v) : 0.f;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restrict__ temperature, float temp_scalar,
@@ -65,7 +91,21 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restri
   const long long step = step_ptr ? *step_ptr : step_scalar;
 
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, load_logit(z, i));
+  if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(z) & 15) == 0) {
+    const int nvec = V >> 3;                       // 16-byte loads over the aligned part, scalar tail
+    for (int i = threadIdx.x; i < nvec; i += SAMPLE_THREADS) {
+      const uint4 u = reinterpret_cast<const uint4*>(z)[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        mx = fmaxf(mx, fmaxf(f.x, f.y));
+      }
+    }
+    for (int i = (nvec << 3) + threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, load_logit(z, i));
+  } else {
+    for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, load_logit(z, i));
+  }
   mx = block_reduce_max(mx, red);
 
   // threshold in x = (z - max) * inv_t space; keep x >= thr
@@ -108,8 +148,107 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restri
     thr = lo_u > 0.f ? __logf(lo_u) : -INFINITY;
   }
 
+  if (!greedy) {
+    // ---- inverse-CDF draw from the kept set: one uniform per (row, step). Warp w owns the contiguous vocabulary
+    // segment [w*S, (w+1)*S); pass 1 gives every warp's probability mass, thread 0 picks the warp that holds the
+    // target quantile, and that warp walks its segment once more with a running prefix sum.
+    __shared__ float s_wsum[SAMPLE_THREADS / 32];
+    __shared__ float s_resid, s_total;
+    __shared__ int s_warp;
+    constexpr int NW = SAMPLE_THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = ((V + NW - 1) / NW + 255) / 256 * 256;
+    const int seg0 = min(V, warp * S), seg1 = min(V, seg0 + S);
+    const bool vec = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+    float acc = 0.f;
+    for (int j = seg0 + lane * 8; j < seg1; j += 256) {
+      float e[8];
+      load8_kept_exp(z, j, seg1, mx, inv_t, thr, vec, e);
+      acc += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) s_wsum[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int w = 0; w < NW; ++w) total += s_wsum[w];
+      curandStatePhilox4_32_10_t rng;
+      curand_init(seed, (unsigned long long)row, (unsigned long long)step, &rng);
+      const float target = curand_uniform(&rng) * total;      // uniform in (0, 1]
+      int sel = -1, last = 0;
+      float pre = 0.f;
+      for (int w = 0; w < NW; ++w) {
+        if (s_wsum[w] > 0.f) {
+          last = w;
+          if (sel < 0 && pre + s_wsum[w] >= target) { sel = w; s_resid = target - pre; }
+        }
+        pre += s_wsum[w];
+      }
+      if (sel < 0) { sel = last; s_resid = s_wsum[last]; }     // rounding: the quantile fell past the last mass
+      s_warp = sel;
+      s_total = total;
+    }
+    __syncthreads();
+    if (warp == s_warp) {
+      float resid = s_resid;
+      int chosen = -1, last_kept = -1;
+      for (int j0 = seg0; j0 < seg1 && chosen < 0; j0 += 256) {
+        const int j = j0 + lane * 8;
+        float e[8];
+        if (j < seg1) {
+          load8_kept_exp(z, j, seg1, mx, inv_t, thr, vec, e);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) e[k] = 0.f;
+        }
+        int lk = -1;
+        float ls = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          ls += e[k];
+          if (e[k] > 0.f) lk = j + k;
+        }
+        float cum = ls;                                        // inclusive prefix over lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, cum, o);
+          if (lane >= o) cum += t;
+        }
+        const float tot = __shfl_sync(0xffffffffu, cum, 31);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lk = max(lk, __shfl_xor_sync(0xffffffffu, lk, o));
+        last_kept = max(last_kept, lk);
+        if (tot > 0.f && resid <= tot) {
+          const unsigned m = __ballot_sync(0xffffffffu, ls > 0.f && cum >= resid);
+          if (m != 0) {
+            const int src = __ffs(m) - 1;
+            int pick = -1;
+            if (lane == src) {
+              const float r = resid - (cum - ls);
+              float c = 0.f;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                c += e[k];
+                if (e[k] > 0.f) {
+                  if (pick < 0 || c - e[k] < r) pick = j + k;   // last kept element whose prefix starts below r
+                }
+              }
+            }
+            chosen = __shfl_sync(0xffffffffu, pick, src);
+          }
+        }
+        if (chosen < 0) resid -= tot;
+      }
+      if (chosen < 0) chosen = max(last_kept, 0);
+      if (lane == 0) {
+        out_tok[row] = chosen;
+        if (out_logp) out_logp[row] = (load_logit(z, chosen) - mx) * inv_t - __logf(s_total);
+      }
+    }
+    return;
+  }
+  // ---- greedy: arg-max of the logits; the reported log-prob is under temperature 1
   curandStatePhilox4_32_10_t rng;
-  if (!greedy) curand_init(seed, (unsigned long long)row * SAMPLE_THREADS + threadIdx.x, (unsigned long long)step * 256ull, &rng);
   float sum = 0.f, best = -INFINITY;
   int best_i = 0x7fffffff;
   float4 u4 = make_float4(0.5f, 0.5f, 0.5f, 0.5f);
@@ -224,6 +363,44 @@ logprob_bwd_rows_kernel(__nv_bfloat16* __restrict__ logits, int T, int V, int ld
   }
 }
 
+
+// One decode step's bookkeeping for all batch rows in one launch (replaces ~35 small elementwise launches per step):
+// append the sampled token and its log-prob, detect EOS / length stops, advance position and context length, and
+// compute the KV slot of the next token from the block table.
+__global__ void decode_advance_kernel(int B, const long long* __restrict__ next_tok, const float* __restrict__ next_lp,
+                                      long long* __restrict__ tok, int* __restrict__ pos, int* __restrict__ seq_lens,
+                                      int* __restrict__ slots, int* __restrict__ active, int* __restrict__ gen_count,
+                                      long long* __restrict__ out_tokens, float* __restrict__ out_logprobs, int out_ld,
+                                      const int* __restrict__ min_tok, const int* __restrict__ max_tok,
+                                      const unsigned char* __restrict__ ignore_eos, long long eos,
+                                      const int* __restrict__ block_table, int max_pages, int page_size,
+                                      long long* __restrict__ step_counter) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r == 0) *step_counter += 1;
+  if (r >= B) return;
+  const bool act = active[r] != 0;
+  int p = pos[r];
+  if (act) {
+    const long long nt = next_tok[r];
+    const int g = min(gen_count[r], out_ld - 1);
+    out_tokens[(size_t)r * out_ld + g] = nt;
+    out_logprobs[(size_t)r * out_ld + g] = next_lp[r];
+    const int gc = gen_count[r] + 1;
+    gen_count[r] = gc;
+    const bool hit_eos = nt == eos && !ignore_eos[r] && gc >= min_tok[r];
+    const bool still = !(hit_eos || gc >= max_tok[r]);
+    tok[r] = nt;
+    if (still) {
+      p += 1;
+      pos[r] = p;
+      seq_lens[r] += 1;
+    }
+    active[r] = still ? 1 : 0;
+  }
+  const int page = block_table[(size_t)r * max_pages + min(p / page_size, max_pages - 1)];
+  slots[r] = page * page_size + p % page_size;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -267,5 +444,17 @@ extern "C" int b200_logprob_bwd_rows(void* logits, int T, int V, int ld, const l
   if (blocks > 148 * 16) blocks = 148 * 16;
   logprob_bwd_rows_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       (__nv_bfloat16*)logits, T, V, ld, labels, lse, dlogp, inv_t);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_decode_advance(int B, const long long* next_tok, const float* next_lp, long long* tok, int* pos,
+                                   int* seq_lens, int* slots, int* active, int* gen_count, long long* out_tokens,
+                                   float* out_logprobs, int out_ld, const int* min_tok, const int* max_tok,
+                                   const void* ignore_eos, long long eos, const int* block_table, int max_pages,
+                                   int page_size, long long* step_counter, void* stream_) {
+  if (B <= 0) return 0;
+  decode_advance_kernel<<<(B + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      B, next_tok, next_lp, tok, pos, seq_lens, slots, active, gen_count, out_tokens, out_logprobs, out_ld, min_tok,
+      max_tok, reinterpret_cast<const unsigned char*>(ignore_eos), eos, block_table, max_pages, page_size, step_counter);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -348,6 +348,19 @@ class RolloutEngine:
         return gemm(x, m.lm_head_weight())
 
     def _advance(self, B: int):
+        """Per-step bookkeeping (append token / log-prob, stop conditions, next position and KV slot): one kernel."""
+        if self.tok.is_cuda:
+            import ctypes
+
+            rc = _lib.lib().b200_decode_advance(
+                ctypes.c_int(B), _lib.ptr(self.next_tok), _lib.ptr(self.next_lp), _lib.ptr(self.tok), _lib.ptr(self.pos),
+                _lib.ptr(self.seq_lens), _lib.ptr(self.slots), _lib.ptr(self.active), _lib.ptr(self.gen_count),
+                _lib.ptr(self.out_tokens), _lib.ptr(self.out_logprobs), ctypes.c_int(self.max_new_cap),
+                _lib.ptr(self.min_tok), _lib.ptr(self.max_tok), _lib.ptr(self.ignore_eos), ctypes.c_longlong(self.eos),
+                _lib.ptr(self.block_table), ctypes.c_int(self.max_pages), ctypes.c_int(PAGE),
+                _lib.ptr(self.step_counter), _lib.stream_ptr())
+            _lib.check_rc(rc, "decode_advance")
+            return
         act = self.active[:B].bool()
         g = self.gen_count[:B].long().clamp_max(self.max_new_cap - 1)
         rows = torch.arange(B, device=self.device)

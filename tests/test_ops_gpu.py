@@ -147,6 +147,26 @@ def test_sampler_greedy_and_distribution():
     assert int(tok.max()) == 0
 
 
+def test_sampler_large_vocab_distribution():
+    """Inverse-CDF draw over a bf16 vocabulary that spans all warp segments: bucketed frequencies follow softmax."""
+    from openrlhf_b200.ops.sampling import sample
+    torch.manual_seed(1)
+    V, R = 20011, 16384
+    row = (torch.randn(V, device="cuda") * 2.0).to(torch.bfloat16)
+    z = row[None, :].repeat(R, 1)
+    tok, lp = sample(z, temperature=0.8, seed=11, step=3)
+    p = torch.softmax(row.float() / 0.8, -1)
+    _close(lp, torch.log(p)[tok], atol=2e-3)
+    buckets = (torch.arange(V, device="cuda") * 16 // V)           # 16 contiguous index ranges (cross warp segments)
+    want = torch.zeros(16, device="cuda").index_add_(0, buckets, p)
+    got = torch.bincount(buckets[tok], minlength=16).float() / R
+    assert (got - want).abs().max().item() < 0.02, (got - want).abs().max().item()
+    # different steps give different draws, same (seed, step) the same draw
+    t2, _ = sample(z, temperature=0.8, seed=11, step=3)
+    t3, _ = sample(z, temperature=0.8, seed=11, step=4)
+    assert torch.equal(tok, t2) and not torch.equal(tok, t3)
+
+
 def test_rl_kernels_match_reference():
     from openrlhf_b200.ops import rl as K
     torch.manual_seed(0)
