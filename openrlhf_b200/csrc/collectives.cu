@@ -60,6 +60,39 @@ __global__ void symm_barrier_kernel(PeerTable pads, int rank, int world, int cha
   __syncthreads();
 }
 
+// The same barrier for use inside CUDA graphs: the epoch is not a launch argument (which a replay could not change)
+// but a device-side counter this kernel advances itself. Every rank replays the same graphs in lockstep, so the
+// counters stay equal.
+__global__ void symm_barrier_dev_kernel(PeerTable pads, int rank, int world, int channel, unsigned int* epoch_counter,
+                                        unsigned long long wait_limit_ns, int* status) {
+  __shared__ unsigned int s_epoch;
+  const int t = threadIdx.x;
+  if (t == 0) {
+    s_epoch = *epoch_counter + 1;
+    *epoch_counter = s_epoch;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  __threadfence_system();
+  if (t < world) {
+    unsigned int* remote = reinterpret_cast<unsigned int*>(pads.ptr[t]) + channel * MAX_PEERS + rank;
+    st_release_sys(remote, epoch);
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pads.ptr[rank]) + channel * MAX_PEERS + t;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      const unsigned int v = ld_acquire_sys(mine);
+      if ((int)(v - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > wait_limit_ns) {
+        atomicCAS(status, 0, ERR_TIMEOUT_FLAG);
+        atomicExch(status + 1, t);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+}
+
 // reduced[i] = scale * sum_r grad_r[lo + i]; scalars[0] += sum reduced^2. n is a multiple of 4.
 __global__ void __launch_bounds__(256)
 zero_reduce_kernel(PeerTable grads, int world, long long lo, long long n, float scale, float* __restrict__ reduced,
@@ -386,5 +419,13 @@ extern "C" int b200_ep_gather(const void* const* buf_ptrs, int world, const int*
   ep_gather_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       make_table(buf_ptrs, world), dest_rank, dest_row, w, reinterpret_cast<__nv_bfloat16*>(out),
       reinterpret_cast<__nv_bfloat16*>(rows_out), reinterpret_cast<const __nv_bfloat16*>(dy), dots, T, k, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_symm_barrier_dev(const void* const* pad_ptrs, int rank, int world, int channel,
+                                     unsigned int* epoch_counter, double wait_limit_s, int* status, void* stream) {
+  if (world > MAX_PEERS || channel < 0 || channel >= 8) return -10;
+  symm_barrier_dev_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_table(pad_ptrs, world), rank, world, channel, epoch_counter, (unsigned long long)(wait_limit_s * 1e9), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -454,6 +454,61 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long
   }
 }
 
+// Tensor-parallel version of the kernel above: the row-parallel projection (o_proj / down_proj) of every TP rank left
+// its split-K slabs in a symmetric workspace; each rank reads ALL ranks' slabs (peer loads, fixed order rank 0..n-1, so
+// every rank gets bit-identical sums), adds the residual and runs the next RMSNorm. The all-reduce of the row-parallel
+// linear is thereby part of the reduction the decode loop performs anyway.
+struct WsTable {
+  const float* p[8];
+};
+__global__ void __launch_bounds__(NORM_THREADS)
+tp_reduce_rmsnorm_kernel(WsTable ws, int world, int splits, long long slab, const __nv_bfloat16* __restrict__ residual,
+                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
+                         __nv_bfloat16* __restrict__ x_out, int M, int N, float eps) {
+  extern __shared__ uint4 row_cache[];
+  __shared__ float red[32];
+  const int nvec = N >> 3;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      for (int r = 0; r < world; ++r) {
+        for (int s = 0; s < splits; ++s) {
+          const float4* bs = reinterpret_cast<const float4*>(ws.p[r] + (size_t)s * slab + (size_t)row * N) + 2 * v;
+          const float4 c = bs[0], d = bs[1];
+          a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+          b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+        }
+      }
+      float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      if (residual != nullptr) {
+        float g[8];
+        unpack8(reinterpret_cast<const uint4*>(residual + (size_t)row * N)[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i]);
+      const uint4 u = pack8(f);
+      reinterpret_cast<uint4*>(h_out + (size_t)row * N)[v] = u;
+      row_cache[v] = u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = block_sum<NORM_THREADS>(ss, red);
+    const float rstd = rsqrtf(ss / (float)N + eps);
+    for (int v = threadIdx.x; v < nvec; v += NORM_THREADS) {
+      float f[8], g[8];
+      unpack8(row_cache[v], f);
+      unpack8(reinterpret_cast<const uint4*>(w)[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i] * rstd) * g[i];
+      reinterpret_cast<uint4*>(x_out + (size_t)row * N)[v] = pack8(f);
+    }
+    __syncthreads();
+  }
+}
+
 // Finishes the split-K qkv projection (sum of slabs + bias), applies RoPE to q and k, writes q compactly and k, v
 // into the paged KV cache. head_dim 128.
 __global__ void rope_kvwrite_splitk_kernel(const float* __restrict__ ws, int splits, long long slab,
@@ -533,4 +588,17 @@ extern "C" int b200_rope_kvwrite_splitk(const float* ws, int splits, const void*
                     ws, splits, (long long)T * (Hq + 2 * Hkv) * 128, (const __nv_bfloat16*)bias, pos, slots,
                     (const float2*)cos_sin, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T,
                     Hq, Hkv, max_pos) == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_tp_reduce_rmsnorm(const void* const* ws_ptrs, int world, int splits, const void* residual,
+                                      const void* w, void* h_out, void* x_out, int M, int N, float eps, void* stream) {
+  if (M <= 0) return 0;
+  if (N % 8 || N > 16384 || world < 1 || world > 8) return -10;
+  WsTable t;
+  for (int i = 0; i < 8; ++i) t.p[i] = i < world ? reinterpret_cast<const float*>(ws_ptrs[i]) : nullptr;
+  int grid = M < 148 * 8 ? M : 148 * 8;
+  tp_reduce_rmsnorm_kernel<<<grid, NORM_THREADS, (size_t)(N / 8) * sizeof(uint4), STREAM(stream)>>>(
+      t, world, splits, (long long)M * N, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, M, N, eps);
+  return LAUNCH_OK();
 }

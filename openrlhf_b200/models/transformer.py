@@ -95,6 +95,7 @@ class TransformerLM(nn.Module):
             self._params[s.name] = p
             self.register_parameter(s.name.replace(".", "__"), p)
         self.gradient_checkpointing = False
+        self.tp_group = None   # set on a tensor-parallel shard of the model (rollout/tp_engine.py)
         self.ep = None   # parallel.ep.EPContext: MoE layers run expert-parallel over its group
         self.cp = None   # parallel.cp.CPContext: attention over a context-parallel group (inputs are this rank's rows)
         self.lora = None                      # optional LoraAdapters (models/lora.py)
@@ -138,6 +139,14 @@ class TransformerLM(nn.Module):
     # ------------------------------------------------------------------ forward
     def _lin(self, i: int, target: str, x, bias=None, residual=None):
         """Projection `target` of layer i, plus its low-rank adapter when adapters are attached."""
+        if self.tp_group is not None and target in ("o", "down"):
+            # row-parallel shard (rollout engine with tensor parallelism, prefill path): partial product, sum over the
+            # TP group, then the residual once
+            import torch.distributed as dist
+
+            y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, None)
+            dist.all_reduce(y, group=self.tp_group)
+            return y if residual is None else y + residual
         y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, residual)
         if self.lora is not None:
             d = self.lora.delta(i, target, x)

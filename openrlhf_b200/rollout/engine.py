@@ -85,9 +85,10 @@ class _Row:
 class RolloutEngine:
     def __init__(self, model: TransformerLM, max_num_seqs: int = 256, max_model_len: int = 4096,
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
-                 eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16):
+                 eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None):
         assert model.cfg.head_dim == 128, "the decode attention kernel is specialised for head_dim 128"
         self.model = model
+        self.tp = tp          # rollout.tp_engine.TPDecode: `model` then holds this rank's tensor-parallel shard
         self.cfg: ModelConfig = model.cfg
         self.device = model.flat.device
         self.max_num_seqs = max_num_seqs
@@ -205,6 +206,9 @@ class RolloutEngine:
     @torch.no_grad()
     def update_weights(self, flat_src: torch.Tensor):
         """Copy a new set of weights (same flat layout) into the engine's buffer; a no-op when they alias."""
+        if self.tp is not None:
+            self.tp.load_shard(flat_src, self.model.flat)      # one planned copy kernel: full layout -> this TP shard
+            return
         if flat_src.data_ptr() != self.model.flat.data_ptr():
             self.model.flat.copy_(flat_src, non_blocking=True)
 
@@ -254,6 +258,7 @@ class RolloutEngine:
         """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
         cfg, m = self.cfg, self.model
         fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None
+        assert fused or self.tp is None, "tensor-parallel rollout covers the dense fused decode path"
         if fused:
             logits = self._decode_layers_fused(B)
         else:
@@ -278,9 +283,19 @@ class RolloutEngine:
         st = _lib.stream_ptr
         i32, f32 = ctypes.c_int, ctypes.c_float
 
-        def reduce_norm(ws, splits, residual, w):
+        tp = self.tp
+
+        def reduce_norm(ws, splits, residual, w, which=0):
             h = torch.empty(B, H, dtype=torch.bfloat16, device=self.device)
             x = torch.empty_like(h)
+            if tp is not None:
+                # row-parallel projection: all ranks' slabs are summed here (the all-reduce rides on the reduction)
+                tp.barrier()
+                rc = L.b200_tp_reduce_rmsnorm(tp.ws_ptrs[which], i32(tp.size), i32(splits), _lib.ptr(residual),
+                                              _lib.ptr(w), _lib.ptr(h), _lib.ptr(x), i32(B), i32(H),
+                                              f32(cfg.rms_norm_eps), st())
+                _lib.check_rc(rc, "tp_reduce_rmsnorm")
+                return h, x
             rc = L.b200_splitk_reduce_rmsnorm(_lib.ptr(ws), i32(splits), _lib.ptr(residual), _lib.ptr(w), _lib.ptr(h),
                                               _lib.ptr(x), i32(B), i32(H), f32(cfg.rms_norm_eps), st())
             _lib.check_rc(rc, "splitk_reduce_rmsnorm")
@@ -298,13 +313,14 @@ class RolloutEngine:
                                             i32(table.shape[0]), st())
             _lib.check_rc(rc, "rope_kvwrite_splitk")
             paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
-            ws, s = gemm_to_workspace(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"))
-            h, x = reduce_norm(ws, s, h, m.p(pre + "norm2.weight"))
+            ws, s = gemm_to_workspace(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"),
+                                      tp.ws[0] if tp is not None else None)
+            h, x = reduce_norm(ws, s, h, m.p(pre + "norm2.weight"), 0)
             gu = gemm(x, m.p(pre + "gate_up.weight"), bn=128)
             a = F.swiglu(gu)
-            ws, s = gemm_to_workspace(a, m.p(pre + "down.weight"))
+            ws, s = gemm_to_workspace(a, m.p(pre + "down.weight"), tp.ws[1] if tp is not None else None)
             nxt = m.p(f"layers.{i + 1}.norm1.weight") if i + 1 < nl else m.p("norm.weight")
-            h, x = reduce_norm(ws, s, h, nxt)
+            h, x = reduce_norm(ws, s, h, nxt, 1)
         return gemm(x, m.lm_head_weight())
 
     def _decode_layers_generic(self, B: int):
@@ -603,9 +619,9 @@ class RolloutEngine:
 
 
 # ---------------------------------------------------------------------------------------------- decode GEMM
-def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor):
+def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor, ws: torch.Tensor | None = None):
     """Split-K projection for small M whose fp32 slabs stay in the shared workspace for the next kernel to reduce.
-    Returns (workspace, number of slabs)."""
+    Returns (workspace, number of slabs). `ws`: use this buffer (a symmetric one under tensor parallelism)."""
     from ..ops.gemm import splitk_workspace
 
     M, K = x.shape
@@ -616,7 +632,9 @@ def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor):
     splits = max(1, min(148 // max(tiles, 1), kb // 4))
     per = (kb + splits - 1) // splits
     splits = (kb + per - 1) // per
-    ws = splitk_workspace(x.device, splits * M * N)
+    if ws is None:
+        ws = splitk_workspace(x.device, splits * M * N)
+    assert ws.numel() >= splits * M * N
     gemm(x, w, out=ws, k_splits=splits, split_stride=M * N, bn=bn)
     return ws, splits
 

@@ -57,3 +57,8 @@ def test_vocab_parallel_logprob():
 def test_zero3_matches_zero2():
     out = _run("zero3_vs_zero2.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "ZERO3_OK" in out
+
+
+def test_tensor_parallel_rollout_engine():
+    out = _run("tp_rollout.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "TP_ROLLOUT_OK" in out
