@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--max-new", type=int, default=2048)
     ap.add_argument("--micro", type=int, default=4)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--rollout-tp", type=int, default=1, help="tensor-parallel size of the rollout engines (N > 1)")
     return ap.parse_args()
 
 
@@ -124,6 +125,10 @@ def main():
         "algo.advantage.estimator": "reinforce_baseline", "algo.kl.init_coef": 0.0, "ds.zero_stage": 2,
     })
     rl_args.rollout.ignore_eos = True
+    if args.rollout_tp > 1:
+        from types import SimpleNamespace
+
+        rl_args.vllm = SimpleNamespace(tensor_parallel_size=args.rollout_tp)
 
     def rule_reward(exps):
         # (sum of response token ids) mod 7 == 0
@@ -200,7 +205,7 @@ def main():
             "config": {"model": args.model, "global_batch": P * n * world, "seq_len": L + new,
                        "prompts_per_gpu": P, "prompt_len": L, "n_samples_per_prompt": n, "max_new_tokens": new,
                        "estimator": "reinforce_baseline", "zero_stage": 2, "micro_batch": args.micro,
-                       "parallelism": f"dp{world}", "optimizer_step": ("peer-memory kernels" if worker.symm is not None else ("nccl" if world > 1 else "local")), "l2": "working set (3 GB weights + KV cache) is larger than L2"},
+                       "parallelism": f"dp{world}" + (f", rollout tp{args.rollout_tp}" if args.rollout_tp > 1 else ""), "optimizer_step": ("peer-memory kernels" if worker.symm is not None else ("nccl" if world > 1 else "local")), "l2": "working set (3 GB weights + KV cache) is larger than L2"},
             "clocks": clocks,
             "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": P * L * 8,
                     "d2h_bytes_per_step": d2h // args.steps},

@@ -110,8 +110,28 @@ class HybridRLWorker:
         self.reward_model = None
         self.reward_fn = reward_fn
         self.kl_ctl = FixedKLController(a.algo.kl.init_coef)
-        self.rollout = RolloutEngine(self.model, max_num_seqs=max_num_seqs, max_model_len=a.data.max_len,
-                                     num_pages=num_pages, seed=seed + 1000 * self.rank, use_cuda_graph=use_cuda_graph)
+        self.rollout_tp = int(getattr(getattr(a, "vllm", None), "tensor_parallel_size", 1) or 1)
+        self.tp_group = None
+        if self.rollout_tp > 1 and self.world > 1:
+            # consecutive ranks form one tensor-parallel rollout engine: same requests on every member, weights sliced
+            # from this rank's full trainer buffer by the weight-sync copy plan at every sync
+            from ..rollout.tp_engine import make_tp_engine
+
+            assert self.world % self.rollout_tp == 0
+            for k in range(self.world // self.rollout_tp):
+                ranks = list(range(k * self.rollout_tp, (k + 1) * self.rollout_tp))
+                g_ = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.tp_group = g_
+            self.rollout = make_tp_engine(self.cfg, self.model.flat, self.tp_group,
+                                          max_num_seqs=max_num_seqs * self.rollout_tp, max_model_len=a.data.max_len,
+                                          num_pages=(num_pages * self.rollout_tp) if num_pages else None,
+                                          seed=seed + 1000 * (self.rank // self.rollout_tp),
+                                          use_cuda_graph=use_cuda_graph)
+        else:
+            self.rollout = RolloutEngine(self.model, max_num_seqs=max_num_seqs, max_model_len=a.data.max_len,
+                                         num_pages=num_pages, seed=seed + 1000 * self.rank,
+                                         use_cuda_graph=use_cuda_graph)
         self.timing: dict[str, float] = {}
         self.global_step = 0
 
@@ -124,7 +144,15 @@ class HybridRLWorker:
         sp = SamplingParams(temperature=a.rollout.temperature, top_p=a.rollout.top_p, top_k=-1,
                             max_tokens=a.rollout.max_new_tokens, min_tokens=1, n=n, logprobs=1,
                             ignore_eos=getattr(a.rollout, "ignore_eos", False))
-        outs = self.rollout.generate(prompts, sp)
+        if self.tp_group is not None:
+            # every member of the TP engine generates for the union of the members' prompts and keeps its own share
+            gathered = [None] * self.rollout_tp
+            dist.all_gather_object(gathered, [list(map(int, p)) for p in prompts], group=self.tp_group)
+            me = dist.get_rank(self.tp_group)
+            start = sum(len(g_) for g_ in gathered[:me])
+            outs = self.rollout.generate([p for g_ in gathered for p in g_], sp)[start:start + len(prompts)]
+        else:
+            outs = self.rollout.generate(prompts, sp)
         exps = []
         dev = self.device
         for pi, ro in enumerate(outs):
