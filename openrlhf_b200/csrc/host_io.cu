@@ -138,6 +138,7 @@ struct Ring {
 constexpr uint64_t RING_MAGIC = 0x62323030726e6731ull;
 
 void ring_copy_in(Ring* r, uint64_t pos, const char* src, uint64_t n) {
+  if (n == 0) return;   // an empty part may come with a null pointer
   const uint64_t cap = r->h->capacity, o = pos % cap;
   const uint64_t first = std::min(n, cap - o);
   memcpy(r->data + o, src, first);
@@ -145,6 +146,7 @@ void ring_copy_in(Ring* r, uint64_t pos, const char* src, uint64_t n) {
 }
 
 void ring_copy_out(Ring* r, uint64_t pos, char* dst, uint64_t n) {
+  if (n == 0) return;
   const uint64_t cap = r->h->capacity, o = pos % cap;
   const uint64_t first = std::min(n, cap - o);
   memcpy(dst, r->data + o, first);

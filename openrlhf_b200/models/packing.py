@@ -21,6 +21,7 @@ class PackedBatch:
     indices: torch.Tensor        # int64 [T] flat index of each packed token in the (B*T) padded matrix
     batch: int
     seqlen: int
+    cu_list: list | None = None   # cu_seqlens as Python ints when the packer had them on the host (no device read)
 
 
 def pack_padded(sequences: torch.Tensor, attention_mask: torch.Tensor) -> PackedBatch:
@@ -54,7 +55,7 @@ def pack_lists(seqs: list[torch.Tensor], device=None) -> PackedBatch:
     labels = torch.cat([torch.cat([s[1:], s[:1]]) for s in seqs]).to(device).long()
     T = int(lens.max())
     idx = torch.cat([torch.arange(int(n)) + i * T for i, n in enumerate(lens)]).to(device)
-    return PackedBatch(ids, labels, pos, cu.to(device), T, idx, len(seqs), T)
+    return PackedBatch(ids, labels, pos, cu.to(device), T, idx, len(seqs), T, cu.tolist())
 
 
 def pack_lists_cp(seqs: list[torch.Tensor], world: int, pad_id: int = 0, device=None):

@@ -312,6 +312,9 @@ class WorkerHandle:
             pass
 
     def call(self, method: str, *args, **kwargs) -> Future:
+        from ..utils.tracing import tracer
+
+        tracer.instant(f"rpc:{method}", cat="runtime", worker=self.name)
         call_id = next(self._ids)
         fut = Future(self, call_id)
         if self._dead is not None:

@@ -182,7 +182,7 @@ class HybridRLWorker:
             chunk = seqs[s:s + micro]
             pb = pack_lists(chunk, self.device)
             logp, _, _ = actor.forward_packed(pb)
-            cu = pb.cu_seqlens.tolist()
+            cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
             for i in range(len(chunk)):
                 out.append(logp[cu[i]:cu[i + 1] - 1])
         actor.train(was)
@@ -196,7 +196,7 @@ class HybridRLWorker:
             pb = pack_lists(chunk, self.device)
             h, _ = self.critic(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
             v = self.critic.values(h)
-            cu = pb.cu_seqlens.tolist()
+            cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
             for i in range(len(chunk)):
                 out.append(v[cu[i]:cu[i + 1] - 1])
         return out
@@ -285,7 +285,7 @@ class HybridRLWorker:
                     mb = window[m0:m0 + micro]
                     pb = pack_lists([e.sequences for e in mb], self.device)
                     logp_t, ent_t, aux = self.actor.forward_packed(pb, return_entropy=a.actor.entropy_coef is not None)
-                    cu = pb.cu_seqlens.tolist()
+                    cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
                     sel = torch.cat([torch.arange(cu[i], cu[i + 1] - 1, device=self.device) for i in range(len(mb))])
                     logp = logp_t[sel]
                     cat = lambda f: torch.cat([getattr(e, f) for e in mb])
@@ -334,7 +334,7 @@ class HybridRLWorker:
                 pb = pack_lists([e.sequences for e in mb], self.device)
                 h, _ = self.critic(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
                 v_t = self.critic.values(h)
-                cu = pb.cu_seqlens.tolist()
+                cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
                 sel = torch.cat([torch.arange(cu[i], cu[i + 1] - 1, device=self.device) for i in range(len(mb))])
                 cat = lambda f: torch.cat([getattr(e, f) for e in mb])
                 mask = cat("action_mask").float()
@@ -358,17 +358,23 @@ class HybridRLWorker:
         ev["t0"].record()
         if isinstance(prompts, torch.Tensor):
             prompts = prompts.to(self.device, non_blocking=True).tolist()
-        exps = self.generate(prompts)
+        from ..utils.tracing import tracer
+
+        with tracer.span("generation", cat="rl_step", step=self.global_step):
+            exps = self.generate(prompts)
         ev["gen"].record()
-        exps = self.make_experience(exps)
-        exps = self.compute_advantages(exps)
+        with tracer.span("make_experience", cat="rl_step", step=self.global_step):
+            exps = self.make_experience(exps)
+            exps = self.compute_advantages(exps)
         ev["exp"].record()
         status = {}
-        if self.critic is not None:
-            status.update(self.train_critic(exps))
-        status.update(self.train(exps))
+        with tracer.span("ppo_train", cat="rl_step", step=self.global_step):
+            if self.critic is not None:
+                status.update(self.train_critic(exps))
+            status.update(self.train(exps))
         ev["train"].record()
-        self.sync_weights()
+        with tracer.span("broadcast", cat="rl_step", step=self.global_step):
+            self.sync_weights()
         ev["sync"].record()
         torch.cuda.synchronize(self.device)
         self.timing = {"timing/generation": ev["t0"].elapsed_time(ev["gen"]) / 1e3,
