@@ -69,7 +69,7 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_splitk", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
+    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
                                                          "rmsnorm", "adamw"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
@@ -95,7 +95,17 @@ def main():
 
     hbm, tf, tag = _peaks()
     dev = "cuda"
-    if a.kernel in ("gemm", "gemm_splitk"):
+    if a.kernel == "gemm_fp8":
+        from openrlhf_b200.ops.fp8 import gemm_e4m3, quantize_e4m3
+        M, N, K = a.m, a.n, a.k
+        A = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        B = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        (aq, sa), (bq, sb) = quantize_e4m3(A), quantize_e4m3(B)
+        t = _time(lambda: gemm_e4m3(aq, sa, bq, sb, bn=a.bn), a.iters)
+        fl = 2.0 * M * N * K
+        print(f"gemm_fp8 M{M} N{N} K{K} bn{a.bn}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+              f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak; nominal fp8 peak is twice the bf16 one)")
+    elif a.kernel in ("gemm", "gemm_splitk"):
         M, N, K = a.m, a.n, a.k
         a_mn, b_mn = a.layout == "tn", a.layout in ("nn", "tn")
         A = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)

@@ -3,6 +3,8 @@
 // They stand in for the PyTorch elementwise kernels HF Transformers launches under the reference
 // (RMSNorm / rotary / MLP activation of transformers' Llama and Qwen2 blocks, nn.Embedding) and for
 // DeepSpeed FusedAdam (openrlhf/utils/deepspeed/deepspeed.py:295-429 builds the optimizer).
+#include <cuda_fp8.h>
+
 #include "ptx.cuh"
 
 namespace b200 {
@@ -454,6 +456,51 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long
   }
 }
 
+// ------------------------------------------------------------------ fp8 (e4m3) per-tensor quantisation
+// amax_bits: non-negative float bit pattern (integer max == float max for non-negative floats), zeroed by the caller.
+__global__ void __launch_bounds__(256)
+absmax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long n, unsigned int* __restrict__ amax_bits) {
+  __shared__ float red[32];
+  float m = 0.f;
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(f[k]));
+  }
+  for (long long i = (nvec << 3) + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(__bfloat162float(x[i])));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    m = warp_max(m);
+    if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(m));
+  }
+}
+
+// q = e4m3(x / scale), scale = amax / 448 (written to scale_out for the GEMM's alpha). n multiple of 8.
+__global__ void __launch_bounds__(256)
+quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, long long n, const unsigned int* __restrict__ amax_bits,
+                     unsigned char* __restrict__ q, float* __restrict__ scale_out) {
+  const float amax = fmaxf(__uint_as_float(*amax_bits), 1e-12f);
+  const float scale = amax / 448.f, inv = 448.f / amax;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+    unsigned long long out = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      out |= (unsigned long long)__nv_cvt_float_to_fp8(f[k] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * k);
+    reinterpret_cast<unsigned long long*>(q)[i] = out;
+  }
+}
+
 // Tensor-parallel version of the kernel above: the row-parallel projection (o_proj / down_proj) of every TP rank left
 // its split-K slabs in a symmetric workspace; each rank reads ALL ranks' slabs (peer loads, fixed order rank 0..n-1, so
 // every rank gets bit-identical sums), adds the residual and runs the next RMSNorm. The all-reduce of the row-parallel
@@ -600,5 +647,18 @@ extern "C" int b200_tp_reduce_rmsnorm(const void* const* ws_ptrs, int world, int
   tp_reduce_rmsnorm_kernel<<<grid, NORM_THREADS, (size_t)(N / 8) * sizeof(uint4), STREAM(stream)>>>(
       t, world, splits, (long long)M * N, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,
       (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, M, N, eps);
+  return LAUNCH_OK();
+}
+
+// x bf16 [n] (n multiple of 8) -> q e4m3 [n] and the de-quantisation scale (amax / 448). amax_bits: 4-byte scratch.
+extern "C" int b200_quantize_e4m3(const void* x, long long n, void* q, float* scale_out, unsigned int* amax_bits,
+                                  void* stream) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  if (cudaMemsetAsync(amax_bits, 0, 4, STREAM(stream)) != cudaSuccess) return -3;
+  const int grid = grid_for(n / 8, 256, 148 * 8);
+  absmax_bf16_kernel<<<grid, 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, n, amax_bits);
+  quantize_e4m3_kernel<<<grid, 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, n, amax_bits, (unsigned char*)q,
+                                                          scale_out);
   return LAUNCH_OK();
 }

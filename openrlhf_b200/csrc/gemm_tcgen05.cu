@@ -46,6 +46,9 @@ struct GemmParams {
   const int* group_offsets;  // mode 2: [G+1] first row of each group in the K dimension (multiples of 64)
   int n_groups;              // mode 2
   long long group_c_stride;  // mode 2: elements between consecutive groups' outputs
+  // fp8 (e4m3) operands, both K-major: a k-block is 128 elements (still 128 bytes per row), MMA kind::f8f6f4
+  int fp8;
+  const float* alpha_dev;    // optional device scalar multiplied into alpha (product of the two quantisation scales)
 };
 
 // Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
@@ -81,7 +84,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int m_blocks = (p.M + BM - 1) / BM;
   const int n_blocks = (p.N + BN - 1) / BN;
-  const int kb_total = (p.K + BK - 1) / BK;
+  const int bke = p.fp8 ? 2 * BK : BK;              // elements per k-block (one 128-byte swizzle row)
+  const int kb_total = (p.K + bke - 1) / bke;
   const int splits = p.k_splits > 1 ? p.k_splits : 1;
   const int kb_per_split = (kb_total + splits - 1) / splits;
   const int num_tiles = m_blocks * n_blocks * splits * (p.group_mode == 2 ? p.n_groups : 1);
@@ -160,7 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               const int owner = row0 / p.ag_rows;
               tma_load_2d(sa, &peer_a.m[owner], &full_bar[stage], kb * BK, row0 - owner * p.ag_rows);
             } else {
-              tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, m_blk * BM);
+              tma_load_2d(sa, &tma_a, &full_bar[stage], kb * bke, m_blk * BM);
             }
           } else {
 #pragma unroll
@@ -169,7 +173,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           const int brow = p.group_mode == 1 ? grp * p.group_b_rows : 0;   // this group's block of the stacked B
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, brow + n_blk * BN);
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * bke, brow + n_blk * BN);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -207,7 +211,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                   : make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
             uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                   : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (p.fp8) umma_e4m3(d_tmem, adesc, bdesc, make_idesc_e4m3(BM, BN), (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -231,6 +236,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool has_work = kb1 > kb0;
+      const float alpha = p.alpha_dev != nullptr ? p.alpha * *p.alpha_dev : p.alpha;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -245,8 +251,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col0 + j < p.N) {
-                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
-                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4 v = make_float4(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha,
+                                       __uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
                 if (p.n_peer_c > 0) {
                   const size_t off = (size_t)row * p.ldc + col0 + j;
                   for (int pr = 0; pr < p.n_peer_c; ++pr) {
@@ -273,7 +279,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + j < p.N) {
                 float v[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]) * p.alpha;
+                for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]) * alpha;
                 if (p.bias != nullptr) {
                   uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
                   const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
@@ -353,6 +359,21 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+// 2-D 8-bit tensor map over a row-major [rows, cols] matrix with `ld` bytes between rows; box = [box_rows, 128].
+static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
@@ -579,4 +600,39 @@ extern "C" int b200_gemm_bf16_grouped(const void* A, const void* B, void* C, int
   if (bn == 128) { B200_DISPATCH(128) }
   B200_DISPATCH(64)
 #undef B200_DISPATCH
+}
+
+
+// fp8 GEMM: C[M,N] (bf16) = alpha * (*alpha_dev) * A[M,K] (e4m3) @ B[N,K]^T (e4m3) (+ bias)(+ residual), fp32
+// accumulation in tensor memory. alpha_dev (optional, device) carries the product of the per-tensor quantisation
+// scales so that no host read is needed. lda / ldb in elements (= bytes), multiples of 16.
+extern "C" int b200_gemm_e4m3(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                              int N, int K, int lda, int ldb, int ldc, float alpha, const float* alpha_dev, int bn,
+                              int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16) || (ldc % 8) || (N % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -12;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (bn != 64 && bn != 128 && bn != 256) bn = (N >= 2048 || (long long)M * N >= (long long)128 * 256 * 148) ? 256 : (N >= 512 ? 128 : 64);
+  CUtensorMap ta, tb;
+  int r = make_tmap_u8_2d(&ta, A, M, K, lda, BM);
+  if (r) return r;
+  r = make_tmap_u8_2d(&tb, B, N, K, ldb, bn);
+  if (r) return r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.k_splits = 1; p.alpha = alpha; p.alpha_dev = alpha_dev; p.status = status;
+  p.fp8 = 1;
+  static PeerMaps no_peers;
+  if (bn == 256) return launch<256, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
+  if (bn == 128) return launch<128, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
+  return launch<64, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
 }

@@ -60,3 +60,31 @@ def test_gemm_f32_accumulate_splitk():
     _lib.check_status()
     ref = 1.0 + dy.float().t() @ x.float()
     assert (grad - ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 512), (300, 1536, 1024), (4096, 2048, 1536), (64, 72, 144)])
+def test_gemm_e4m3_matches_dequantised_reference(M, N, K):
+    """fp8 tcgen05 GEMM against an fp32 matmul of the de-quantised operands (same rounding of the inputs, so only
+    the accumulation order and the bf16 output rounding differ)."""
+    from openrlhf_b200.ops import _lib
+    from openrlhf_b200.ops.fp8 import Fp8Linear, gemm_e4m3, quantize_e4m3
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    aq, sa = quantize_e4m3(a)
+    bq, sb = quantize_e4m3(b)
+    assert abs(float(sa) - float(a.float().abs().max()) / 448) < 1e-6
+    # quantisation itself: matches torch's e4m3 cast of the scaled tensor
+    ref_q = (a.float() / sa).to(torch.float8_e4m3fn)
+    assert (aq.float() - ref_q.float()).abs().max().item() <= 1e-6 * 448 + (ref_q.float().abs().max().item() * 0.07)
+    out = gemm_e4m3(aq, sa, bq, sb, bias=bias)
+    _lib.check_status()
+    ref = (aq.float() * sa) @ (bq.float() * sb).t() + bias.float()
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+    # end to end against the bf16 product: fp8 rounding error only
+    y = Fp8Linear(b, bias)(a)
+    full = a.float() @ b.float().t() + bias.float()
+    rel = ((y.float() - full).norm() / full.norm()).item()
+    assert rel < 6e-2, rel
