@@ -127,7 +127,9 @@ class Zero3Engine:
         model.flat = self.work          # the logical flat buffer no longer exists on this rank
         model.z3 = self
         del full
-        self.slot_layer = [-1, -1]      # which layer's parameters each slot holds
+        self.slot_layer = [-1, -1]      # which layer's parameters each slot holds (or is being filled with)
+        self._inflight: dict = {}       # layer -> event of its gather on the side stream
+        self._side = None
         self._plans: dict = {}
         self._tmp = torch.empty(min(self.per, _round(slot, 256)), dtype=torch.float32, device=self.device)
         self._pending_zero = -1
@@ -186,12 +188,35 @@ class Zero3Engine:
                 pieces.append((s.offset, s.offset + _round(s.numel, ALIGN), self.res_map[s.name]))
         self._gather_range("resident", pieces)
 
-    def gather_layer(self, i: int):
+    def _start_gather(self, i: int):
+        """Begin pulling layer i into its slot. On a GPU the copy kernel runs on a side stream, after everything that
+        is already enqueued on the compute stream (which includes the last user of that slot), so it overlaps with
+        the layer that is about to run."""
         if self.slot_layer[i % 2] == i:
             return
         a, b = self.layer_rng[i]
-        self._gather_range(("layer", i), [(a, b, self.slot_base[i % 2])])
+        pieces = [(a, b, self.slot_base[i % 2])]
+        if self.on_gpu and self.world > 1:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(ready)
+                self._gather_range(("layer", i), pieces)
+                done = torch.cuda.Event()
+                done.record(self._side)
+            self._inflight[i] = done
+        else:
+            self._gather_range(("layer", i), pieces)
         self.slot_layer[i % 2] = i
+
+    def gather_layer(self, i: int):
+        """Layer i's parameters are in their slot for everything enqueued on the compute stream after this call."""
+        self._start_gather(i)
+        done = self._inflight.pop(i, None)
+        if done is not None:
+            torch.cuda.current_stream(self.device).wait_event(done)
 
     def _reduce_range(self, a: int, b: int, w_off: int):
         """grad_shard[my part of logical [a, b)] += mean over ranks of the working gradients at w_off + (x - a)."""
@@ -221,10 +246,14 @@ class Zero3Engine:
     # ------------------------------------------------------------------------------------------------ model hooks
     def before_layer_forward(self, i: int):
         self.gather_layer(i)
+        if i + 1 < len(self.layer_rng):
+            self._start_gather(i + 1)          # prefetch: overlaps with layer i's compute
 
     def pre_backward_hook(self, i: int):
         def hook(grad):
             self.gather_layer(i)
+            if i > 0:
+                self._start_gather(i - 1)      # prefetch for the next layer of the backward pass
             return grad
         return hook
 
@@ -336,6 +365,9 @@ class Zero3Engine:
             self.param_shard.copy_(self.master.to(self.param_shard.dtype))
             self.grad_shard.zero_()
         self._sync()                       # every rank's new parameter slice is visible
+        for ev in self._inflight.values():
+            torch.cuda.current_stream(self.device).wait_event(ev)
+        self._inflight.clear()
         self.slot_layer = [-1, -1]
         self.gather_resident()
         if self.scheduler is not None:
