@@ -35,8 +35,16 @@ class _ValueModel(nn.Module):
     def gradient_checkpointing_enable(self, **_kw):
         self.model.gradient_checkpointing = True
 
-    def _token_values(self, input_ids, attention_mask):
+    def _token_values(self, input_ids, attention_mask, ring_attn_group=None):
         pb = pack_padded(input_ids, attention_mask)
+        if ring_attn_group is not None and input_ids.is_cuda:
+            # context parallel: this rank runs its rows of the re-packed stream, values are gathered per token
+            if getattr(self, "_cp", None) is None or self._cp.group is not ring_attn_group:
+                from ..parallel.cp import ContextParallel
+
+                self._cp = ContextParallel(ring_attn_group)
+            v, _ = self._cp.forward_values(self.model, pb)
+            return unpack_to_padded(v, pb), None, pb
         h, _ = self.model(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
         v = self.model.values(h)
         return unpack_to_padded(v, pb), h, pb
@@ -50,7 +58,7 @@ class RewardModel(_ValueModel):
         if attention_mask is None:
             attention_mask = torch.ones_like(input_ids)
         last = attention_mask.size(1) - 1 - attention_mask.long().fliplr().argmax(dim=1, keepdim=True)
-        values, h, _ = self._token_values(input_ids, attention_mask)
+        values, h, _ = self._token_values(input_ids, attention_mask, ring_attn_group)
         reward = values.gather(1, last).squeeze(1)
         if not self.training and self.normalize_reward:
             reward = (reward - self.mean.to(reward.device)) / self.std.to(reward.device)
@@ -65,7 +73,7 @@ class CriticModel(_ValueModel):
                 packed_seq_lens=None):
         if attention_mask is None:
             attention_mask = torch.ones_like(input_ids)
-        values, h, _ = self._token_values(input_ids, attention_mask)
+        values, h, _ = self._token_values(input_ids, attention_mask, ring_attn_group)
         if action_mask is None:
             assert return_output
             return {"last_hidden_state": h}

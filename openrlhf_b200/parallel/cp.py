@@ -216,6 +216,31 @@ class ContextParallel:
             self._ctx[key] = c
         return c
 
+    def _run(self, model, pb):
+        """This rank's rows through the decoder stack; returns (hidden [T_loc, H], aux, local labels, index that maps
+        the gathered context-parallel stream back to pb's packed order)."""
+        from ..models.packing import cp_slice, pack_lists_cp
+
+        cu = pb.cu_seqlens.tolist()
+        seqs = [pb.input_ids[a:b] for a, b in zip(cu[:-1], cu[1:])]
+        pb_cp, _ = pack_lists_cp(seqs, self.size, device=pb.input_ids.device)
+        ids, labels, pos = cp_slice(pb_cp, self.rank, self.size)
+        ctx = self._context(ids.numel(), model.cfg, ids.device)
+        model.cp = ctx
+        try:
+            h, aux = model(ids, pos, pb_cp.cu_seqlens, pb_cp.max_seqlen)
+        finally:
+            model.cp = None
+        cu_cp = pb_cp.cu_seqlens.tolist()
+        idx = torch.cat([torch.arange(b - a) + c for a, b, c in zip(cu[:-1], cu[1:], cu_cp[:-1])]).to(ids.device)
+        return h, aux, labels, idx
+
+    def forward_values(self, model, pb):
+        """Per-token values of a reward / critic model over the packed batch (context-parallel attention)."""
+        h, aux, _, idx = self._run(model, pb)
+        v = model.values(h)
+        return _GatherTokens.apply(v, self.group)[idx], aux
+
     def forward_logprobs(self, model, pb, temperature: float = 1.0, return_entropy: bool = False):
         from ..models.packing import cp_slice, pack_lists_cp
 

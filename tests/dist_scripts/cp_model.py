@@ -50,6 +50,17 @@ def main():
         rel = ((g_cp - g_ref).norm() / g_ref.norm()).item()
         print(f"rank {rank}: grad rel err {rel:.3e}", flush=True)
         assert rel < 3e-2, rel
+    # reward model: value at the last token, with and without context parallelism
+    from openrlhf_b200.models.model import get_llm_for_sequence_regression
+    rm = get_llm_for_sequence_regression("tiny-qwen2", "reward", device="cuda", seed=0, init_value_head=True)
+    with torch.no_grad():
+        r_ref = rm(seqs, attention_mask=mask)
+        r_cp = rm(seqs, attention_mask=mask, ring_attn_group=dist.group.WORLD)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    rerr = (r_ref.float() - r_cp.float()).abs().max().item()
+    print(f"rank {rank}: reward max |diff| {rerr:.3e}", flush=True)
+    assert rerr < 5e-2, rerr
     dist.barrier()
     if rank == 0:
         print("CP_MODEL_OK", flush=True)
