@@ -56,7 +56,7 @@ def synthetic_dataset(spec: str) -> ListDataset:
     kind = u.netloc or u.path.strip("/")
     rows = []
     for i in range(n):
-        if kind == "pairs":
+        if kind in ("pairs", "preference"):
             rows.append({"prompt": ids(ln), "chosen": ids(out_len), "rejected": ids(out_len)})
         elif kind == "sft":
             rows.append({"input": ids(ln), "output": ids(out_len)})
