@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--max-new", type=int, default=2048)
     ap.add_argument("--micro", type=int, default=4)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--zero-stage", type=int, default=2, choices=[1, 2, 3])
     ap.add_argument("--rollout-tp", type=int, default=1, help="tensor-parallel size of the rollout engines (N > 1)")
     return ap.parse_args()
 
@@ -122,7 +123,7 @@ def main():
     rl_args = default_rl_args(**{
         "rollout.n_samples_per_prompt": n, "rollout.max_new_tokens": new, "rollout.micro_batch_size": 8,
         "train.micro_batch_size": args.micro, "train.batch_size": 16 * world, "data.max_len": L + new,
-        "algo.advantage.estimator": "reinforce_baseline", "algo.kl.init_coef": 0.0, "ds.zero_stage": 2,
+        "algo.advantage.estimator": "reinforce_baseline", "algo.kl.init_coef": 0.0, "ds.zero_stage": args.zero_stage,
     })
     rl_args.rollout.ignore_eos = True
     if args.rollout_tp > 1:
@@ -137,7 +138,7 @@ def main():
     worker = HybridRLWorker(args.model, rl_args, device=f"cuda:{local}", reward_fn=rule_reward, seed=0, group=group,
                             max_num_seqs=P * n, num_pages=P * n * ((L + new) // 128 + 1) + P * (L // 128) + 8,
                             use_cuda_graph=not args.no_graph,
-                            use_symm=world > 1 and os.environ.get("OPENRLHF_B200_SYMM", "1") == "1")
+                            use_symm=world > 1 and args.zero_stage != 3 and os.environ.get("OPENRLHF_B200_SYMM", "1") == "1")
     vocab = worker.cfg.vocab_size
     g = torch.Generator().manual_seed(1234 + rank)
     total_steps = args.warmup + 2 * args.steps
@@ -204,8 +205,8 @@ def main():
             "phase_s_per_step": {k: v / args.steps for k, v in phases.items()},
             "config": {"model": args.model, "global_batch": P * n * world, "seq_len": L + new,
                        "prompts_per_gpu": P, "prompt_len": L, "n_samples_per_prompt": n, "max_new_tokens": new,
-                       "estimator": "reinforce_baseline", "zero_stage": 2, "micro_batch": args.micro,
-                       "parallelism": f"dp{world}" + (f", rollout tp{args.rollout_tp}" if args.rollout_tp > 1 else ""), "optimizer_step": ("peer-memory kernels" if worker.symm is not None else ("nccl" if world > 1 else "local")), "l2": "working set (3 GB weights + KV cache) is larger than L2"},
+                       "estimator": "reinforce_baseline", "zero_stage": args.zero_stage, "micro_batch": args.micro,
+                       "parallelism": f"dp{world}" + (f", rollout tp{args.rollout_tp}" if args.rollout_tp > 1 else ""), "optimizer_step": ("zero-3 peer-memory gathers and per-layer reductions" if getattr(worker, "zero3", False) else "peer-memory kernels" if worker.symm is not None else ("nccl" if world > 1 else "local")), "l2": "working set (3 GB weights + KV cache) is larger than L2"},
             "clocks": clocks,
             "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": P * L * 8,
                     "d2h_bytes_per_step": d2h // args.steps},

@@ -88,13 +88,30 @@ class HybridRLWorker:
             self.actor.gradient_checkpointing_enable()
         sched = LRScheduler(a.actor.adam.lr, max_steps, a.actor.lr_warmup_ratio, a.actor.min_lr_ratio,
                             a.actor.lr_scheduler)
-        self.engine = ZeroEngine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas), eps=a.actor.adam.eps,
-                                 weight_decay=a.actor.adam.weight_decay, max_norm=a.actor.max_norm,
-                                 zero_stage=a.ds.zero_stage, group=group, scheduler=sched, symm=self.symm)
+        self.zero3 = a.ds.zero_stage == 3 and self.world > 1 and not use_symm
+        self.rollout_model = self.model
+        ref_init = None
+        if self.zero3:
+            # stage 3: the trainer keeps only its slice of the parameters (plus two layer slots); the rollout engine
+            # gets a full copy of its own that the weight sync refreshes from the owners' slices (one copy kernel)
+            from ..parallel.zero3 import Zero3Engine
+
+            self.rollout_model = TransformerLM(cfg, device=self.device, seed=None, shard_world=self.world)
+            self.rollout_model.requires_grad_(False)
+            self.rollout_model.flat.copy_(self.model.flat[: self.rollout_model.flat.numel()])
+            ref_init = self.rollout_model.flat
+            self.engine = Zero3Engine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas),
+                                      eps=a.actor.adam.eps, weight_decay=a.actor.adam.weight_decay,
+                                      max_norm=a.actor.max_norm, group=group, scheduler=sched)
+        else:
+            self.engine = ZeroEngine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas),
+                                     eps=a.actor.adam.eps, weight_decay=a.actor.adam.weight_decay,
+                                     max_norm=a.actor.max_norm, zero_stage=a.ds.zero_stage, group=group,
+                                     scheduler=sched, symm=self.symm)
         self.ref = None
         if a.algo.kl.init_coef > 0:
             ref_model = TransformerLM(cfg, device=self.device, seed=None)
-            ref_model.flat.copy_(self.model.flat[: ref_model.flat.numel()])
+            ref_model.flat.copy_((ref_init if ref_init is not None else self.model.flat)[: ref_model.flat.numel()])
             ref_model.requires_grad_(False)
             self.ref = Actor(ref_model, temperature=a.rollout.temperature)
         self.critic = self.critic_engine = None
@@ -123,13 +140,13 @@ class HybridRLWorker:
                 g_ = dist.new_group(ranks)
                 if self.rank in ranks:
                     self.tp_group = g_
-            self.rollout = make_tp_engine(self.cfg, self.model.flat, self.tp_group,
+            self.rollout = make_tp_engine(self.cfg, self.rollout_model.flat, self.tp_group,
                                           max_num_seqs=max_num_seqs * self.rollout_tp, max_model_len=a.data.max_len,
                                           num_pages=(num_pages * self.rollout_tp) if num_pages else None,
                                           seed=seed + 1000 * (self.rank // self.rollout_tp),
                                           use_cuda_graph=use_cuda_graph)
         else:
-            self.rollout = RolloutEngine(self.model, max_num_seqs=max_num_seqs, max_model_len=a.data.max_len,
+            self.rollout = RolloutEngine(self.rollout_model, max_num_seqs=max_num_seqs, max_model_len=a.data.max_len,
                                          num_pages=num_pages, seed=seed + 1000 * self.rank,
                                          use_cuda_graph=use_cuda_graph)
         self.timing: dict[str, float] = {}
@@ -349,6 +366,11 @@ class HybridRLWorker:
     def sync_weights(self):
         """Actor -> rollout weight hand-off. Trainer and rollout engine read the same buffer on this GPU, so after the
         optimizer step (which all-gathers updated shards into every rank's buffer) there is nothing left to move."""
+        if self.zero3:
+            self.engine.gather_full(self.rollout_model.flat)     # K-SYNC from the owners' parameter slices
+            if self.tp_group is not None:
+                self.rollout.update_weights(self.rollout_model.flat)
+            return
         self.rollout.update_weights(self.model.flat)
 
     # ------------------------------------------------------------------ the RL step
