@@ -386,7 +386,10 @@ extern "C" int b200_reshard_copy(const void* plan_dev, int n_entries, const void
                                  void* stream) {
   if (n_entries <= 0) return 0;
   if (world > MAX_PEERS) return -10;
-  dim3 grid(n_entries, 8);
+  // enough blocks per entry to fill the GPU even when a plan has only a handful of large entries
+  int gy = (148 * 8 + n_entries - 1) / n_entries;
+  gy = gy < 8 ? 8 : (gy > 1024 ? 1024 : gy);
+  dim3 grid(n_entries, gy);
   reshard_copy_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const ReshardEntry*>(plan_dev), make_table(src_ptrs, world), reinterpret_cast<__nv_bfloat16*>(dst));
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
