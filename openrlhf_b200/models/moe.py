@@ -168,7 +168,8 @@ def permute_plan(idx: torch.Tensor, num_experts: int):
     flat_e = idx.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
     sorted_e = flat_e[order]
-    counts = torch.bincount(flat_e, minlength=E)
+    # scatter_add instead of bincount: no device->host read, so the decode loop can be captured in a CUDA graph
+    counts = torch.zeros(E, dtype=torch.long, device=idx.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
     padded = (counts + 127) // 128 * 128
     ends = torch.cumsum(padded, 0)
     starts = ends - padded

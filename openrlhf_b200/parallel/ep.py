@@ -72,7 +72,8 @@ class EPContext:
         T, k = idx.shape
         E, E_loc, W = self.E, self.E_loc, self.world
         flat_e = idx.reshape(-1)
-        counts = torch.bincount(flat_e, minlength=E).to(torch.int32)
+        counts = torch.zeros(E, dtype=torch.long, device=idx.device).scatter_add_(
+            0, flat_e, torch.ones_like(flat_e)).to(torch.int32)
         allc = torch.empty(W, E, dtype=torch.int32, device=idx.device)
         dist.all_gather_into_tensor(allc, counts, group=self.group)
         allc = allc.long()
