@@ -44,18 +44,33 @@ def unpack_to_padded(values: torch.Tensor, pb: PackedBatch, fill: float = 0.0) -
     return out.view(pb.batch, pb.seqlen)
 
 
+def _to_device(t: torch.Tensor, device):
+    """Host -> device without stalling the host: a pageable source makes the copy wait for the stream to drain (one
+    pipeline bubble per call), a pinned source with non_blocking does not."""
+    device = torch.device(device)
+    if device.type != "cuda" or t.is_cuda:
+        return t.to(device)
+    return t.pin_memory().to(device, non_blocking=True)
+
+
 def pack_lists(seqs: list[torch.Tensor], device=None) -> PackedBatch:
-    """Pack a list of 1-D token tensors directly (no padded intermediate)."""
+    """Pack a list of 1-D token tensors directly (no padded intermediate). Sequences that live on the host are
+    concatenated there and moved with one asynchronous copy per field."""
     device = device or seqs[0].device
     lens = torch.tensor([len(s) for s in seqs], dtype=torch.int32)
-    ids = torch.cat([s.to(device) for s in seqs]).long()
     cu = torch.zeros(len(seqs) + 1, dtype=torch.int32)
     cu[1:] = torch.cumsum(lens, 0)
-    pos = torch.cat([torch.arange(int(n), dtype=torch.int32) for n in lens]).to(device)
-    labels = torch.cat([torch.cat([s[1:], s[:1]]) for s in seqs]).to(device).long()
     T = int(lens.max())
-    idx = torch.cat([torch.arange(int(n)) + i * T for i, n in enumerate(lens)]).to(device)
-    return PackedBatch(ids, labels, pos, cu.to(device), T, idx, len(seqs), T, cu.tolist())
+    pos_c = torch.cat([torch.arange(int(n), dtype=torch.int32) for n in lens])
+    idx_c = torch.cat([torch.arange(int(n)) + i * T for i, n in enumerate(lens)])
+    if all(not s.is_cuda for s in seqs):
+        ids = _to_device(torch.cat(list(seqs)).long(), device)
+        labels = _to_device(torch.cat([torch.cat([s[1:], s[:1]]) for s in seqs]).long(), device)
+    else:
+        ids = torch.cat([s.to(device) for s in seqs]).long()
+        labels = torch.cat([torch.cat([s[1:], s[:1]]) for s in seqs]).to(device).long()
+    return PackedBatch(ids, labels, _to_device(pos_c, device), _to_device(cu, device), T, _to_device(idx_c, device),
+                       len(seqs), T, cu.tolist())
 
 
 def pack_lists_cp(seqs: list[torch.Tensor], world: int, pad_id: int = 0, device=None):
