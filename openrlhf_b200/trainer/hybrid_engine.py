@@ -63,7 +63,7 @@ class HybridRLWorker:
     def __init__(self, model_cfg: ModelConfig | str, args: SimpleNamespace | None = None, device=None,
                  reward_fn: Callable | None = None, max_steps: int = 1000, seed: int = 0, group=None,
                  max_num_seqs: int = 256, num_pages: int | None = None, use_cuda_graph: bool = True,
-                 with_critic: bool | None = None, use_symm: bool = False):
+                 with_critic: bool | None = None, use_symm: bool = False, reward_model=None):
         self.args = args or default_rl_args()
         a = self.args
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -124,7 +124,7 @@ class HybridRLWorker:
                                             eps=a.critic.adam.eps, weight_decay=a.critic.adam.weight_decay,
                                             max_norm=a.critic.max_norm, zero_stage=a.ds.zero_stage, group=group,
                                             scheduler=LRScheduler(a.critic.adam.lr, max_steps, 0.03, 0.1))
-        self.reward_model = None
+        self.reward_model = reward_model      # models.model.RewardModel: scores full sequences when no reward_fn is set
         self.reward_fn = reward_fn
         self.kl_ctl = FixedKLController(a.algo.kl.init_coef)
         self.rollout_tp = int(getattr(getattr(a, "vllm", None), "tensor_parallel_size", 1) or 1)
@@ -224,9 +224,20 @@ class HybridRLWorker:
         seqs = [e.sequences for e in exps]
         micro = a.rollout.micro_batch_size
         if exps[0].rewards is None:
-            if self.reward_fn is None:
+            if self.reward_fn is None and self.reward_model is None:
                 raise ValueError("no rewards on the samples and no reward function / model configured")
-            r = self.reward_fn(exps)
+            if self.reward_fn is not None:
+                r = self.reward_fn(exps)
+            else:
+                from ..utils.utils import zero_pad_sequences
+
+                r = []
+                self.reward_model.eval()
+                for s0 in range(0, len(seqs), micro):
+                    chunk = [t.to(self.device) for t in seqs[s0:s0 + micro]]
+                    ids = zero_pad_sequences(chunk, side="right", value=0, stack=True)
+                    att = zero_pad_sequences([torch.ones_like(t) for t in chunk], side="right", value=0, stack=True)
+                    r += list(self.reward_model(ids, attention_mask=att).float().unbind(0))
             for e, ri in zip(exps, r):
                 e.rewards = torch.as_tensor(ri, dtype=torch.float32).reshape(())
                 e.scores = e.rewards.clone()

@@ -131,14 +131,16 @@ def test_moe_model_trains_and_rolls_out():
 
 
 def test_rl_step_with_critic_and_kl():
-    """Full PPO flavour of the hybrid worker on a tiny model: critic + reference model + GAE + KL penalty."""
+    """Full PPO flavour of the hybrid worker on a tiny model: actor, reference, critic and a reward model (scalar head
+    on the last token), GAE and a KL penalty."""
     from openrlhf_b200.trainer.hybrid_engine import HybridRLWorker, default_rl_args
     args = default_rl_args(**{"rollout.n_samples_per_prompt": 2, "rollout.max_new_tokens": 8, "train.micro_batch_size": 2,
                               "train.batch_size": 4, "data.max_len": 64, "algo.advantage.estimator": "gae",
                               "algo.kl.init_coef": 0.05})
     args.rollout.ignore_eos = True
-    w = HybridRLWorker("tiny-qwen2", args, device="cuda", reward_fn=lambda exps: [float(i % 2) for i in range(len(exps))],
-                       max_num_seqs=8, num_pages=32)
+    from openrlhf_b200.models.model import get_llm_for_sequence_regression
+    rm = get_llm_for_sequence_regression("tiny-qwen2", "reward", device="cuda", seed=7, init_value_head=True)
+    w = HybridRLWorker("tiny-qwen2", args, device="cuda", reward_model=rm, max_num_seqs=8, num_pages=32)
     prompts = [torch.randint(3, w.cfg.vocab_size, (12,)).tolist() for _ in range(2)]
     st = w.rl_step(prompts)
     assert "critic_loss" in st and st["num_samples"] == 4
