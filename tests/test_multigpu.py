@@ -62,3 +62,8 @@ def test_zero3_matches_zero2():
 def test_tensor_parallel_rollout_engine():
     out = _run("tp_rollout.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "TP_ROLLOUT_OK" in out
+
+
+def test_hybrid_worker_zero3_and_tp_rollout():
+    out = _run("hybrid_modes.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "HYBRID_MODES_OK" in out
