@@ -14,7 +14,7 @@ namespace b200 {
 constexpr int PAGE = 128;   // tokens per KV page == kv tile
 constexpr int HD = 128;     // head dim
 constexpr int NPAD = 16;    // query heads per kv head, padded
-constexpr int DEC_STAGES = 1;   // one K and one V buffer per CTA; two CTAs share an SM and interleave their loads
+// one K and one V buffer per CTA; two CTAs share an SM and interleave their loads
 constexpr int KV_TILE_BYTES = PAGE * HD * 2;  // 32 KB for K, same for V
 
 struct DecodeParams {

@@ -248,24 +248,12 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restri
     return;
   }
   // ---- greedy: arg-max of the logits; the reported log-prob is under temperature 1
-  curandStatePhilox4_32_10_t rng;
   float sum = 0.f, best = -INFINITY;
   int best_i = 0x7fffffff;
-  float4 u4 = make_float4(0.5f, 0.5f, 0.5f, 0.5f);
-  int k = 0;
-  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS, ++k) {
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
     const float x = (load_logit(z, i) - mx) * inv_t;
-    const bool keep = x >= thr;
-    float key = x;
-    if (!greedy) {
-      if ((k & 3) == 0) u4 = curand_uniform4(&rng);
-      const float u = (k & 3) == 0 ? u4.x : ((k & 3) == 1 ? u4.y : ((k & 3) == 2 ? u4.z : u4.w));
-      key = x - __logf(-__logf(u));  // Gumbel noise
-    }
-    if (keep) {
-      sum += __expf(x);
-      if (key > best || (key == best && i < best_i)) { best = key; best_i = i; }
-    }
+    sum += __expf(x);
+    if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
   }
   sum = block_reduce_sum(sum, red);
   // argmax over the block

@@ -58,6 +58,29 @@ def main():
         print(f"rank {rank} {key}: weight rel {rel:.2e}, update rel {upd_rel:.2e}, losses {losses[:2]} vs {ref_losses[:2]}, "
               f"grad norm {norm:.4f} vs {ref_norm:.4f}", flush=True)
         assert abs(losses[0] - ref_losses[0]) < 1e-3 and upd_rel < 0.2 and abs(norm - ref_norm) < 0.05 * ref_norm, key
+    # ---- mixture-of-experts model: ZeRO-3 sharding combined with expert-parallel compute against plain ZeRO-2
+    from openrlhf_b200.parallel.ep import EPContext
+    mcfg = PRESETS["tiny-qwen3-moe"]
+    mdata = [[torch.randint(0, mcfg.vocab_size, (n,), generator=g) for n in (200, 90)] for _ in range(2)]
+    outs = {}
+    for kind in ("z2", "z3ep"):
+        model = TransformerLM(mcfg, device="cuda", seed=0, shard_world=world, init_std=0.05)
+        model.train()
+        eng = ZeroEngine(model, lr=1e-3, zero_stage=2) if kind == "z2" else Zero3Engine(model, lr=1e-3)
+        if kind == "z3ep":
+            model.ep = EPContext(None, 512, mcfg.num_experts_per_tok, mcfg.hidden_size, mcfg.num_experts, "cuda")
+        for j in range(2):
+            eng.backward(loss_of(model, mdata[j]) / 2)
+        eng.step()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        outs[kind] = (model.flat[: model.total_numel].float().clone() if kind == "z2" else eng.gather_full().float(),
+                      eng.grad_norm())
+    ref, full = outs["z2"][0], outs["z3ep"][0][: outs["z2"][0].numel()]
+    base = TransformerLM(mcfg, device="cuda", seed=0, init_std=0.05).flat[: ref.numel()].float()
+    upd_rel = ((full - ref).norm() / (ref - base).norm().clamp_min(1e-9)).item()
+    print(f"rank {rank} moe z3+ep: update rel {upd_rel:.2e}, grad norm {outs['z3ep'][1]:.4f} vs {outs['z2'][1]:.4f}", flush=True)
+    assert upd_rel < 0.25 and abs(outs["z3ep"][1] - outs["z2"][1]) < 0.05 * outs["z2"][1]
     dist.barrier()
     if rank == 0:
         print("ZERO3_OK", flush=True)
