@@ -39,8 +39,11 @@ def _round(n: int, m: int) -> int:
 
 class Zero3Engine:
     def __init__(self, model: TransformerLM, lr: float = 1e-6, betas=(0.9, 0.95), eps: float = 1e-8,
-                 weight_decay: float = 0.0, max_norm: float = 1.0, group=None, scheduler: LRScheduler | None = None):
+                 weight_decay: float = 0.0, max_norm: float = 1.0, group=None, scheduler: LRScheduler | None = None,
+                 expert_range: tuple[int, int] | None = None):
         self.model = model
+        # expert parallelism: this rank only computes experts [lo, hi) of every MoE layer, so only those are gathered
+        self.expert_range = expert_range
         initialised = dist.is_available() and dist.is_initialized()
         self.group = group if group is not None else (dist.group.WORLD if initialised else None)
         self.world = dist.get_world_size(self.group) if initialised else 1
@@ -196,6 +199,19 @@ class Zero3Engine:
             return
         a, b = self.layer_rng[i]
         pieces = [(a, b, self.slot_base[i % 2])]
+        if self.expert_range is not None:
+            pieces = []
+            e0, e1 = self.expert_range
+            for sp in self.model.specs:
+                if not sp.name.startswith(f"layers.{i}."):
+                    continue
+                w = self.slot_base[i % 2] + (sp.offset - a)
+                if len(sp.shape) == 3:                       # [experts, rows, cols]: the local experts' block only
+                    per_e = sp.shape[1] * sp.shape[2]
+                    pieces.append((sp.offset + e0 * per_e, sp.offset + e1 * per_e, w + e0 * per_e))
+                else:
+                    n = _round(sp.numel, ALIGN)
+                    pieces.append((sp.offset, sp.offset + n, w))
         if self.on_gpu and self.world > 1:
             if self._side is None:
                 self._side = torch.cuda.Stream(device=self.device)

@@ -66,7 +66,9 @@ def main():
     for kind in ("z2", "z3ep"):
         model = TransformerLM(mcfg, device="cuda", seed=0, shard_world=world, init_std=0.05)
         model.train()
-        eng = ZeroEngine(model, lr=1e-3, zero_stage=2) if kind == "z2" else Zero3Engine(model, lr=1e-3)
+        E_loc = mcfg.num_experts // world
+        eng = (ZeroEngine(model, lr=1e-3, zero_stage=2) if kind == "z2"
+               else Zero3Engine(model, lr=1e-3, expert_range=(rank * E_loc, (rank + 1) * E_loc)))
         if kind == "z3ep":
             model.ep = EPContext(None, 512, mcfg.num_experts_per_tok, mcfg.hidden_size, mcfg.num_experts, "cuda")
         for j in range(2):
