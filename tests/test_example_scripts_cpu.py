@@ -8,6 +8,7 @@ import shlex
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+NO_CLI = {"docker_run.sh"}     # helper scripts that start no trainer
 
 
 def _commands(path):
@@ -33,4 +34,4 @@ def test_script_flags_parse(script):
             known.update(a.option_strings)
         missing = [f for f in flags if f not in known]
         assert not missing, f"{os.path.basename(script)}: {module} does not accept {missing}"
-    assert found, "no CLI invocation found"
+    assert found or os.path.basename(script) in NO_CLI, "no CLI invocation found"
