@@ -32,7 +32,8 @@ class ActorOutput:
 class Actor(nn.Module):
     def __init__(self, pretrain_or_model, device="cuda", temperature: float = 1.0, packing_samples: bool = True,
                  shard_world: int = 1, seed: int = 0, lora_rank: int = 0, lora_alpha: float = 16,
-                 target_modules="all-linear", lora_dropout: float = 0.0, **_unused):
+                 target_modules="all-linear", lora_dropout: float = 0.0, freeze_visual_encoder: bool = False,
+                 **_unused):
         super().__init__()
         if isinstance(pretrain_or_model, TransformerLM):
             self.model = pretrain_or_model
@@ -49,6 +50,13 @@ class Actor(nn.Module):
             self.lora._cfg = self.cfg
         self.temperature = temperature
         self.packing_samples = packing_samples
+        self.is_vlm = self.cfg.is_vlm
+        if self.is_vlm and freeze_visual_encoder:
+            # only the language model trains (and only it changes between weight syncs);
+            # openrlhf/models/actor.py:167-175
+            for s, p in self.model.named_specs():
+                if s.name.startswith("visual."):
+                    p.requires_grad_(False)
 
     def gradient_checkpointing_enable(self, **_kw):
         self.model.gradient_checkpointing = True
@@ -57,11 +65,20 @@ class Actor(nn.Module):
         self.model.gradient_checkpointing = False
 
     # ------------------------------------------------------------------ native packed API
-    def forward_packed(self, pb: PackedBatch, return_entropy: bool = False, context_parallel=None):
-        """Per-token log-prob of the next token over the packed stream: returns (logp [T], entropy [T] | None, aux)."""
+    def forward_packed(self, pb: PackedBatch, return_entropy: bool = False, context_parallel=None,
+                       pixel_values=None, image_grid_thw=None):
+        """Per-token log-prob of the next token over the packed stream: returns (logp [T], entropy [T] | None, aux).
+        pixel_values / image_grid_thw: the image processor's outputs for the images of the batch, in batch order."""
         if context_parallel is not None and context_parallel.size > 1:
+            assert pixel_values is None, "context parallelism does not cover image inputs"
             return context_parallel.forward_logprobs(self.model, pb, self.temperature, return_entropy)
-        h, aux = self.model(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+        if self.is_vlm and pixel_values is not None:
+            cu_list = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()
+            dev = pb.input_ids.device
+            emb, pos = self.model.multimodal_inputs(pb.input_ids, cu_list, pixel_values.to(dev), image_grid_thw)
+            h, aux = self.model(pb.input_ids, pos, pb.cu_seqlens, pb.max_seqlen, inputs_embeds=emb)
+        else:
+            h, aux = self.model(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
         logp, ent = self.model.logprobs(h, pb.labels, self.temperature, return_entropy)
         return logp, ent, aux
 
@@ -69,7 +86,8 @@ class Actor(nn.Module):
     def forward(self, sequences: torch.LongTensor, action_mask: torch.Tensor | None = None,
                 attention_mask: torch.Tensor | None = None, return_output: bool = False,
                 allgather_logits: bool = False, return_logprobs: bool = False, ring_attn_group=None,
-                packed_seq_lens=None, return_entropy: bool = False, context_parallel=None):
+                packed_seq_lens=None, return_entropy: bool = False, context_parallel=None,
+                pixel_values=None, image_grid_thw=None, **_mm_unused):
         if attention_mask is None:
             attention_mask = torch.ones_like(sequences)
         pb = pack_padded(sequences, attention_mask)
@@ -79,7 +97,7 @@ class Actor(nn.Module):
 
                 self._cp = ContextParallel(ring_attn_group)
             context_parallel = self._cp
-        logp_t, ent_t, aux = self.forward_packed(pb, return_entropy, context_parallel)
+        logp_t, ent_t, aux = self.forward_packed(pb, return_entropy, context_parallel, pixel_values, image_grid_thw)
         log_probs = unpack_to_padded(logp_t, pb)[:, :-1]
         out = ActorOutput(aux_loss=aux)
         if return_entropy:

@@ -9,6 +9,7 @@ and the value-head conventions of openrlhf/models/model.py:70-82,183-198.
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 from typing import Iterator
@@ -27,6 +28,18 @@ def hf_names_for(cfg: ModelConfig, name: str) -> list[tuple[str, tuple | None]]:
     A selector is None (whole tensor), ("rows", a, b) for a row range of a fused matrix / bias, or
     ("expert", e, a, b) for rows [a, b) of expert e of a fused 3-D tensor.
     """
+    if name.startswith("visual."):
+        # vision tower (Qwen2-VL): same names under "model."; the patch embedding is stored as a Conv3d kernel
+        if name == "visual.patch_embed.weight":
+            v = cfg.vision_config()
+            return [("model.visual.patch_embed.proj.weight",
+                     ("view", (v.embed_dim, v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)))]
+        return [("model." + name, None)]
+    if cfg.is_vlm and name not in ("lm_head.weight", "value_head.weight"):
+        # the language model of a vision-language checkpoint lives under "model.language_model."
+        plain = dataclasses.replace(cfg, vision=None)
+        return [(("model.language_model." + n[len("model."):]) if n.startswith("model.") else n, sel)
+                for n, sel in hf_names_for(plain, name)]
     if name == "embed.weight":
         return [("model.embed_tokens.weight", None)]
     if name == "norm.weight":
@@ -65,11 +78,26 @@ def hf_names_for(cfg: ModelConfig, name: str) -> list[tuple[str, tuple | None]]:
     raise KeyError(name)
 
 
+def _alternate_names(hf_name: str) -> list[str]:
+    """Other spellings of a tensor name found in the wild: checkpoints saved from a bare base model (no "model."
+    prefix) and vision-language checkpoints written before the language model moved under "model.language_model."."""
+    alts = []
+    if hf_name.startswith("model.language_model."):
+        alts.append("model." + hf_name[len("model.language_model."):])
+    if hf_name.startswith("model.visual."):
+        alts.append(hf_name[len("model."):])
+    if hf_name.startswith("model."):
+        alts.append(hf_name[len("model."):])
+    return alts
+
+
 def _select(t: torch.Tensor, sel):
     if sel is None:
         return t
     if sel[0] == "rows":
         return t[sel[1]:sel[2]]
+    if sel[0] == "view":
+        return t.reshape(sel[1])
     return t[sel[1], sel[2]:sel[3]]
 
 
@@ -159,11 +187,15 @@ def load_weights(model: TransformerLM, path: str, strict: bool = True) -> list[s
     for spec, p in model.named_specs():
         for hf_name, sel in hf_names_for(model.cfg, spec.name):
             src_name = hf_name
-            if src_name not in wm and src_name.startswith("model.") and src_name[6:] in wm:
-                src_name = src_name[6:]            # checkpoints saved from a bare base model
+            for alt in _alternate_names(hf_name):
+                if src_name in wm:
+                    break
+                if alt in wm:
+                    src_name = alt
             if src_name not in wm:
-                if hf_name == "lm_head.weight" and "model.embed_tokens.weight" in wm:
-                    src_name = "model.embed_tokens.weight"
+                tied = [n for n in ("model.embed_tokens.weight", "model.language_model.embed_tokens.weight") if n in wm]
+                if hf_name == "lm_head.weight" and tied:
+                    src_name = tied[0]
                 else:
                     missing.append(hf_name)
                     continue

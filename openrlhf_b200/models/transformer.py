@@ -67,6 +67,11 @@ def build_param_specs(cfg: ModelConfig, with_lm_head: bool = True, with_value_he
         add("lm_head.weight", (cfg.vocab_size, H))
     if with_value_head:
         add("value_head.weight", (1, H))
+    if cfg.vision is not None:
+        from .vision import vision_param_shapes
+
+        for name, shape, decay, init in vision_param_shapes(cfg.vision_config()):
+            add(name, shape, decay, init)
     return specs
 
 
@@ -157,8 +162,13 @@ class TransformerLM(nn.Module):
     def _attention_block(self, i: int, h, pos, cu_seqlens, max_seqlen, attn_fn=None):
         cfg = self.cfg
         pre = f"layers.{i}."
+        rope_tab = None
+        if isinstance(pos, tuple):          # (row index, per-token rotary rows): multimodal positions
+            pos, rope_tab = pos
         x = F.rmsnorm(h, self.p(pre + "norm1.weight"), cfg.rms_norm_eps)
         qkv = self._lin(i, "qkv", x, self._params.get(pre + "qkv.bias"))
+        if rope_tab is None:
+            rope_tab = self.rope(qkv.device)
         T = qkv.shape[0]
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         if cfg.qk_norm:
@@ -167,14 +177,14 @@ class TransformerLM(nn.Module):
             kn = F.rmsnorm(qk[:, Hq:].reshape(-1, D), self.p(pre + "k_norm.weight"), cfg.rms_norm_eps).view(T, Hkv * D)
             qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * D:]], dim=1)
         if self.cp is not None and attn_fn is None:
-            a = self.cp.attention(qkv, pos, self.rope(qkv.device), cu_seqlens, 1.0 / math.sqrt(D))
+            a = self.cp.attention(qkv, pos, rope_tab, cu_seqlens, 1.0 / math.sqrt(D))
             return self._lin(i, "o", a, None, h)
         if attn_fn is None and qkv.is_cuda and D == 128 and qkv.dtype == torch.bfloat16:
             from ..ops.attention import rope_attention
 
-            a = rope_attention(qkv, pos, self.rope(qkv.device), cu_seqlens, Hq, Hkv, 1.0 / math.sqrt(D))
+            a = rope_attention(qkv, pos, rope_tab, cu_seqlens, Hq, Hkv, 1.0 / math.sqrt(D))
             return self._lin(i, "o", a, None, h)
-        qkv = F.rope(qkv, pos, self.rope(qkv.device), Hq + Hkv, D)
+        qkv = F.rope(qkv, pos, rope_tab, Hq + Hkv, D)
         q = qkv[:, : Hq * D].view(T, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
@@ -205,12 +215,52 @@ class TransformerLM(nn.Module):
             aux = h.new_zeros((), dtype=torch.float32)
         return h, aux
 
-    def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
-                attn_fn=None):
+    def image_embeds(self, pixel_values: torch.Tensor, image_grid_thw: torch.Tensor) -> torch.Tensor:
+        """Vision tower: the processor's flattened patches -> one embedding per image placeholder token."""
+        from .vision import vision_forward
+
+        return vision_forward(self.p, self.cfg.vision_config(), pixel_values, image_grid_thw)
+
+    def multimodal_inputs(self, input_ids, cu_list, pixel_values, image_grid_thw):
+        """Embeddings with the image placeholders filled in, and per-token M-RoPE rows for the packed stream.
+        cu_list: document boundaries as Python ints. Returns (embeds [T, H], (row index [T], rows [T, D/2, 2]))."""
+        from .vision import mrope_positions, mrope_rows, scatter_image_embeds
+
+        cfg = self.cfg
+        merge = cfg.vision_config().spatial_merge_size
+        embeds = F.embedding(input_ids, self.p("embed.weight"))
+        grids = [tuple(g) for g in image_grid_thw.tolist()] if image_grid_thw is not None else []
+        if pixel_values is not None and len(grids):
+            embeds = scatter_image_embeds(embeds, input_ids, self.image_embeds(pixel_values, image_grid_thw),
+                                          cfg.image_token_id)
+        ids = input_ids.tolist()
+        pos3, gi = [], 0
+        for a, b in zip(cu_list[:-1], cu_list[1:]):
+            # count the images of this document: every run of placeholders consumes the next grid
+            doc = ids[a:b]
+            n_img, k = 0, 0
+            while k < len(doc):
+                if doc[k] == cfg.image_token_id and gi + n_img < len(grids):
+                    t, hh, ww = grids[gi + n_img]
+                    k += t * (hh // merge) * (ww // merge)
+                    n_img += 1
+                else:
+                    k += 1
+            p3, _ = mrope_positions(doc, grids[gi:gi + n_img], cfg.image_token_id, merge, cfg.video_token_id)
+            gi += n_img
+            pos3.append(p3)
+        pos3 = torch.cat(pos3, dim=1)
+        rows = mrope_rows(self.rope(input_ids.device), pos3, cfg.mrope_section or (cfg.head_dim // 2,))
+        return embeds, (torch.arange(input_ids.numel(), dtype=torch.int32, device=input_ids.device), rows)
+
+    def forward(self, input_ids: torch.Tensor, position_ids, cu_seqlens: torch.Tensor, max_seqlen: int,
+                attn_fn=None, inputs_embeds: torch.Tensor | None = None):
         """input_ids int64 [T], position_ids int32 [T] (restart at 0 per document), cu_seqlens int32 [n+1].
+        Vision-language batches pass `inputs_embeds` and `position_ids = (row index, rotary rows)` from
+        `multimodal_inputs`.
 
         Returns (hidden [T,H] after the final norm, aux_loss scalar: sum of the MoE load-balancing terms)."""
-        h = F.embedding(input_ids, self.p("embed.weight"))
+        h = inputs_embeds if inputs_embeds is not None else F.embedding(input_ids, self.p("embed.weight"))
         aux_total = h.new_zeros((), dtype=torch.float32)
         z3 = getattr(self, "z3", None)      # parallel.zero3.Zero3Engine: layer parameters live in two shared slots
         for i in range(self.cfg.num_hidden_layers):

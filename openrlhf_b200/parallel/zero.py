@@ -113,7 +113,7 @@ class ZeroEngine:
         if weight_decay != 0.0:
             mask = torch.zeros(self.padded, dtype=torch.bool, device=self.device)
             for s in model.specs:
-                if s.decay:
+                if s.decay and model.p(s.name).requires_grad:      # frozen parameters (no gradient) must not decay
                     mask[s.offset:s.offset + s.numel] = True
             self.decay_mask = mask[sl].clone()
 

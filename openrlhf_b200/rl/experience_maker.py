@@ -54,6 +54,8 @@ class RemoteExperienceMaker:
     def _forward(self, role: str, samples: list[Experience], sync: bool):
         kw = dict(sequences=[s.sequences for s in samples], action_mask=[s.action_mask for s in samples],
                   attention_mask=[s.attention_mask for s in samples], role=[role] * len(samples))
+        if role != "critic" and any(any(m for m in (s.mm_train_inputs or [])) for s in samples):
+            kw["mm_train_inputs"] = [s.mm_train_inputs for s in samples]      # per-sample image inputs of each batch
         futs = self.group.async_run_method_batch("forward", **kw)
         if sync:
             get(futs)

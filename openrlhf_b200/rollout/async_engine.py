@@ -25,7 +25,7 @@ class AsyncRolloutEngine:
         rid = ("async", next(self._ids))
         fut = loop.create_future()
         self._futures[rid] = fut
-        self.engine.add_request(rid, prompt_token_ids, sampling_params)
+        self.engine.add_request(rid, prompt_token_ids, sampling_params, multi_modal_data)
         if self._driver is None or self._driver.done():
             self._driver = loop.create_task(self._drive())
         out = await fut

@@ -114,6 +114,11 @@ class RolloutEngine:
         dev = self.device
         self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        # vision-language models: rotary position of a generated token = token index + the prompt's M-RoPE offset
+        self.mrope = cfg.is_vlm
+        self.rope_delta = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.rope_pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        self._mm: dict = {}                     # request id -> {"pixel_values", "image_grid_thw"}
         self.seq_lens = torch.ones(B, dtype=torch.int32, device=dev)
         self.slots = torch.zeros(B, dtype=torch.int32, device=dev)
         self.block_table = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32, device=dev)
@@ -214,8 +219,9 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ model execution
     @torch.no_grad()
-    def _prefill(self, prompts: list[list[int]], row_groups: list[list[int]]):
-        """Run the prompts through the model once each, fill their KV pages, and return last-position logits [P, V]."""
+    def _prefill(self, prompts: list[list[int]], row_groups: list[list[int]], mms: list | None = None):
+        """Run the prompts through the model once each, fill their KV pages, and return last-position logits [P, V].
+        mms: per prompt None or {"pixel_values", "image_grid_thw"}; sets the rows' rotary offsets."""
         cfg, m = self.cfg, self.model
         dev = self.device
         lens = [len(p) for p in prompts]
@@ -240,7 +246,26 @@ class RolloutEngine:
 
         was_training = m.training
         m.eval()
-        h, _ = m(ids, pos, cu, max(lens), attn_fn=attn_fn)
+        embeds = None
+        if self.mrope:
+            deltas = [0] * len(prompts)
+            if mms and any(mms):
+                from ..models.vision import mrope_positions
+
+                pv = torch.cat([mm["pixel_values"] for mm in mms if mm]).to(dev)
+                thw = torch.cat([torch.as_tensor(mm["image_grid_thw"]).view(-1, 3) for mm in mms if mm])
+                cu_list = [0]
+                for n in lens:
+                    cu_list.append(cu_list[-1] + n)
+                embeds, pos = m.multimodal_inputs(ids, cu_list, pv, thw)
+                merge = cfg.vision_config().spatial_merge_size
+                for k, (p, mm) in enumerate(zip(prompts, mms)):
+                    if mm:
+                        grids = [tuple(g) for g in torch.as_tensor(mm["image_grid_thw"]).view(-1, 3).tolist()]
+                        deltas[k] = mrope_positions(p, grids, cfg.image_token_id, merge, cfg.video_token_id)[1]
+            for d, rows in zip(deltas, row_groups):
+                self.rope_delta[rows] = d
+        h, _ = m(ids, pos, cu, max(lens), attn_fn=attn_fn, inputs_embeds=embeds)
         m.train(was_training)
         last = (cu[1:] - 1).long()
         logits = gemm(h[last].contiguous(), m.lm_head_weight())
@@ -259,6 +284,8 @@ class RolloutEngine:
         cfg, m = self.cfg, self.model
         fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None
         assert fused or self.tp is None, "tensor-parallel rollout covers the dense fused decode path"
+        if self.mrope:
+            torch.add(self.pos[:B], self.rope_delta[:B], out=self.rope_pos[:B])
         if fused:
             logits = self._decode_layers_fused(B)
         else:
@@ -277,7 +304,7 @@ class RolloutEngine:
         Hq, Hkv, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size
         scale = 1.0 / math.sqrt(cfg.head_dim)
         table = m.rope(self.device)
-        tok, pos, slots = self.tok[:B], self.pos[:B], self.slots[:B]
+        tok, pos, slots = self.tok[:B], (self.rope_pos if self.mrope else self.pos)[:B], self.slots[:B]
         bt, sl = self.block_table[:B], self.seq_lens[:B]
         q_buf, attn_buf = self.q_buf[:B], self.attn_buf[:B]
         st = _lib.stream_ptr
@@ -328,7 +355,7 @@ class RolloutEngine:
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         scale = 1.0 / math.sqrt(cfg.head_dim)
         table = m.rope(self.device)
-        tok, pos, slots = self.tok[:B], self.pos[:B], self.slots[:B]
+        tok, pos, slots = self.tok[:B], (self.rope_pos if self.mrope else self.pos)[:B], self.slots[:B]
         bt, sl = self.block_table[:B], self.seq_lens[:B]
         q_buf, attn_buf = self.q_buf[:B], self.attn_buf[:B]
         h = F.embedding(tok, m.p("embed.weight"))
@@ -460,9 +487,27 @@ class RolloutEngine:
         self.block_table_host[row].fill_(self.dummy_page)
 
     # ------------------------------------------------------------------ request API (continuous batching)
-    def add_request(self, request_id, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
-        """Queue one request; it is admitted by a later ``step()`` when rows and KV pages are available."""
+    def add_request(self, request_id, prompt_token_ids: list[int], sampling_params: SamplingParams,
+                    multi_modal_data: dict | None = None) -> None:
+        """Queue one request; it is admitted by a later ``step()`` when rows and KV pages are available.
+        multi_modal_data: {"pixel_values": [N, patch_dim], "image_grid_thw": [n, 3]} for prompts that contain image
+        placeholder tokens (vision-language models), or {"image": [PIL images]} when an image processor is attached
+        (``self.image_processor``)."""
+        if multi_modal_data:
+            assert self.mrope, "this model takes no image inputs"
+            self._mm[request_id] = self._mm_tensors(multi_modal_data)
         self.waiting.append((request_id, list(prompt_token_ids), sampling_params))
+
+    image_processor = None
+
+    def _mm_tensors(self, mm: dict) -> dict:
+        if "pixel_values" in mm:
+            return {"pixel_values": mm["pixel_values"], "image_grid_thw": mm["image_grid_thw"]}
+        if self.image_processor is None:
+            raise ValueError("multi_modal_data carries images but the engine has no image_processor; pass "
+                             "pixel_values / image_grid_thw instead")
+        enc = self.image_processor(images=list(mm["image"]), return_tensors="pt")
+        return {"pixel_values": enc["pixel_values"], "image_grid_thw": enc["image_grid_thw"]}
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting) or any(r is not None for r in self.rows)
@@ -486,6 +531,7 @@ class RolloutEngine:
         while self.waiting:
             rid, prompt, sp = self.waiting[0]
             if len(prompt) >= self.max_model_len:
+                assert rid not in self._mm, "a prompt with images exceeds max_model_len (truncation would cut an image)"
                 prompt = prompt[-(self.max_model_len - 1):]
             max_new = self._max_new(prompt, sp)
             pages_needed = sp.n * ((len(prompt) + max_new) // PAGE + 1)
@@ -515,7 +561,8 @@ class RolloutEngine:
             admitted.append((prompt, sp))
             groups.append(rows)
         if admitted:
-            self._start_rows([a[0] for a in admitted], groups, [a[1] for a in admitted])
+            self._start_rows([a[0] for a in admitted], groups, [a[1] for a in admitted],
+                             [self._mm.pop(r, None) for r in (self.rows[g[0]].request_id for g in groups)])
         live = [i for i, r in enumerate(self.rows) if r is not None]
         if not live:
             return finished
@@ -562,8 +609,9 @@ class RolloutEngine:
 
     @torch.no_grad()
     def generate(self, prompt_token_ids: list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
-                 request_ids: list | None = None) -> list[RequestOutput]:
-        """Blocking batch generation on top of the request API (requests wait when rows or KV pages run out)."""
+                 request_ids: list | None = None, multi_modal_data: list | None = None) -> list[RequestOutput]:
+        """Blocking batch generation on top of the request API (requests wait when rows or KV pages run out).
+        multi_modal_data: per prompt None or the dict `add_request` takes."""
         if isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params] * len(prompt_token_ids)
         if sampling_params and sampling_params[0].seed is not None:
@@ -571,8 +619,9 @@ class RolloutEngine:
         base = self._batch_counter
         self._batch_counter += len(prompt_token_ids)
         keys = [("batch", base + i) for i in range(len(prompt_token_ids))]
-        for k, p, sp in zip(keys, prompt_token_ids, sampling_params):
-            self.add_request(k, p, sp)
+        mmd = multi_modal_data or [None] * len(keys)
+        for k, p, sp, mm in zip(keys, prompt_token_ids, sampling_params, mmd):
+            self.add_request(k, p, sp, mm)
         got: dict = {}
         while len(got) < len(keys):
             for ro in self.step():
@@ -584,11 +633,11 @@ class RolloutEngine:
             outs.append(ro)
         return outs
 
-    def _start_rows(self, prompts, groups, sps):
+    def _start_rows(self, prompts, groups, sps, mms=None):
         """Prefill admitted prompts and initialise the device state of their rows with the first sampled token."""
         dev = self.device
         self.block_table.copy_(self.block_table_host, non_blocking=True)
-        logits = self._prefill(prompts, groups)                      # [P, V]
+        logits = self._prefill(prompts, groups, mms)                 # [P, V]
         rep = torch.tensor([len(g) for g in groups], device=dev)
         rows = torch.tensor([r for g in groups for r in g], dtype=torch.int64, device=dev)
         lg = logits.repeat_interleave(rep, dim=0)                    # one row per sample

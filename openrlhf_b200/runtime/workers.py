@@ -48,6 +48,16 @@ def _cpu(x):
     return x.detach().to("cpu") if isinstance(x, torch.Tensor) else x
 
 
+def _mm_kwargs(mm_train_inputs, device) -> dict:
+    """Per-sample image inputs of a batch (list of dicts or None) -> keyword arguments of Actor.forward
+    (openrlhf/trainer/ray/ppo_actor.py merges them the same way before the policy forward)."""
+    if not mm_train_inputs or not any(mm_train_inputs):
+        return {}
+    from ..utils.vlm_utils import merge_mm_train_inputs
+
+    return merge_mm_train_inputs(mm_train_inputs, device)
+
+
 class RLWorker:
     def __init__(self, args: SimpleNamespace, roles=ALL_ROLES, max_steps: int = 1000, backend: str | None = None):
         self.args = args
@@ -63,7 +73,8 @@ class RLWorker:
         temp = a.rollout.temperature
         if "actor" in self.roles:
             lm = load_pretrained(a.actor.model_name_or_path, device=self.device, shard_world=dp, seed=a.train.seed)
-            self.actor = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples)
+            self.actor = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples,
+                               freeze_visual_encoder=getattr(a.actor, "freeze_visual_encoder", False))
             if a.actor.gradient_checkpointing_enable:
                 self.actor.gradient_checkpointing_enable()
             sched = LRScheduler(a.actor.adam.lr, max_steps, a.actor.lr_warmup_ratio, a.actor.min_lr_ratio,
@@ -190,7 +201,7 @@ class RLWorker:
 
     # ------------------------------------------------------------------ inference forwards (one micro-batch per call)
     @torch.no_grad()
-    def forward(self, sequences, action_mask, attention_mask, role: str = "actor", **_unused):
+    def forward(self, sequences, action_mask, attention_mask, role: str = "actor", mm_train_inputs=None, **_unused):
         seq, am, att = sequences.to(self.device), action_mask.to(self.device), attention_mask.to(self.device)
         if role == "critic":
             self.critic.eval()
@@ -201,7 +212,7 @@ class RLWorker:
             dev = next(model.parameters()).device
             was = model.training
             model.eval()
-            out = model(seq.to(dev), am.to(dev), att.to(dev))
+            out = model(seq.to(dev), am.to(dev), att.to(dev), **_mm_kwargs(mm_train_inputs, dev))
             model.train(was)
         return _cpu(out)
 
@@ -269,7 +280,8 @@ class RLWorker:
                 exp.to_device(self.device)
                 mask = exp.action_mask.float()
                 logp, out = self.actor(exp.sequences, exp.action_mask, exp.attention_mask, return_output=True,
-                                       return_entropy=a.actor.entropy_coef is not None)
+                                       return_entropy=a.actor.entropy_coef is not None,
+                                       **_mm_kwargs(getattr(exp, "mm_train_inputs", None), self.device))
                 norm = {k: info[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size")}
                 loss, clip_ratio, ppo_kl, vllm_kl = self.policy_loss(logp, exp.action_log_probs, exp.advantages, mask,
                                                                      exp.rollout_log_probs, **norm)
