@@ -13,6 +13,8 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
     def find_spec(self, fullname, path=None, target=None):
         if fullname == "openrlhf" or not fullname.startswith("openrlhf."):
             return None
+        if fullname == "openrlhf.cli" or fullname.startswith("openrlhf.cli."):
+            return None                  # physical launcher stubs of this package
         real = _TARGET + fullname[len("openrlhf"):]
         try:
             real_spec = importlib.util.find_spec(real)
@@ -32,5 +34,8 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
 
 
 if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
-    sys.meta_path.append(_AliasFinder())  # after the regular finders: physical modules under openrlhf/ win
+    # ahead of the path finder: a submodule of an aliased package (openrlhf.utils.agent) must be the *same* module
+    # object as its target, not a second copy loaded from the target's directory under the alias name, or user classes
+    # deriving from openrlhf.utils.agent.AgentExecutorBase would fail the workers' issubclass checks
+    sys.meta_path.insert(0, _AliasFinder())
 __version__ = "0.11.0+b200"

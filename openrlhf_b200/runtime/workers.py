@@ -143,6 +143,8 @@ class RLWorker:
                                          gpu_memory_utilization=a.vllm.gpu_memory_utilization,
                                          seed=a.train.seed + s.rank, eos_token_id=self.tokenizer.eos_token_id,
                                          use_cuda_graph=not a.vllm.enforce_eager)
+            # vision-language models: the processor's image part turns the PIL images an agent passes into patches
+            self.rollout.image_processor = getattr(self.tokenizer, "image_processor", None)
             self.async_engine = AsyncRolloutEngine(self.rollout, self.tokenizer)
             if a.train.agent_func_path:
                 cls = load_python_object(a.train.agent_func_path, "AgentExecutor")

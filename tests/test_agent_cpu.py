@@ -142,3 +142,13 @@ def test_openai_shim_over_http():
         pytest.skip(f"local HTTP endpoint unavailable: {e}")
     text = CharTokenizer().decode(res["observation_tokens"])
     assert text.endswith("pong") and len(res["action_ranges"]) == 1
+
+
+@pytest.mark.parametrize("fname", ["agent_func.py", "agent_func_gem_multiturn.py", "agent_func_openai_server_executor.py"])
+def test_example_executors_pass_the_worker_type_check(fname):
+    """User files import the base classes through the ``openrlhf`` alias package; the workers check them against
+    ``openrlhf_b200.utils.agent``: both must be the same class objects."""
+    from openrlhf_b200.utils.agent import AgentExecutorBase
+
+    cls = load_python_object(os.path.join(EX, fname), "AgentExecutor")
+    assert issubclass(cls, AgentExecutorBase)
