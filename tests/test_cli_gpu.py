@@ -46,3 +46,42 @@ def test_train_ppo_ray_end_to_end(variant, tmp_path):
     assert "global step 1" in r.stdout, tail
     assert os.path.exists(os.path.join(out_dir, "config.json")), tail
     assert any(f.endswith(".safetensors") for f in os.listdir(out_dir)), tail
+
+
+def _run(args, timeout=600):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, *args], cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    return r.stdout + r.stderr
+
+
+SPMD = ["--data.max_len", "128", "--train.batch_size", "16", "--train.micro_batch_size", "4", "--train.max_epochs", "1",
+        "--ds.zero_stage", "2", "--ds.packing_samples", "--adam.lr", "1e-4"]
+
+
+def test_sft_lora_then_combiner(tmp_path):
+    lora_dir, merged = str(tmp_path / "lora"), str(tmp_path / "merged")
+    _run(["-m", "openrlhf.cli.train_sft", "--model.model_name_or_path", "tiny-qwen2",
+          "--data.dataset", "synthetic://sft?n=64&len=48&vocab=2000", "--data.input_key", "input",
+          "--data.output_key", "output", *SPMD, "--ds.lora.rank", "8", "--ds.lora.alpha", "16",
+          "--ckpt.output_dir", lora_dir])
+    assert os.listdir(lora_dir)
+    _run(["-m", "openrlhf.cli.lora_combiner", "--model_path", "tiny-qwen2", "--lora_path", lora_dir,
+          "--output_path", merged])
+    assert os.path.exists(os.path.join(merged, "config.json"))
+
+
+def test_rm_then_dpo(tmp_path):
+    rm_dir, dpo_dir = str(tmp_path / "rm"), str(tmp_path / "dpo")
+    data = ["--data.dataset", "synthetic://preference?n=64&len=48&vocab=2000", "--data.prompt_key", "prompt",
+            "--data.chosen_key", "chosen", "--data.rejected_key", "rejected"]
+    log = _run(["-m", "openrlhf.cli.train_rm", "--model.model_name_or_path", "tiny-qwen2", *data, *SPMD,
+                "--ckpt.output_dir", rm_dir])
+    assert "acc" in log
+    import json
+
+    cfg = json.load(open(os.path.join(rm_dir, "config.json")))
+    assert cfg.get("value_head_prefix") == "score"            # the trained reward model carries its head's name
+    _run(["-m", "openrlhf.cli.train_dpo", "--model.model_name_or_path", "tiny-qwen2", "--ref.model_name_or_path",
+          "tiny-qwen2", *data, *SPMD, "--model.beta", "0.1", "--ckpt.output_dir", dpo_dir])
+    assert os.path.exists(os.path.join(dpo_dir, "config.json"))
