@@ -99,7 +99,6 @@ def validate(args):
         assert a.rollout.n_samples_per_prompt > 1, f"{a.algo.advantage.estimator} requires n_samples_per_prompt > 1"
     if a.data.max_images_per_prompt > 0:
         assert a.critic.model_name_or_path is None, "VLM training does not support a critic model; use a critic-free estimator"
-        assert not a.ds.packing_samples, "VLM training does not support --ds.packing_samples"
     if a.reward.remote_url and isinstance(a.reward.remote_url, str):
         a.reward.remote_url = a.reward.remote_url.split(",")
     if a.data.input_template and "{}" not in a.data.input_template:

@@ -46,7 +46,9 @@ class ListDataset(list):
 def synthetic_dataset(spec: str) -> ListDataset:
     """``synthetic://prompts?n=128&len=512&vocab=151936&seed=0``: rows {"input": "<ids>", "label": "<ids>"} whose text
     is a space-separated list of token ids (pairs with utils.SyntheticTokenizer). ``synthetic://pairs?...`` yields
-    {"prompt","chosen","rejected"} rows and ``synthetic://sft`` {"input","output"} rows."""
+    {"prompt","chosen","rejected"} rows and ``synthetic://sft`` {"input","output"} rows;
+    ``synthetic://vlm_prompts?...&image=56`` prepends an ``<image>`` tag and attaches one random RGB image of that
+    side length per row (pairs with utils.SyntheticProcessor)."""
     u = urlparse(spec)
     q = {k: v[0] for k, v in parse_qs(u.query).items()}
     n, ln, vocab, seed = int(q.get("n", 64)), int(q.get("len", 64)), int(q.get("vocab", 1024)), int(q.get("seed", 0))
@@ -60,6 +62,12 @@ def synthetic_dataset(spec: str) -> ListDataset:
             rows.append({"prompt": ids(ln), "chosen": ids(out_len), "rejected": ids(out_len)})
         elif kind == "sft":
             rows.append({"input": ids(ln), "output": ids(out_len)})
+        elif kind == "vlm_prompts":
+            from PIL import Image
+
+            side = int(q.get("image", 56))
+            img = Image.frombytes("RGB", (side, side), bytes(rng.randrange(256) for _ in range(3 * side * side)))
+            rows.append({"input": "<image> " + ids(ln), "label": str(i % 7), "datasource": "synthetic", "images": [img]})
         else:
             rows.append({"input": ids(ln), "label": str(i % 7), "datasource": "synthetic"})
     return ListDataset(rows)

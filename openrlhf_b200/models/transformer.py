@@ -224,31 +224,26 @@ class TransformerLM(nn.Module):
     def multimodal_inputs(self, input_ids, cu_list, pixel_values, image_grid_thw):
         """Embeddings with the image placeholders filled in, and per-token M-RoPE rows for the packed stream.
         cu_list: document boundaries as Python ints. Returns (embeds [T, H], (row index [T], rows [T, D/2, 2]))."""
-        from .vision import mrope_positions, mrope_rows, scatter_image_embeds
+        from .vision import image_runs, mrope_positions, mrope_rows, scatter_image_embeds
 
         cfg = self.cfg
         merge = cfg.vision_config().spatial_merge_size
         embeds = F.embedding(input_ids, self.p("embed.weight"))
         grids = [tuple(g) for g in image_grid_thw.tolist()] if image_grid_thw is not None else []
-        if pixel_values is not None and len(grids):
-            embeds = scatter_image_embeds(embeds, input_ids, self.image_embeds(pixel_values, image_grid_thw),
-                                          cfg.image_token_id)
         ids = input_ids.tolist()
-        pos3, gi = [], 0
+        pos3, where, gi = [], [], 0
         for a, b in zip(cu_list[:-1], cu_list[1:]):
-            # count the images of this document: every run of placeholders consumes the next grid
             doc = ids[a:b]
-            n_img, k = 0, 0
-            while k < len(doc):
-                if doc[k] == cfg.image_token_id and gi + n_img < len(grids):
-                    t, hh, ww = grids[gi + n_img]
-                    k += t * (hh // merge) * (ww // merge)
-                    n_img += 1
-                else:
-                    k += 1
-            p3, _ = mrope_positions(doc, grids[gi:gi + n_img], cfg.image_token_id, merge, cfg.video_token_id)
-            gi += n_img
+            runs = image_runs(doc, grids[gi:], cfg.image_token_id, merge, cfg.video_token_id)
+            mine = [r[2] for r in runs]
+            p3, _ = mrope_positions(doc, mine, cfg.image_token_id, merge, cfg.video_token_id)
+            for start, cnt, _g in runs:
+                where.append(torch.arange(a + start, a + start + cnt))
+            gi += len(runs)
             pos3.append(p3)
+        assert gi == len(grids), f"{len(grids)} images were passed but the token stream holds {gi} complete image runs"
+        if pixel_values is not None and len(grids):
+            embeds = scatter_image_embeds(embeds, torch.cat(where), self.image_embeds(pixel_values, image_grid_thw))
         pos3 = torch.cat(pos3, dim=1)
         rows = mrope_rows(self.rope(input_ids.device), pos3, cfg.mrope_section or (cfg.head_dim // 2,))
         return embeds, (torch.arange(input_ids.numel(), dtype=torch.int32, device=input_ids.device), rows)

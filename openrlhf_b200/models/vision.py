@@ -151,6 +151,26 @@ def vision_forward(p, v: VisionConfig, pixel_values: torch.Tensor, grid_thw: tor
 
 
 # ---------------------------------------------------------------------------------------------- language-model side
+def image_runs(ids: list[int], grids: list[tuple[int, int, int]], image_token_id: int, merge: int,
+               video_token_id: int | None = None) -> list[tuple[int, int, tuple[int, int, int]]]:
+    """Match the placeholder runs of one sequence to the next grids, in order: [(start, length, grid)]. A run counts
+    only when it is complete (t * h/merge * w/merge placeholders in a row); a stray placeholder token, e.g. one the
+    policy sampled itself, stays an ordinary text token."""
+    media = {image_token_id} | ({video_token_id} if video_token_id is not None and video_token_id >= 0 else set())
+    out, i, gi, n = [], 0, 0, len(ids)
+    while i < n and gi < len(grids):
+        if ids[i] in media:
+            t, h, w = grids[gi]
+            cnt = t * (h // merge) * (w // merge)
+            if i + cnt <= n and all(x in media for x in ids[i:i + cnt]):
+                out.append((i, cnt, (t, h, w)))
+                gi += 1
+                i += cnt
+                continue
+        i += 1
+    return out
+
+
 def mrope_positions(ids: list[int], grids: list[tuple[int, int, int]], image_token_id: int, merge: int,
                     video_token_id: int | None = None) -> tuple[torch.Tensor, int]:
     """3-component positions of one sequence. Text tokens count up with all components equal; the tokens of an image
@@ -161,26 +181,21 @@ def mrope_positions(ids: list[int], grids: list[tuple[int, int, int]], image_tok
     ``len(ids) + k + delta`` in every component."""
     n = len(ids)
     pos = torch.zeros(3, n, dtype=torch.int32)
-    nxt, i, gi = 0, 0, 0
-    media = {image_token_id} | ({video_token_id} if video_token_id is not None else set())
-    while i < n:
-        if ids[i] in media and gi < len(grids):
-            t, h, w = grids[gi]
-            gi += 1
-            lh, lw = h // merge, w // merge
-            cnt = t * lh * lw
-            assert all(x in media for x in ids[i:i + cnt]) and i + cnt <= n, \
-                "the run of image tokens is shorter than image_grid_thw says"
-            tt = torch.arange(t).view(t, 1, 1).expand(t, lh, lw).reshape(-1)
-            hh = torch.arange(lh).view(1, lh, 1).expand(t, lh, lw).reshape(-1)
-            ww = torch.arange(lw).view(1, 1, lw).expand(t, lh, lw).reshape(-1)
-            pos[:, i:i + cnt] = (torch.stack([tt, hh, ww]) + nxt).to(torch.int32)
-            nxt += max(t, lh, lw)
-            i += cnt
-        else:
-            pos[:, i] = nxt
-            nxt += 1
-            i += 1
+    nxt, i = 0, 0
+    for start, cnt, (t, h, w) in image_runs(ids, grids, image_token_id, merge, video_token_id):
+        if start > i:
+            pos[:, i:start] = torch.arange(nxt, nxt + start - i, dtype=torch.int32)
+            nxt += start - i
+        lh, lw = h // merge, w // merge
+        tt = torch.arange(t).view(t, 1, 1).expand(t, lh, lw).reshape(-1)
+        hh = torch.arange(lh).view(1, lh, 1).expand(t, lh, lw).reshape(-1)
+        ww = torch.arange(lw).view(1, 1, lw).expand(t, lh, lw).reshape(-1)
+        pos[:, start:start + cnt] = (torch.stack([tt, hh, ww]) + nxt).to(torch.int32)
+        nxt += max(t, lh, lw)
+        i = start + cnt
+    if n > i:
+        pos[:, i:] = torch.arange(nxt, nxt + n - i, dtype=torch.int32)
+        nxt += n - i
     return pos, nxt - n
 
 
@@ -195,10 +210,8 @@ def mrope_rows(table: torch.Tensor, pos3: torch.Tensor, sections) -> torch.Tenso
     return table[idx, j].transpose(0, 1).contiguous()            # [T, half, 2]
 
 
-def scatter_image_embeds(embeds: torch.Tensor, input_ids: torch.Tensor, image_embeds: torch.Tensor,
-                         image_token_id: int) -> torch.Tensor:
-    """Replace the embedding of every image placeholder token, in order, by the tower's output rows."""
-    where = (input_ids == image_token_id).nonzero(as_tuple=False).squeeze(-1)
+def scatter_image_embeds(embeds: torch.Tensor, where: torch.Tensor, image_embeds: torch.Tensor) -> torch.Tensor:
+    """Replace the embeddings at the placeholder positions `where` (int64, in order) by the tower's output rows."""
     assert where.numel() == image_embeds.shape[0], \
-        f"{where.numel()} image tokens in the batch but {image_embeds.shape[0]} image embeddings"
-    return embeds.index_put((where,), image_embeds.to(embeds.dtype))
+        f"{where.numel()} image placeholder tokens matched but {image_embeds.shape[0]} image embeddings"
+    return embeds.index_put((where.to(embeds.device),), image_embeds.to(embeds.dtype))

@@ -92,6 +92,104 @@ class SyntheticTokenizer:
                        "pad_token_id": self.pad_token_id}, f)
 
 
+class SyntheticImageProcessor:
+    """Image -> flattened patches in the Qwen2-VL order (merge x merge neighbours adjacent, temporal patch made of
+    the frame repeated), without files: sides are rounded to a multiple of patch * merge, pixels scaled to [-1, 1]."""
+
+    def __init__(self, patch_size=14, merge_size=2, temporal_patch_size=2, max_side=448):
+        self.patch_size, self.merge_size, self.temporal_patch_size, self.max_side = (
+            patch_size, merge_size, temporal_patch_size, max_side)
+
+    def _one(self, img):
+        import numpy as np
+
+        P, m, Tp = self.patch_size, self.merge_size, self.temporal_patch_size
+        unit = P * m
+        w, h = img.size
+        gh = max(1, min(round(h / unit), self.max_side // unit)) * m
+        gw = max(1, min(round(w / unit), self.max_side // unit)) * m
+        arr = np.asarray(img.convert("RGB").resize((gw * P, gh * P)), dtype=np.float32) / 127.5 - 1.0
+        x = torch.from_numpy(arr).permute(2, 0, 1)                                   # [C, H, W]
+        x = x[None].repeat(Tp, 1, 1, 1)                                              # [Tp, C, H, W]
+        x = x.view(Tp, 3, gh // m, m, P, gw // m, m, P).permute(2, 5, 3, 6, 1, 0, 4, 7)
+        return x.reshape(gh * gw, 3 * Tp * P * P), (1, gh, gw)
+
+    def __call__(self, images, return_tensors="pt", **_kw):
+        outs = [self._one(im) for im in images]
+        return {"pixel_values": torch.cat([o[0] for o in outs]),
+                "image_grid_thw": torch.tensor([o[1] for o in outs], dtype=torch.long)}
+
+
+class SyntheticProcessor:
+    """Processor for vision-language presets: SyntheticTokenizer for the text, SyntheticImageProcessor for the images;
+    every ``<image>`` tag in the text becomes vision_start + one placeholder per merged patch + vision_end."""
+
+    def __init__(self, tokenizer: SyntheticTokenizer, cfg):
+        v = cfg.vision_config()
+        self.tokenizer = tokenizer
+        self.image_processor = SyntheticImageProcessor(v.patch_size, v.spatial_merge_size, v.temporal_patch_size)
+        self.image_token_id, self.video_token_id = cfg.image_token_id, cfg.video_token_id
+        self.vision_start_token_id, self.vision_end_token_id = cfg.vision_start_token_id, cfg.vision_end_token_id
+        self.merge = v.spatial_merge_size
+        for attr in ("pad_token", "pad_token_id", "eos_token", "eos_token_id", "vocab_size", "chat_template"):
+            setattr(self, attr, getattr(tokenizer, attr))
+
+    @property
+    def padding_side(self):
+        return self.tokenizer.padding_side
+
+    @padding_side.setter
+    def padding_side(self, v):
+        self.tokenizer.padding_side = v
+
+    def __call__(self, text=None, images=None, return_tensors=None, **kw):
+        if not images:
+            return self.tokenizer(text=text, return_tensors=return_tensors, **kw)
+        texts = [text] if isinstance(text, str) else list(text)
+        enc = self.image_processor(images)
+        grids = enc["image_grid_thw"].tolist()
+        rows, gi = [], 0
+        for t in texts:
+            ids = []
+            for k, piece in enumerate(t.split("<image>")):
+                if k:
+                    tt, gh, gw = grids[gi]
+                    gi += 1
+                    ids += ([self.vision_start_token_id] + [self.image_token_id] * (tt * gh * gw // self.merge ** 2)
+                            + [self.vision_end_token_id])
+                ids += self.tokenizer._enc(piece)
+            rows.append(ids)
+        assert gi == len(grids), f"{len(grids)} images for {gi} <image> tags"
+        assert len(rows) == 1 or return_tensors != "pt", "batched image prompts are tokenised one at a time"
+        out = {"input_ids": torch.tensor(rows, dtype=torch.long) if return_tensors == "pt" else rows,
+               "attention_mask": torch.ones(1, len(rows[0]), dtype=torch.long) if return_tensors == "pt"
+               else [[1] * len(r) for r in rows]}
+        out.update(enc)
+        return out
+
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=False, **kw):
+        parts = []
+        for m in messages:
+            c = m["content"] if isinstance(m, dict) else m
+            if isinstance(c, list):
+                c = " ".join("<image>" if p.get("type") == "image" else p.get("text", "") for p in c)
+            parts.append(str(c))
+        text = " ".join(parts)
+        return self.tokenizer._enc(text) if tokenize else text
+
+    def decode(self, ids, skip_special_tokens=False):
+        return self.tokenizer.decode(ids, skip_special_tokens)
+
+    def batch_decode(self, seqs, skip_special_tokens=False):
+        return self.tokenizer.batch_decode(seqs, skip_special_tokens)
+
+    def encode(self, text, add_special_tokens=False):
+        return self.tokenizer.encode(text)
+
+    def save_pretrained(self, path):
+        self.tokenizer.save_pretrained(path)
+
+
 def get_tokenizer(pretrain, model=None, padding_side="left", strategy=None, use_fast=True):
     """HF tokenizer (or processor for VLMs) with pad = eos when no pad token exists; architecture presets and
     checkpoints without tokenizer files get the synthetic integer tokenizer."""
@@ -108,7 +206,7 @@ def get_tokenizer(pretrain, model=None, padding_side="left", strategy=None, use_
             cfg = ModelConfig.from_pretrained(pretrain)
         tok = SyntheticTokenizer(cfg.vocab_size, cfg.eos_token_id, cfg.pad_token_id)
         tok.padding_side = padding_side
-        return tok
+        return SyntheticProcessor(tok, cfg) if cfg.is_vlm else tok
     is_vlm = getattr(model, "is_vlm", False) if model is not None else is_vlm_model(pretrain)
     if is_vlm:
         from transformers import AutoProcessor

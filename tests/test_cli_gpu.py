@@ -29,6 +29,13 @@ VARIANTS = {
         "--vllm.enable_sleep", "--reward.remote_url", "examples/python/reward_func.py",
         "--critic.num_nodes", "1", "--critic.num_gpus_per_node", "1",
         "--algo.advantage.estimator", "gae", "--rollout.n_samples_per_prompt", "2", "--critic.adam.lr", "1e-5"],
+    "vlm_reinforce_baseline": [
+        "--actor.model_name_or_path", "tiny-qwen2-vl", "--actor.freeze_visual_encoder",
+        "--data.prompt_dataset", "synthetic://vlm_prompts?n=64&len=24&vocab=2000&image=56",
+        "--data.image_key", "images", "--data.max_images_per_prompt", "1",
+        "--reward.remote_url", "examples/python/reward_func.py",
+        "--algo.advantage.estimator", "reinforce_baseline", "--rollout.n_samples_per_prompt", "4",
+        "--algo.kl.init_coef", "1e-3", "--algo.kl.use_loss", "--algo.kl.estimator", "k2"],
     "async_multiturn_agent": [
         "--train.agent_func_path", "examples/python/agent_func.py", "--train.async_enable",
         "--algo.advantage.estimator", "group_norm", "--rollout.n_samples_per_prompt", "4"],

@@ -119,3 +119,24 @@ def test_vision_tower_gets_gradients():
     g = m.p("visual.blocks.0.attn.qkv.weight").grad
     assert g is not None and g.abs().sum() > 0
     assert m.p("visual.merger.mlp.2.weight").grad.abs().sum() > 0
+
+
+def test_stray_placeholder_token_is_text():
+    """A placeholder id the policy sampled itself (not part of a complete image run) keeps its ordinary embedding and a
+    text position; the real run still receives the tower's rows."""
+    import dataclasses
+
+    from openrlhf_b200.models.config import PRESETS
+    from openrlhf_b200.models.vision import image_runs
+
+    cfg = dataclasses.replace(PRESETS["tiny-qwen2-vl"])
+    IMGT = cfg.image_token_id
+    ids = [5, cfg.vision_start_token_id] + [IMGT] * 4 + [cfg.vision_end_token_id, 7, IMGT, 9]
+    assert image_runs(ids, [(1, 4, 4)], IMGT, 2) == [(2, 4, (1, 4, 4))]
+    pos, delta = mrope_positions(ids, [(1, 4, 4)], IMGT, 2)
+    assert pos[:, -3:].tolist() == [[5, 6, 7]] * 3 and delta == 8 - len(ids)
+    m = TransformerLM(cfg, device="cpu", dtype=torch.float32, seed=3)
+    t = torch.tensor(ids)
+    emb, _ = m.multimodal_inputs(t, [0, len(ids)], torch.randn(16, 1176), torch.tensor([[1, 4, 4]]))
+    plain = m.p("embed.weight")[t]
+    assert torch.equal(emb[8], plain[8]) and not torch.equal(emb[2], plain[2])
