@@ -27,10 +27,19 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
 
     def create_module(self, spec):
         real = _TARGET + spec.name[len("openrlhf"):]
-        return importlib.import_module(real)
+        mod = importlib.import_module(real)
+        self._real_specs[id(mod)] = mod.__spec__
+        return mod
 
     def exec_module(self, module):
+        # the import machinery has just stamped the alias spec on the (shared) module object: put the real one back so
+        # that relative imports inside the module keep resolving against its real package
+        real = self._real_specs.get(id(module))
+        if real is not None:
+            module.__spec__ = real
         return None
+
+    _real_specs: dict = {}
 
 
 if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):

@@ -152,3 +152,33 @@ def test_example_executors_pass_the_worker_type_check(fname):
 
     cls = load_python_object(os.path.join(EX, fname), "AgentExecutor")
     assert issubclass(cls, AgentExecutorBase)
+
+
+def test_vlm_multiturn_agent_accumulates_images():
+    from openrlhf_b200.models.config import PRESETS
+    from openrlhf_b200.models.vision import image_runs
+    from openrlhf_b200.utils.utils import get_tokenizer
+    from openrlhf_b200.datasets.utils import synthetic_dataset
+
+    proc = get_tokenizer("tiny-qwen2-vl")
+    cfg = PRESETS["tiny-qwen2-vl"]
+    row = synthetic_dataset("synthetic://vlm_prompts?n=1&len=5&vocab=2000&image=56")[0]
+    ex = load_python_object(os.path.join(EX, "vlm_multiturn_agent.py"), "AgentExecutor")()
+
+    class Eng:
+        calls = []
+
+        async def generate(self, token_ids, sampling_params, multi_modal_data=None):
+            self.calls.append((len(token_ids), len(multi_modal_data["image"]) if multi_modal_data else 0))
+            ids = [1, 2]
+            out = SimpleNamespace(token_ids=ids, text="1 2", logprobs=[-0.1, -0.2], finish_reason="stop")
+            return SimpleNamespace(outputs=[out])
+
+    eng = Eng()
+    res = asyncio.run(ex.execute(row["input"], row["label"], _sp(max_tokens=8), 512, proc, eng, images=row["images"]))
+    assert [c[1] for c in eng.calls] == [1, 2, 3, 4]              # one more picture every turn
+    mm = res["mm_train_inputs"]
+    assert mm["image_grid_thw"].tolist() == [[1, 4, 4]] * 4 and mm["pixel_values"].shape == (64, 1176)
+    runs = image_runs(res["observation_tokens"], [tuple(g) for g in mm["image_grid_thw"].tolist()],
+                      cfg.image_token_id, 2)
+    assert len(runs) == 4 and len(res["action_ranges"]) == 4
