@@ -69,7 +69,7 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
+    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
                                                          "rmsnorm", "adamw"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
@@ -105,6 +105,19 @@ def main():
         fl = 2.0 * M * N * K
         print(f"gemm_fp8 M{M} N{N} K{K} bn{a.bn}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
               f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak; nominal fp8 peak is twice the bf16 one)")
+    elif a.kernel == "gemm_swiglu":
+        # --n is the intermediate size I: y[M, I] = swiglu(x[M, K] @ w[2I, K]^T), fused vs GEMM + separate kernel
+        from openrlhf_b200.ops.gemm import gemm_swiglu
+        M, I, K = a.m, a.n, a.k
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(2 * I, K, device=dev, dtype=torch.bfloat16)
+        fl = 2.0 * M * 2 * I * K
+        for name, fn in (("fused (y only)", lambda: gemm_swiglu(x, w, bn=a.bn)),
+                         ("fused (y + gate_up)", lambda: gemm_swiglu(x, w, want_gate_up=True, bn=a.bn)),
+                         ("gemm + swiglu kernel", lambda: F.swiglu(gemm(x, w, bn=a.bn)))):
+            t = _time(fn, a.iters)
+            print(f"gemm_swiglu M{M} I{I} K{K} bn{a.bn} {name}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
+                  f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
     elif a.kernel in ("gemm", "gemm_splitk"):
         M, N, K = a.m, a.n, a.k
         a_mn, b_mn = a.layout == "tn", a.layout in ("nn", "tn")

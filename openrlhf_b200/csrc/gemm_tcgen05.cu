@@ -49,6 +49,13 @@ struct GemmParams {
   // fp8 (e4m3) operands, both K-major: a k-block is 128 elements (still 128 bytes per row), MMA kind::f8f6f4
   int fp8;
   const float* alpha_dev;    // optional device scalar multiplied into alpha (product of the two quantisation scales)
+  // SwiGLU epilogue (K-major B = [gate rows | up rows], N = 2 * sw_half): a tile multiplies BN/2 gate rows and the
+  // BN/2 up rows of the same columns (two TMA boxes per stage), and the epilogue writes silu(gate) * up to
+  // C[M, sw_half]; C2 (optional, [M, ldc2]) receives the bf16 gate / up values for the backward pass
+  int swiglu;
+  int sw_half;
+  __nv_bfloat16* C2;
+  int ldc2;
 };
 
 // Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
@@ -173,7 +180,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           const int brow = p.group_mode == 1 ? grp * p.group_b_rows : 0;   // this group's block of the stacked B
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * bke, brow + n_blk * BN);
+            if (p.swiglu) {
+              tma_load_2d(sb, &tma_b, &full_bar[stage], kb * bke, n_blk * (BN / 2));
+              tma_load_2d(sb + (BN / 2) * 128, &tma_b, &full_bar[stage], kb * bke, p.sw_half + n_blk * (BN / 2));
+            } else {
+              tma_load_2d(sb, &tma_b, &full_bar[stage], kb * bke, brow + n_blk * BN);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -223,6 +235,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else {
     // ------------------------------------------------------------ epilogue (4 warps, 32 TMEM lanes each)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+    // 32-byte stores need 32-byte aligned rows: base pointer and leading dimension (bf16 elements) both allow it
+    const bool wide_c = !p.out_f32 && (p.ldc % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
+    const bool wide_c2 = p.C2 != nullptr && (p.ldc2 % 16 == 0) && (p.sw_half % 16 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(p.C2) & 31) == 0);
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -237,6 +253,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool has_work = kb1 > kb0;
       const float alpha = p.alpha_dev != nullptr ? p.alpha * *p.alpha_dev : p.alpha;
+      if (p.swiglu) {
+        // TMEM columns [0, BN/2) hold the gate products, [BN/2, BN) the up products of the same output columns
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, g);
+          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          const int col0 = n_blk * (BN / 2) + c * 32;
+          if (row_ok && has_work && col0 < p.sw_half) {
+            __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 16) {
+              // sw_half is a multiple of BN / 2 >= 64: a 32-column chunk is never ragged
+              uint4 o[2], og[2], ou[2];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const int jj = j + 8 * hh;
+                float y[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const float gv = __uint_as_float(g[jj + q]);
+                  y[q] = gv / (1.f + __expf(-gv)) * __uint_as_float(u[jj + q]);
+                }
+                o[hh].x = pack_bf16x2(y[0], y[1]);
+                o[hh].y = pack_bf16x2(y[2], y[3]);
+                o[hh].z = pack_bf16x2(y[4], y[5]);
+                o[hh].w = pack_bf16x2(y[6], y[7]);
+                og[hh].x = pack_bf16x2(__uint_as_float(g[jj]), __uint_as_float(g[jj + 1]));
+                og[hh].y = pack_bf16x2(__uint_as_float(g[jj + 2]), __uint_as_float(g[jj + 3]));
+                og[hh].z = pack_bf16x2(__uint_as_float(g[jj + 4]), __uint_as_float(g[jj + 5]));
+                og[hh].w = pack_bf16x2(__uint_as_float(g[jj + 6]), __uint_as_float(g[jj + 7]));
+                ou[hh].x = pack_bf16x2(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]));
+                ou[hh].y = pack_bf16x2(__uint_as_float(u[jj + 2]), __uint_as_float(u[jj + 3]));
+                ou[hh].z = pack_bf16x2(__uint_as_float(u[jj + 4]), __uint_as_float(u[jj + 5]));
+                ou[hh].w = pack_bf16x2(__uint_as_float(u[jj + 6]), __uint_as_float(u[jj + 7]));
+              }
+              if (wide_c) {
+                st_global_256(yrow + j, o[0], o[1]);
+              } else {
+                *reinterpret_cast<uint4*>(yrow + j) = o[0];
+                *reinterpret_cast<uint4*>(yrow + j + 8) = o[1];
+              }
+              if (p.C2 != nullptr) {
+                __nv_bfloat16* grow = p.C2 + (size_t)row * p.ldc2 + col0 + j;
+                if (wide_c2) {
+                  st_global_256(grow, og[0], og[1]);
+                  st_global_256(grow + p.sw_half, ou[0], ou[1]);
+                } else {
+                  *reinterpret_cast<uint4*>(grow) = og[0];
+                  *reinterpret_cast<uint4*>(grow + 8) = og[1];
+                  *reinterpret_cast<uint4*>(grow + p.sw_half) = ou[0];
+                  *reinterpret_cast<uint4*>(grow + p.sw_half + 8) = ou[1];
+                }
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -275,37 +350,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           } else {
             __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j < p.N) {
-                float v[8];
+            for (int j = 0; j < 32; j += 16) {
+              uint4 o[2];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]) * alpha;
-                if (p.bias != nullptr) {
-                  uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
-                  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+              for (int hh = 0; hh < 2; ++hh) {
+                const int jj = j + 8 * hh;
+                if (col0 + jj < p.N) {
+                  float v[8];
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    float2 f = __bfloat1622float2(b2[q]);
-                    v[2 * q] += f.x;
-                    v[2 * q + 1] += f.y;
+                  for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[jj + q]) * alpha;
+                  if (p.bias != nullptr) {
+                    uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + jj);
+                    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                      float2 f = __bfloat1622float2(b2[q]);
+                      v[2 * q] += f.x;
+                      v[2 * q + 1] += f.y;
+                    }
                   }
-                }
-                if (p.residual != nullptr) {
-                  uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldc + col0 + j);
-                  const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+                  if (p.residual != nullptr) {
+                    uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldc + col0 + jj);
+                    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    float2 f = __bfloat1622float2(r2[q]);
-                    v[2 * q] += f.x;
-                    v[2 * q + 1] += f.y;
+                    for (int q = 0; q < 4; ++q) {
+                      float2 f = __bfloat1622float2(r2[q]);
+                      v[2 * q] += f.x;
+                      v[2 * q + 1] += f.y;
+                    }
                   }
+                  o[hh].x = pack_bf16x2(v[0], v[1]);
+                  o[hh].y = pack_bf16x2(v[2], v[3]);
+                  o[hh].z = pack_bf16x2(v[4], v[5]);
+                  o[hh].w = pack_bf16x2(v[6], v[7]);
                 }
-                uint4 o;
-                o.x = pack_bf16x2(v[0], v[1]);
-                o.y = pack_bf16x2(v[2], v[3]);
-                o.z = pack_bf16x2(v[4], v[5]);
-                o.w = pack_bf16x2(v[6], v[7]);
-                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+              if (wide_c && col0 + j + 16 <= p.N) {
+                st_global_256(crow + j, o[0], o[1]);          // one full 32-byte sector per thread
+              } else {
+                if (col0 + j < p.N) *reinterpret_cast<uint4*>(crow + j) = o[0];
+                if (col0 + j + 8 < p.N) *reinterpret_cast<uint4*>(crow + j + 8) = o[1];
               }
             }
           }
@@ -492,6 +576,39 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   if (bn == 128) { B200_DISPATCH(128) }
   B200_DISPATCH(64)
 #undef B200_DISPATCH
+}
+
+
+// Y[M, I] = silu(A W_gate^T) * (A W_up^T) with W = [gate rows | up rows] ([2I, K], K-major); GU (optional, [M, ldgu])
+// receives the bf16 gate / up products for the backward pass. I must be a multiple of bn / 2.
+extern "C" int b200_gemm_bf16_swiglu(const void* A, const void* W, void* Y, void* GU, int M, int I, int K, int lda,
+                                     int ldb, int ldy, int ldgu, int bn, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if (bn != 128 && bn != 256) bn = ((long long)M * 2 * I >= (long long)128 * 256 * 148) ? 256 : 128;
+  if ((lda % 8) || (ldb % 8) || (ldy % 8) || (I % (bn / 2)) || (GU != nullptr && (ldgu % 8))) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y) |
+       reinterpret_cast<uintptr_t>(GU)) & 15) return -12;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tb, W, 2 * I, K, ldb, bn / 2, BK);      // two boxes of bn/2 rows per stage
+  if (r) return r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = Y;
+  p.M = M; p.N = 2 * I; p.K = K; p.ldc = ldy;
+  p.k_splits = 1; p.alpha = 1.f; p.status = status;
+  p.swiglu = 1; p.sw_half = I;
+  p.C2 = reinterpret_cast<__nv_bfloat16*>(GU); p.ldc2 = ldgu;
+  static PeerMaps no_peers;
+  if (bn == 256) return launch<256, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
+  return launch<128, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
 }
 
 

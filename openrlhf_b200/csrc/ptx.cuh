@@ -259,6 +259,15 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---------------------------------------------------------------- 256-bit global store
+// One 32-byte store per thread fills whole 32-byte sectors even when the threads of a warp write different rows
+// (epilogues where a thread owns a row). The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_256(void* ptr, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // A kernel launched with launch_pdl() may start while its predecessor in the stream is still running; it must call
 // pdl_wait() before it touches memory the predecessor writes (or reads), and calls pdl_launch_dependents() as early

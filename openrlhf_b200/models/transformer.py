@@ -204,8 +204,10 @@ class TransformerLM(nn.Module):
             y, aux = moe_forward(x, self.p(pre + "router.weight"), self.p(pre + "experts.gate_up"),
                                  self.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob, ep=self.ep)
             return h + y, aux
-        gu = self._lin(i, "gate_up", x)
-        a = F.swiglu(gu)
+        if self.lora is None:
+            a = F.linear_swiglu(x, self.p(pre + "gate_up.weight"))      # activation fused into the GEMM epilogue
+        else:
+            a = F.swiglu(self._lin(i, "gate_up", x))
         return self._lin(i, "down", a, None, h), None
 
     def _layer(self, i, h, pos, cu_seqlens, max_seqlen, attn_fn=None):

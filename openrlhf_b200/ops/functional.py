@@ -184,6 +184,48 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(gu.contiguous())
 
 
+class _LinearSwiGLU(torch.autograd.Function):
+    """y = swiglu(x @ w.T) with the activation in the GEMM epilogue; the bf16 gate / up products are written next to
+    y only when a backward pass will need them."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from .gemm import gemm_swiglu
+
+        need = any(ctx.needs_input_grad)
+        y, gu = gemm_swiglu(x, w, want_gate_up=need)
+        ctx.save_for_backward(x, w, gu)
+        ctx.w_ref = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, gu = ctx.saved_tensors
+        dy = dy.contiguous()
+        dgu = torch.empty_like(gu)
+        rc = _L().b200_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dy), _lib.ptr(dgu), _c_ll(gu.shape[0]),
+                                  _c_int(gu.shape[1] // 2), _lib.stream_ptr())
+        _lib.check_rc(rc, "swiglu_bwd")
+        dx = gemm(dgu, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            T = x.shape[0]
+            tiles = ((w.shape[0] + 127) // 128) * ((w.shape[1] + 255) // 256)
+            splits = max(1, min(8, 148 // max(tiles, 1), T // 512)) if tiles < 148 else 1
+            dw = _acc_grad(ctx.w_ref, lambda buf: gemm(dgu, x, a_mn=True, b_mn=True, out=buf, accumulate=True,
+                                                       k_splits=splits))
+        return dx, dw
+
+
+def linear_swiglu(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """swiglu(x @ w.T) for w = [gate rows | up rows]; one kernel on the GPU when the shapes allow it."""
+    from .gemm import swiglu_fusable
+
+    if x.is_cuda and x.dtype == torch.bfloat16 and swiglu_fusable(w.shape[0] // 2) and x.stride(1) == 1:
+        return _LinearSwiGLU.apply(x, w)
+    return swiglu(linear(x, w))
+
+
 # ---------------------------------------------------------------------------------------------- embedding
 class _Embedding(torch.autograd.Function):
     @staticmethod

@@ -76,6 +76,32 @@ def gemm(
     return out
 
 
+def gemm_swiglu(x: torch.Tensor, w: torch.Tensor, want_gate_up: bool = False, bn: int = 0):
+    """silu(x @ w[:I].T) * (x @ w[I:].T) in one kernel: the gate and up products of the same output columns share a
+    tile and the SwiGLU runs in the GEMM epilogue on the fp32 accumulators. x [M, K], w [2I, K] (gate rows, then up
+    rows). Returns (y [M, I], gate_up [M, 2I] bf16 or None: the products the backward pass needs)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    M, K = x.shape
+    I = w.shape[0] // 2
+    assert w.shape == (2 * I, K) and swiglu_fusable(I)
+    y = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=x.device) if want_gate_up else None
+    if M == 0:
+        return y, gu
+    st = _lib.status_word(x.device)
+    rc = _lib.lib().b200_gemm_bf16_swiglu(
+        _lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(gu), ctypes.c_int(M), ctypes.c_int(I), ctypes.c_int(K),
+        ctypes.c_int(x.stride(0)), ctypes.c_int(w.stride(0)), ctypes.c_int(I), ctypes.c_int(2 * I), ctypes.c_int(bn),
+        _lib.ptr(st), _lib.stream_ptr())
+    _lib.check_rc(rc, "b200_gemm_bf16_swiglu")
+    return y, gu
+
+
+def swiglu_fusable(intermediate: int) -> bool:
+    """The fused kernel pairs 128-row (or 64-row) blocks of the gate and up matrices."""
+    return intermediate % 128 == 0
+
+
 _splitk_ws: dict = {}
 _splitk_retired: list = []  # outgrown buffers stay alive: captured CUDA graphs may still point at them
 

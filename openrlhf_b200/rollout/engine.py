@@ -25,7 +25,7 @@ from ..models.transformer import TransformerLM
 from ..ops import _lib
 from ..ops import functional as F
 from ..ops.attention import PAGE, paged_decode, rope_kvwrite
-from ..ops.gemm import gemm
+from ..ops.gemm import gemm, gemm_swiglu, swiglu_fusable
 from ..ops.sampling import sample
 from .block_manager import BlockManager
 
@@ -343,8 +343,11 @@ class RolloutEngine:
             ws, s = gemm_to_workspace(attn_buf.view(B, Hq * 128), m.p(pre + "o.weight"),
                                       tp.ws[0] if tp is not None else None)
             h, x = reduce_norm(ws, s, h, m.p(pre + "norm2.weight"), 0)
-            gu = gemm(x, m.p(pre + "gate_up.weight"), bn=128)
-            a = F.swiglu(gu)
+            wgu = m.p(pre + "gate_up.weight")
+            if swiglu_fusable(wgu.shape[0] // 2):
+                a, _ = gemm_swiglu(x, wgu, bn=128)          # SwiGLU in the GEMM epilogue: one launch less per layer
+            else:
+                a = F.swiglu(gemm(x, wgu, bn=128))
             ws, s = gemm_to_workspace(a, m.p(pre + "down.weight"), tp.ws[1] if tp is not None else None)
             nxt = m.p(f"layers.{i + 1}.norm1.weight") if i + 1 < nl else m.p("norm.weight")
             h, x = reduce_norm(ws, s, h, nxt, 1)

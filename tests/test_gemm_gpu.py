@@ -88,3 +88,36 @@ def test_gemm_e4m3_matches_dequantised_reference(M, N, K):
     full = a.float() @ b.float().t() + bias.float()
     rel = ((y.float() - full).norm() / full.norm()).item()
     assert rel < 6e-2, rel
+
+
+@pytest.mark.parametrize("M,I,K,bn", [(128, 8960, 1536, 128), (1000, 512, 256, 0), (4096, 1024, 1536, 256),
+                                      (37, 128, 72, 128), (10240, 8960, 1536, 0)])
+def test_gemm_swiglu_epilogue(M, I, K, bn):
+    """SwiGLU fused into the GEMM epilogue (two B boxes per stage) against fp32 PyTorch; the optional gate / up output
+    and the autograd wrapper against the unfused composition."""
+    from openrlhf_b200.ops import _lib
+    from openrlhf_b200.ops import functional as F
+    from openrlhf_b200.ops.gemm import gemm_swiglu
+
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda") / K ** 0.5).bfloat16()
+    y, gu = gemm_swiglu(x, w, want_gate_up=True, bn=bn)
+    _lib.check_status()
+    ref_gu = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(ref_gu[:, :I]) * ref_gu[:, I:]
+    assert (gu.float() - ref_gu).abs().max().item() < 0.02 * ref_gu.abs().max().item()
+    assert (y.float() - ref).abs().max().item() < 0.02 * ref.abs().max().item()
+    y2, none = gemm_swiglu(x, w, bn=bn)
+    assert none is None and torch.equal(y, y2)
+    if M > 2000:
+        return
+    # autograd: same gradients as linear followed by the separate SwiGLU kernel
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    dy = torch.randn(M, I, device="cuda", dtype=torch.bfloat16)
+    F.linear_swiglu(xa, wa).backward(dy)
+    F.swiglu(F.linear(xb, wb)).backward(dy)
+    _lib.check_status()
+    assert (xa.grad.float() - xb.grad.float()).abs().max().item() <= 0.02 * xb.grad.float().abs().max().item()
+    assert (wa.grad.float() - wb.grad.float()).abs().max().item() <= 0.02 * wb.grad.float().abs().max().item()
