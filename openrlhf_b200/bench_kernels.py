@@ -184,6 +184,18 @@ def main():
             t = _time(lambda: F.rmsnorm(x, w, 1e-6), a.iters)
         byt = 4.0 * T * H
         print(f"rmsnorm T{T} H{H}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+        # backward: reads x and dy, writes dx (the fp32 weight gradient is H floats)
+        import ctypes
+
+        dy, dx = torch.randn_like(x), torch.empty_like(x)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+        dw = torch.zeros(H, device=dev)
+        L = _lib.lib()
+        bwd = lambda: L.b200_rmsnorm_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(dy), _lib.ptr(rstd), None, _lib.ptr(dx),
+                                         _lib.ptr(dw), ctypes.c_int(T), ctypes.c_int(H), _lib.stream_ptr())
+        t = _time(bwd, a.iters)
+        byt = 6.0 * T * H
+        print(f"rmsnorm_bwd T{T} H{H}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
     elif a.kernel == "adamw":
         import ctypes
 

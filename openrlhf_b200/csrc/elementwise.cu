@@ -95,6 +95,146 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// Warp-per-row variant for H <= 32 * 8 * MAXV: the row stays in registers, the reduction is a shuffle, and a warp has
+// all of its row's loads in flight at once (one CTA per row with a block-wide reduction left too few bytes in flight
+// per SM to approach the HBM rate).
+template <int MAXV>
+__global__ void __launch_bounds__(512)
+rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                        __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int T, int H, int ldx, int ldy,
+                        float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int nvec = H >> 3;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < T; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * ldx) : nullptr;
+    uint4 c[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) c[i] = xr[v];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float f[8];
+        unpack8(c[i], f);
+        if (rr) {
+          float g[8];
+          unpack8(rr[v], g);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) f[q] = round_bf16(f[q] + g[q]);
+          c[i] = pack8(f);
+          reinterpret_cast<uint4*>(h_out + (size_t)row * ldx)[v] = c[i];
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) ss += f[q] * f[q];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float f[8], g[8];
+        unpack8(c[i], f);
+        unpack8(reinterpret_cast<const uint4*>(w)[v], g);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = round_bf16(f[q] * rstd) * g[q];
+        yr[v] = pack8(f);
+      }
+    }
+  }
+}
+
+// Backward, warp per row (H <= 2048): x and dy of the row stay in registers between the dot product and the dx pass,
+// each lane accumulates the weight gradient of its own columns in registers over all of the warp's rows; the CTA's
+// warps are summed in shared memory and one atomic per column and CTA reaches the fp32 gradient.
+template <int MAXV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                        const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw, int T, int H) {
+  extern __shared__ float dw_acc[];  // H floats
+  const int nvec = H >> 3;
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_acc[i] = 0.f;
+  __syncthreads();
+  float acc[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < T; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    uint4 cx[MAXV], cd[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        cx[i] = xr[v];
+        cd[i] = dyr[v];
+      }
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float fx[8], fd[8], fw[8];
+        unpack8(cx[i], fx);
+        unpack8(cd[i], fd);
+        unpack8(reinterpret_cast<const uint4*>(w)[v], fw);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dot += fd[q] * fw[q] * fx[q];
+      }
+    }
+    dot = warp_sum(dot);
+    const float cc = dot * rstd * rstd * rstd / (float)H;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float fx[8], fd[8], fw[8], o[8];
+        unpack8(cx[i], fx);
+        unpack8(cd[i], fd);
+        unpack8(reinterpret_cast<const uint4*>(w)[v], fw);
+        if (dres_in) unpack8(reinterpret_cast<const uint4*>(dres_in + (size_t)row * H)[v], o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float g = fd[q] * fw[q] * rstd - fx[q] * cc;
+          o[q] = dres_in ? o[q] + g : g;
+          acc[i][q] += fd[q] * round_bf16(fx[q] * rstd);
+        }
+        reinterpret_cast<uint4*>(dx + (size_t)row * H)[v] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) atomicAdd(&dw_acc[v * 8 + q], acc[i][q]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) atomicAdd(dw + i, dw_acc[i]);
+}
+
 // dx = rstd * (dy*w) - x * rstd^3 * mean(dy*w*x)  (+ dres_in);  dw += sum_rows dy * (x*rstd)
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
@@ -317,6 +457,18 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, v
                                 int T, int H, int ldx, int ldy, float eps, void* stream) {
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8 || ldy % 8 || H > 16384) return -10;
+  if (H <= 32 * 8 * 24 && T >= 512) {
+    // warp per row, 16 rows per CTA, two CTAs per SM in flight
+    const int ctas = (T + 15) / 16 < 148 * 2 ? (T + 15) / 16 : 148 * 2;
+#define B200_NORM_FWD(MAXV_)                                                                                      \
+    return launch_pdl(rmsnorm_fwd_warp_kernel<MAXV_>, dim3(ctas), dim3(512), (size_t)0, STREAM(stream),            \
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,                 \
+                      (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, T, H, ldx, ldy, eps) == cudaSuccess ? 0 : -3;
+    if (H <= 32 * 8 * 8) { B200_NORM_FWD(8) }
+    if (H <= 32 * 8 * 16) { B200_NORM_FWD(16) }
+    B200_NORM_FWD(24)
+#undef B200_NORM_FWD
+  }
   int grid = T < 148 * 8 ? T : 148 * 8;
   return launch_pdl(rmsnorm_fwd_kernel, dim3(grid), dim3(NORM_THREADS), (size_t)(H / 8) * sizeof(uint4), STREAM(stream),
                     (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
@@ -326,6 +478,13 @@ extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* dy, co
                                 void* dx, float* dw, int T, int H, void* stream) {
   if (T <= 0) return 0;
   if (H % 8 || H > 11264) return -10;
+  if (H <= 32 * 8 * 8 && T >= 512) {
+    const int ctas = (T + 7) / 8 < 148 ? (T + 7) / 8 : 148;   // 254 registers per thread: one CTA per SM
+    rmsnorm_bwd_warp_kernel<8><<<ctas, 256, H * sizeof(float), STREAM(stream)>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres_in,
+        (__nv_bfloat16*)dx, dw, T, H);
+    return LAUNCH_OK();
+  }
   int grid = T < 148 * 2 ? T : 148 * 2;
   rmsnorm_bwd_kernel<<<grid, NORM_THREADS, H * sizeof(float), STREAM(stream)>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (const __nv_bfloat16*)dres_in,

@@ -237,6 +237,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
     // 32-byte stores need 32-byte aligned rows: base pointer and leading dimension (bf16 elements) both allow it
     const bool wide_c = !p.out_f32 && (p.ldc % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
+    // fp32 outputs: rows and slabs 32-byte aligned (8 floats)
+    const bool wide_f = p.out_f32 && (p.ldc % 8 == 0) && (p.split_stride % 8 == 0) && (p.group_c_stride % 8 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
     const bool wide_c2 = p.C2 != nullptr && (p.ldc2 % 16 == 0) && (p.sw_half % 16 == 0) &&
                          ((reinterpret_cast<uintptr_t>(p.C2) & 31) == 0);
     int local = 0;
@@ -323,6 +326,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             float* crow = reinterpret_cast<float*>(p.C) +
                           (p.group_mode == 2 ? (size_t)grp * p.group_c_stride : (size_t)(tile % splits) * p.split_stride) +
                           (size_t)row * p.ldc + col0;
+            if (wide_f && p.n_peer_c == 0 && !p.accumulate && col0 + 32 <= p.N) {
+              // plain fp32 tile (split-K slabs of the decode path): 32-byte stores, whole sectors per thread
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 lo, hi;
+                lo.x = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                lo.y = __float_as_uint(__uint_as_float(r[j + 1]) * alpha);
+                lo.z = __float_as_uint(__uint_as_float(r[j + 2]) * alpha);
+                lo.w = __float_as_uint(__uint_as_float(r[j + 3]) * alpha);
+                hi.x = __float_as_uint(__uint_as_float(r[j + 4]) * alpha);
+                hi.y = __float_as_uint(__uint_as_float(r[j + 5]) * alpha);
+                hi.z = __float_as_uint(__uint_as_float(r[j + 6]) * alpha);
+                hi.w = __float_as_uint(__uint_as_float(r[j + 7]) * alpha);
+                st_global_256(crow + j, lo, hi);
+              }
+            } else
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col0 + j < p.N) {

@@ -13,10 +13,11 @@ def _close(a, b, rtol=2e-2, atol=2e-2):
     assert err <= rtol * ref + atol, f"max err {err} vs ref scale {ref}"
 
 
-def test_rmsnorm_fwd_bwd():
+@pytest.mark.parametrize("T,H", [(333, 1536), (2000, 1536), (1031, 2048), (700, 3584), (600, 5120), (513, 72)])
+def test_rmsnorm_fwd_bwd(T, H):
+    """Covers the block-per-row kernels (few rows, or wide rows in the backward) and the warp-per-row kernels."""
     from openrlhf_b200.ops import functional as F, reference as R
     torch.manual_seed(0)
-    T, H = 333, 1536
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_()
     y = F.rmsnorm(x, w, 1e-6)
