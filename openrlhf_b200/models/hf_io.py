@@ -103,6 +103,17 @@ def _select(t: torch.Tensor, sel):
 
 def iter_hf_tensors(model: TransformerLM) -> Iterator[tuple[str, torch.Tensor]]:
     z3 = getattr(model, "z3", None)
+    tpt = getattr(model, "tp_train", None)
+    if tpt is not None:
+        # tensor-parallel shard: rebuild the full fused layout from all shards and name it with the full configuration
+        from .transformer import build_param_specs
+
+        full = tpt.gather_full(model)
+        for spec in build_param_specs(tpt.full_cfg, model.with_lm_head, model.with_value_head):
+            t = full[spec.offset:spec.offset + spec.numel].view(spec.shape)
+            for hf_name, sel in hf_names_for(tpt.full_cfg, spec.name):
+                yield hf_name, _select(t, sel)
+        return
     full = z3.gather_full() if z3 is not None else None     # ZeRO-3: parameters are sharded, gather the logical buffer
     for spec, p in model.named_specs():
         t = p.detach() if full is None else full[spec.offset:spec.offset + spec.numel].view(spec.shape)
@@ -156,7 +167,8 @@ def save_pretrained(model: TransformerLM, path: str, tokenizer=None, extra_confi
             extra.setdefault("normalize_reward", model.cfg.normalize_reward)
             extra.setdefault("mean", model.cfg.mean)
             extra.setdefault("std", model.cfg.std)
-        model.cfg.save_pretrained(path, extra)
+        tpt = getattr(model, "tp_train", None)
+        (tpt.full_cfg if tpt is not None else model.cfg).save_pretrained(path, extra)
         if tokenizer is not None:
             tokenizer.save_pretrained(path)
 

@@ -101,6 +101,7 @@ class TransformerLM(nn.Module):
             self.register_parameter(s.name.replace(".", "__"), p)
         self.gradient_checkpointing = False
         self.tp_group = None   # set on a tensor-parallel shard of the model (rollout/tp_engine.py)
+        self.tp_train = None   # parallel.tp_train.TPTrain: this model is one rank's shard of a TP-trained model
         self.ep = None   # parallel.ep.EPContext: MoE layers run expert-parallel over its group
         self.cp = None   # parallel.cp.CPContext: attention over a context-parallel group (inputs are this rank's rows)
         self.lora = None                      # optional LoraAdapters (models/lora.py)
@@ -152,6 +153,10 @@ class TransformerLM(nn.Module):
             y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, None)
             dist.all_reduce(y, group=self.tp_group)
             return y if residual is None else y + residual
+        if self.tp_train is not None and target in ("o", "down"):
+            # row-parallel shard in training: the sum over the group is differentiable (identity backwards)
+            y = self.tp_train.reduce_out(F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, None))
+            return y if residual is None else y + residual
         y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, residual)
         if self.lora is not None:
             d = self.lora.delta(i, target, x)
@@ -166,6 +171,8 @@ class TransformerLM(nn.Module):
         if isinstance(pos, tuple):          # (row index, per-token rotary rows): multimodal positions
             pos, rope_tab = pos
         x = F.rmsnorm(h, self.p(pre + "norm1.weight"), cfg.rms_norm_eps)
+        if self.tp_train is not None:
+            x = self.tp_train.copy_in(x)        # column-parallel input: gradients are summed over the group
         qkv = self._lin(i, "qkv", x, self._params.get(pre + "qkv.bias"))
         if rope_tab is None:
             rope_tab = self.rope(qkv.device)
@@ -198,6 +205,8 @@ class TransformerLM(nn.Module):
         cfg = self.cfg
         pre = f"layers.{i}."
         x = F.rmsnorm(h, self.p(pre + "norm2.weight"), cfg.rms_norm_eps)
+        if self.tp_train is not None:
+            x = self.tp_train.copy_in(x)
         if cfg.is_moe_layer(i):
             from .moe import moe_forward
 

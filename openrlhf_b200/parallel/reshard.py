@@ -61,10 +61,11 @@ def _tp_row_ranges(name: str, shape, cfg: ModelConfig, tp_rank: int, tp: int):
     return rows_all, cols_all
 
 
-def tp_param_specs(cfg: ModelConfig, tp_rank: int, tp: int, with_lm_head: bool = True) -> list[ParamSpec]:
+def tp_param_specs(cfg: ModelConfig, tp_rank: int, tp: int, with_lm_head: bool = True,
+                   with_value_head: bool = False) -> list[ParamSpec]:
     """Layout of one TP rank's flat buffer (same order and alignment rule as the trainer's)."""
     out, off = [], 0
-    for s in build_param_specs(cfg, with_lm_head):
+    for s in build_param_specs(cfg, with_lm_head, with_value_head):
         if len(s.shape) == 3:          # experts [E, rows, cols]: kept whole (expert parallelism shards by expert)
             shape = s.shape
         else:
@@ -80,13 +81,13 @@ def tp_param_specs(cfg: ModelConfig, tp_rank: int, tp: int, with_lm_head: bool =
 
 
 def build_plan(cfg: ModelConfig, tp_rank: int = 0, tp: int = 1, src_world: int = 1, src_shard_elems: int | None = None,
-               with_lm_head: bool = True) -> tuple[list[CopyEntry], int]:
+               with_lm_head: bool = True, with_value_head: bool = False) -> tuple[list[CopyEntry], int]:
     """Copy plan for one destination TP rank. Sources: `src_world` == 1 (every rank holds the whole flat buffer: read
     locally, source rank 0 in the table the caller passes) or a flat buffer cut into `src_world` slices of
     `src_shard_elems` elements (ZeRO-3: entries are split where a row block crosses a slice boundary).
     Returns (entries, destination buffer size in elements)."""
-    src_specs = build_param_specs(cfg, with_lm_head)
-    dst_specs = tp_param_specs(cfg, tp_rank, tp, with_lm_head)
+    src_specs = build_param_specs(cfg, with_lm_head, with_value_head)
+    dst_specs = tp_param_specs(cfg, tp_rank, tp, with_lm_head, with_value_head)
     entries: list[CopyEntry] = []
 
     def emit(src_off, dst_off, rows, row_elems, src_ld, dst_ld):

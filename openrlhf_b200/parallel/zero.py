@@ -93,8 +93,15 @@ class ZeroEngine:
         self.lo = per * self.rank if zero_stage >= 1 else 0
         self.hi = self.lo + per if zero_stage >= 1 else self.padded
         self.symm = None
+        # tensor-parallel shard (parallel/tp_train.py): replicated parameters are averaged over the TP group before
+        # the step and count once in the clipping norm
+        self.tp = getattr(model, "tp_train", None)
+        self.tp_rep_mask = None
         if not train:
             return
+        if self.tp is not None:
+            assert symm is None, "the peer-memory optimizer step is not combined with tensor-parallel training"
+            self.tp_rep_mask = self.tp.replicated_mask(model, self.lo, self.hi, self.device)
         on_gpu = self.flat.is_cuda
         self.symm = symm if (symm is not None and on_gpu and self.world > 1) else None
         if self.symm is not None:
@@ -146,6 +153,8 @@ class ZeroEngine:
         """One optimizer step. `grad_scale` multiplies the accumulated gradient (1 / accumulation steps)."""
         self.opt_step += 1
         lr = self.current_lr()
+        if self.tp is not None:
+            self.tp.sync_replicated_grads(self.model)
         if self.symm is not None:
             self.symm.step(self, lr, grad_scale)
         elif self.flat.is_cuda:
@@ -170,6 +179,14 @@ class ZeroEngine:
         self.grad_flat /= self.world
         return self.grad_flat
 
+    def _tp_norm_fix(self, g: torch.Tensor, sq: torch.Tensor):
+        """sq holds sum(g^2) of this rank's slice; the TP-wide sum that follows would count replicated parameters
+        tp times: keep 1/tp of their share here."""
+        mask = self.tp_rep_mask if g.numel() == self.tp_rep_mask.numel() else \
+            self.tp.replicated_mask(self.model, 0, g.numel(), g.device)
+        rep = (torch.where(mask, g, torch.zeros((), dtype=g.dtype, device=g.device)).double() ** 2).sum().float()
+        sq -= rep * (1.0 - 1.0 / self.tp.size)
+
     def _gather_params(self):
         if self.world > 1 and self.zero_stage >= 1:
             dist.all_gather_into_tensor(self.flat[: self.padded], self.flat[self.lo:self.hi].clone(), group=self.group)
@@ -181,8 +198,12 @@ class ZeroEngine:
         st = _lib.stream_ptr()
         self.scalars.zero_()
         _lib.check_rc(L.b200_sumsq(_lib.ptr(g), ctypes.c_longlong(n), _lib.ptr(self.scalars), st), "sumsq")
+        if self.tp is not None:
+            self._tp_norm_fix(g, self.scalars[:1])
         if self.world > 1 and self.zero_stage >= 1:
             dist.all_reduce(self.scalars[:1], group=self.group)
+        if self.tp is not None:
+            dist.all_reduce(self.scalars[:1], group=self.tp.group)
         _lib.check_rc(L.b200_clip_coef(_lib.ptr(self.scalars), ctypes.c_float(self.max_norm or 0.0),
                                        ctypes.c_float(grad_scale), st), "clip_coef")
         self._adam_cuda(g, lr, zero_grad=self.world == 1)
@@ -215,8 +236,12 @@ class ZeroEngine:
         """PyTorch restatement (CPU ranks / gloo): same arithmetic as the kernels."""
         g = self._reduce_grads()
         sq = (g.double() ** 2).sum().float().reshape(1)
+        if self.tp is not None:
+            self._tp_norm_fix(g, sq)
         if self.world > 1 and self.zero_stage >= 1:
             dist.all_reduce(sq, group=self.group)
+        if self.tp is not None:
+            dist.all_reduce(sq, group=self.tp.group)
         norm = sq.sqrt().item() * grad_scale
         coef = 1.0
         if self.max_norm and norm > self.max_norm:

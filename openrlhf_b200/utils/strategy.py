@@ -102,6 +102,26 @@ def _inner_lm(module):
     raise TypeError("object does not wrap a TransformerLM")
 
 
+def _replace_inner_lm(module, new_lm):
+    """Swap the TransformerLM held by an Actor / reward / critic wrapper (or return new_lm for a bare model)."""
+    m = module
+    for _ in range(4):
+        for attr in ("module", "model"):
+            child = m.__dict__.get(attr) or getattr(m, "_modules", {}).get(attr)
+            if child is None:
+                continue
+            if hasattr(child, "specs") and hasattr(child, "flat"):
+                setattr(m, attr, new_lm)
+                return module
+            m = child
+            break
+        else:
+            break
+    if hasattr(module, "specs") and hasattr(module, "flat"):
+        return new_lm
+    raise TypeError("object does not wrap a TransformerLM")
+
+
 class Strategy:
     CKPT_METRIC_FILENAME = ckpt.METRIC_FILE
 
@@ -175,10 +195,24 @@ class Strategy:
         Returns the prepared object(s): modules with ``.engine`` attached."""
         self.is_rlhf = is_rlhf
         out = []
+        tp = self.ds_tensor_parallel_size if self.world_size > 1 else 1
+
+        def tp_shard(module):
+            """--ds.tensor_parallel_size: replace the full model by this rank's shard (parallel/tp_train.py)."""
+            from ..parallel.tp_train import shard_for_training
+
+            full = _inner_lm(module)
+            if getattr(full, "tp_train", None) is not None:
+                return module
+            shard = shard_for_training(full, self.mesh.group("tp"), shard_world=self.mesh.dp)
+            return _replace_inner_lm(module, shard)
+
         for arg in models_or_model_optim_pairs:
             if isinstance(arg, tuple):
                 module, cfg = arg
                 cfg = dict(cfg or {})
+                if tp > 1:
+                    module = tp_shard(module)
                 lm = _inner_lm(module)
                 sched = LRScheduler(cfg.get("lr", 1e-6), cfg.get("max_steps", 1000), cfg.get("lr_warmup_ratio", 0.03),
                                     cfg.get("min_lr_ratio", 0.1), cfg.get("lr_scheduler", "cosine_with_min_lr"))
@@ -191,7 +225,8 @@ class Strategy:
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
                                      max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched,
                                      ns_steps=mu.get("ns_steps", 5), nesterov=mu.get("nesterov", True))
-                elif self.stage == 3 and self.world_size > 1 and self.ring_attn_size == 1 and getattr(lm, "lora", None) is None:
+                elif (self.stage == 3 and self.world_size > 1 and self.ring_attn_size == 1 and tp == 1
+                      and getattr(lm, "lora", None) is None):
                     from ..parallel.zero3 import Zero3Engine
 
                     eng = Zero3Engine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
@@ -201,9 +236,11 @@ class Strategy:
                     eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
                                      max_norm=self.max_norm, zero_stage=self.stage, group=self.mesh.group("dp"),
-                                     scheduler=sched, use_symm=cfg.get("use_symm"))
+                                     scheduler=sched, use_symm=False if tp > 1 else cfg.get("use_symm"))
                 out.append(_Prepared(module, eng))
             else:
+                if arg is not None and tp > 1:
+                    arg = tp_shard(arg)       # frozen models (reference policy) run tensor-parallel as well
                 if arg is not None:
                     arg.eval() if hasattr(arg, "eval") else None
                 out.append(_Prepared(arg, None) if arg is not None else None)
@@ -328,7 +365,15 @@ class Strategy:
             ckpt.rotate(save_dir, tag, max_num, max_mem, log=self.print)
         torch_dist_barrier_and_cuda_sync()
         eng = model.engine
-        ckpt.save_sharded(eng, save_dir, tag, client_state, save_latest, rank=eng.rank, world=eng.world)
+        if getattr(eng, "tp", None) is not None:
+            # one set of optimizer shards per tensor-parallel rank; tp rank 0 owns the manifest / latest pointer
+            sub = os.path.join(save_dir, tag, f"tp_{eng.tp.rank:02d}")
+            ckpt.save_sharded(eng, sub, "state", client_state, False, rank=eng.rank, world=eng.world)
+            if self.is_rank_0() and save_latest:
+                with open(os.path.join(save_dir, "latest"), "w") as f:
+                    f.write(tag)
+        else:
+            ckpt.save_sharded(eng, save_dir, tag, client_state, save_latest, rank=eng.rank, world=eng.world)
         torch_dist_barrier_and_cuda_sync()
         if self.is_rank_0():
             ckpt.write_metric(os.path.join(save_dir, tag), metric_value, metric_key)
@@ -337,9 +382,17 @@ class Strategy:
     def load_ckpt(self, model, load_dir: str, tag=None, load_module_strict: bool = True,
                   load_optimizer_states: bool = True, load_lr_scheduler_states: bool = True,
                   load_module_only: bool = False):
-        path, states = ckpt.load_sharded(model.engine, load_dir, tag,
-                                         load_optimizer_states and not load_module_only,
-                                         load_lr_scheduler_states and not load_module_only)
+        eng = model.engine
+        if getattr(eng, "tp", None) is not None:
+            tag = ckpt.resolve_tag(load_dir, tag)
+            sub = os.path.join(load_dir, tag or "", f"tp_{eng.tp.rank:02d}")
+            path, states = (None, {}) if tag is None else ckpt.load_sharded(
+                eng, sub, "state", load_optimizer_states and not load_module_only,
+                load_lr_scheduler_states and not load_module_only)
+        else:
+            path, states = ckpt.load_sharded(eng, load_dir, tag,
+                                             load_optimizer_states and not load_module_only,
+                                             load_lr_scheduler_states and not load_module_only)
         if path is None:
             self.print(f"Warning: no checkpoint found at {load_dir}, skipping checkpoint loading.")
             return None, {}

@@ -67,3 +67,8 @@ def test_tensor_parallel_rollout_engine():
 def test_hybrid_worker_zero3_and_tp_rollout():
     out = _run("hybrid_modes.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "HYBRID_MODES_OK" in out
+
+
+def test_tensor_parallel_training():
+    out = _run("tp_train.py", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "TP_TRAIN_OK" in out
