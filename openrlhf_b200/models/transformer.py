@@ -155,7 +155,8 @@ class TransformerLM(nn.Module):
             return y if residual is None else y + residual
         if self.tp_train is not None and target in ("o", "down"):
             # row-parallel shard in training: the sum over the group is differentiable (identity backwards)
-            y = self.tp_train.reduce_out(F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, None))
+            assert bias is None
+            y = self.tp_train.row_parallel_linear(x, self.p(f"layers.{i}.{target}.weight"))
             return y if residual is None else y + residual
         y = F.linear(x, self.p(f"layers.{i}.{target}.weight"), bias, residual)
         if self.lora is not None:

@@ -54,6 +54,38 @@ class _ReduceFromTP(torch.autograd.Function):
         return g, None
 
 
+class _RowParallelFused(torch.autograd.Function):
+    """Row-parallel projection whose all-reduce rides on the GEMM: the epilogue adds every output tile into the fp32
+    accumulation buffer of all TP ranks over NVLink (parallel/tp.py::TPContext.row_parallel, one kernel plus two flag
+    barriers). Backward is local: dx = dy @ w, dw += dy^T x."""
+
+    @staticmethod
+    def forward(ctx, x, w, tpt):
+        from ..ops import functional as F
+
+        acc = tpt.fused_context(x.shape[0], w.shape[0]).row_parallel(x.contiguous(), w)
+        ctx.save_for_backward(x, w)
+        ctx.w_ref = w
+        ctx.F = F
+        return acc.to(torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            T = x.shape[0]
+            tiles = ((w.shape[0] + 127) // 128) * ((w.shape[1] + 255) // 256)
+            splits = max(1, min(8, 148 // max(tiles, 1), T // 512)) if tiles < 148 else 1
+            dw = ctx.F._acc_grad(ctx.w_ref, lambda buf: gemm(dy, x, a_mn=True, b_mn=True, out=buf, accumulate=True,
+                                                             k_splits=splits))
+        return dx, dw, None
+
+
 def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
     assert cfg.num_experts == 0, "tensor-parallel training covers dense models (MoE layers use expert parallelism)"
     assert cfg.num_attention_heads % tp == 0 and cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % tp == 0, \
@@ -74,6 +106,13 @@ class TPTrain:
         self.with_lm_head, self.with_value_head = with_lm_head, with_value_head
         self.entries, self.shard_numel = build_plan(full_cfg, self.rank, self.size, with_lm_head=with_lm_head,
                                                     with_value_head=with_value_head)
+        # GEMM + all-reduce in one kernel for the row-parallel projections of the forward pass (GPU, bf16);
+        # OPENRLHF_B200_TP_FUSED=0 falls back to a GEMM followed by an NCCL all-reduce
+        import os
+
+        self.fused = os.environ.get("OPENRLHF_B200_TP_FUSED", "1") != "0"
+        self._fctx = None
+        self.device = None
 
     # ---- collectives used by TransformerLM
     def copy_in(self, x):
@@ -81,6 +120,26 @@ class TPTrain:
 
     def reduce_out(self, y):
         return _ReduceFromTP.apply(y, self.group)
+
+    def row_parallel_linear(self, x, w):
+        """sum over the TP group of x @ w.T for a row-parallel weight shard w [N, K/tp]."""
+        from ..ops import functional as F
+
+        if self.fused and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] > 0:
+            return _RowParallelFused.apply(x, w, self)
+        return self.reduce_out(F.linear(x, w))
+
+    def fused_context(self, rows: int, cols: int):
+        """Symmetric accumulation buffers of the fused GEMM + all-reduce, grown (collectively: every TP rank sees the
+        same shapes) when a larger micro-batch arrives."""
+        from .tp import TPContext
+
+        need = rows * cols
+        if self._fctx is None or need > self._fctx.max_rows * self._fctx.max_cols:
+            cap_rows = max(rows, 4096)
+            cap_rows = (cap_rows + 1023) // 1024 * 1024
+            self._fctx = TPContext(self.group, cap_rows, cols, 8, self.device)
+        return self._fctx
 
     # ---- parameter classes
     def replicated_specs(self, model: TransformerLM):
@@ -150,6 +209,7 @@ def shard_for_training(full: TransformerLM, group, shard_world: int = 1) -> Tran
                           shard_world=shard_world)
     assert shard.total_numel <= ctx.shard_numel + 128
     ctx.load_from_full(full.flat, shard)
+    ctx.device = full.flat.device
     shard.tp_train = ctx
     shard.gradient_checkpointing = full.gradient_checkpointing
     shard.train(full.training)

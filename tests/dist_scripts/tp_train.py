@@ -89,6 +89,8 @@ def main():
 
         torch.cuda.synchronize()
         _lib.check_status()
+        # the row-parallel projections went through the fused GEMM + all-reduce kernel
+        assert shard.tp_train._fctx is not None and shard.tp_train._fctx.epoch > 0
     if rank == 0:
         print("TP_TRAIN_OK", flush=True)
     dist.destroy_process_group()
