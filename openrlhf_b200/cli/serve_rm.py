@@ -17,7 +17,8 @@ class RewardModelProxy:
         device = "cuda" if torch.cuda.is_available() else "cpu"
         self.reward_model = get_llm_for_sequence_regression(
             args.reward.model_name_or_path, "reward", normalize_reward=args.reward.normalize_enable,
-            value_head_prefix=args.ds.value_head_prefix, device=device, packing_samples=args.ds.packing_samples)
+            value_head_prefix=args.ds.value_head_prefix, device=device, packing_samples=args.ds.packing_samples,
+            load_in_4bit=args.ds.load_in_4bit)
         self.reward_model.eval()
         self.device = device
         self.tokenizer = get_tokenizer(args.reward.model_name_or_path, self.reward_model, "left", None,

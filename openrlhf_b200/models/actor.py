@@ -33,7 +33,7 @@ class Actor(nn.Module):
     def __init__(self, pretrain_or_model, device="cuda", temperature: float = 1.0, packing_samples: bool = True,
                  shard_world: int = 1, seed: int = 0, lora_rank: int = 0, lora_alpha: float = 16,
                  target_modules="all-linear", lora_dropout: float = 0.0, freeze_visual_encoder: bool = False,
-                 **_unused):
+                 load_in_4bit: bool = False, **_unused):
         super().__init__()
         if isinstance(pretrain_or_model, TransformerLM):
             self.model = pretrain_or_model
@@ -48,6 +48,11 @@ class Actor(nn.Module):
 
             self.lora = LoraAdapters(self.model, lora_rank, lora_alpha, target_modules, lora_dropout, seed)
             self.lora._cfg = self.cfg
+        if load_in_4bit:
+            # QLoRA: the frozen projection weights take their NF4 values (ops/nf4.py); adapters train in bf16
+            from ..ops.nf4 import apply_to_model
+
+            apply_to_model(self.model)
         self.temperature = temperature
         self.packing_samples = packing_samples
         self.is_vlm = self.cfg.is_vlm

@@ -87,12 +87,17 @@ class CriticModel(_ValueModel):
 def get_llm_for_sequence_regression(model_name_or_path: str, model_type: str, *, param_dtype: str = "bf16",
                                     normalize_reward: bool = False, init_value_head: bool = False,
                                     value_head_prefix: str = "score", device="cuda", packing_samples: bool = True,
-                                    shard_world: int = 1, seed: int = 0, **_unused) -> nn.Module:
+                                    shard_world: int = 1, seed: int = 0, load_in_4bit: bool = False,
+                                    **_unused) -> nn.Module:
     """Build a reward (``model_type='reward'``) or critic (``'critic'``) model from an HF checkpoint or a preset."""
     if model_type not in ("reward", "critic"):
         raise AssertionError(f"invalid model_type: {model_type}, should be critic or reward.")
     base = load_pretrained(model_name_or_path, device=device, with_lm_head=False, with_value_head=True,
                            shard_world=shard_world, seed=seed, init_value_head=init_value_head,
                            value_head_prefix=value_head_prefix)
+    if load_in_4bit:
+        from ..ops.nf4 import apply_to_model
+
+        apply_to_model(base)           # projection weights take their NF4 values (openrlhf/models/model.py:96-105)
     cls = RewardModel if model_type == "reward" else CriticModel
     return cls(base, normalize_reward=normalize_reward, packing_samples=packing_samples)

@@ -350,3 +350,15 @@ def test_moe_router_kernel(T, E, k, norm):
     (w.gather(1, idx.argsort(-1)) * gw).sum().add((probs * gp).sum()).backward()
     (rw.gather(1, ridx.argsort(-1)) * gw).sum().add((rp * gp).sum()).backward()
     _close(logits.grad, ref_l.grad, rtol=1e-3, atol=1e-5)
+
+
+def test_nf4_kernels_match_cpu_restatement():
+    from openrlhf_b200.ops import nf4
+    torch.manual_seed(0)
+    w = (torch.randn(64 * 4097) * 0.03).bfloat16()
+    w[64:128] = 0
+    codes, absmax = nf4.quantize(w.cuda())
+    rc, ra = nf4.quantize(w.float())
+    assert torch.equal(codes.cpu(), rc) and torch.allclose(absmax.cpu(), ra)
+    d = nf4.dequantize(codes, absmax)
+    assert torch.equal(d.cpu(), nf4.dequantize(rc, ra, torch.bfloat16))
