@@ -27,6 +27,7 @@ RL_FLAGS = [
     ("--vllm.num_engines", int, None), ("--vllm.tensor_parallel_size", int, 1), ("--vllm.sync_backend", str, "nccl"),
     ("--vllm.sync_with_ray", B, False), ("--vllm.enable_prefix_caching", B, False), ("--vllm.enforce_eager", B, False),
     ("--vllm.enable_sleep", B, False), ("--vllm.gpu_memory_utilization", float, 0.95), ("--vllm.max_num_seqs", int, 256),
+    ("--vllm.quantization", str, None),
     # algorithm
     ("--algo.advantage.is_correction_enable", B, False),
     ("--algo.advantage.is_correction_threshold", float, [0.5, 5.0], {"nargs": 2}),

@@ -85,9 +85,16 @@ class _Row:
 class RolloutEngine:
     def __init__(self, model: TransformerLM, max_num_seqs: int = 256, max_model_len: int = 4096,
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
-                 eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None):
+                 eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None,
+                 quantization: str | None = None):
         assert model.cfg.head_dim == 128, "the decode attention kernel is specialised for head_dim 128"
+        assert quantization in (None, "fp8"), "rollout quantisation: None or 'fp8' (per-tensor e4m3)"
         self.model = model
+        # fp8 decode: the projection weights are kept as e4m3 copies with one scale per matrix (re-quantised after
+        # every weight update), activations are quantised per call; halves the weight bytes a decode step streams.
+        # Prefill, attention, norms and the lm_head stay bf16.
+        self.quantization = quantization
+        self.fp8: dict = {}
         self.tp = tp          # rollout.tp_engine.TPDecode: `model` then holds this rank's tensor-parallel shard
         self.cfg: ModelConfig = model.cfg
         self.device = model.flat.device
@@ -216,6 +223,20 @@ class RolloutEngine:
             return
         if flat_src.data_ptr() != self.model.flat.data_ptr():
             self.model.flat.copy_(flat_src, non_blocking=True)
+        if self.quantization == "fp8":
+            self._refresh_fp8()
+
+    @torch.no_grad()
+    def _refresh_fp8(self):
+        from ..ops.fp8 import Fp8Linear
+
+        cfg, m = self.cfg, self.model
+        assert cfg.num_experts == 0 and m.lora is None and self.tp is None, \
+            "fp8 rollout covers dense models without adapters or tensor parallelism"
+        for i in range(cfg.num_hidden_layers):
+            pre = f"layers.{i}."
+            for t in ("qkv", "o", "gate_up", "down"):
+                self.fp8[(i, t)] = Fp8Linear(m.p(pre + t + ".weight"), m._params.get(pre + t + ".bias"))
 
     # ------------------------------------------------------------------ model execution
     @torch.no_grad()
@@ -282,7 +303,9 @@ class RolloutEngine:
     def _decode_step(self, B: int):
         """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
         cfg, m = self.cfg, self.model
-        fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None
+        fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None and self.quantization is None
+        if self.quantization == "fp8" and not self.fp8:
+            self._refresh_fp8()
         assert fused or self.tp is None, "tensor-parallel rollout covers the dense fused decode path"
         if self.mrope:
             torch.add(self.pos[:B], self.rope_delta[:B], out=self.rope_pos[:B])
@@ -365,8 +388,11 @@ class RolloutEngine:
         for i in range(cfg.num_hidden_layers):
             pre = f"layers.{i}."
             x = F.rmsnorm(h, m.p(pre + "norm1.weight"), cfg.rms_norm_eps)
-            qkv = m._lin(i, "qkv", x, m._params.get(pre + "qkv.bias")) if m.lora is not None else \
-                decode_gemm(x, m.p(pre + "qkv.weight"), m._params.get(pre + "qkv.bias"))
+            if self.quantization == "fp8":
+                qkv = self.fp8[(i, "qkv")](x)
+            else:
+                qkv = m._lin(i, "qkv", x, m._params.get(pre + "qkv.bias")) if m.lora is not None else \
+                    decode_gemm(x, m.p(pre + "qkv.weight"), m._params.get(pre + "qkv.bias"))
             if cfg.qk_norm:
                 T = qkv.shape[0]
                 qk = qkv[:, : (Hq + Hkv) * 128].reshape(T, Hq + Hkv, 128)
@@ -376,7 +402,10 @@ class RolloutEngine:
             rope_kvwrite(qkv, pos, slots, table, q_buf, self.kv[i, 0], self.kv[i, 1], Hq, Hkv)
             paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
             ao = attn_buf.view(B, Hq * 128)
-            h = m._lin(i, "o", ao, None, h) if m.lora is not None else decode_gemm(ao, m.p(pre + "o.weight"), None, h)
+            if self.quantization == "fp8":
+                h = self.fp8[(i, "o")](ao, residual=h)
+            else:
+                h = m._lin(i, "o", ao, None, h) if m.lora is not None else decode_gemm(ao, m.p(pre + "o.weight"), None, h)
             x = F.rmsnorm(h, m.p(pre + "norm2.weight"), cfg.rms_norm_eps)
             if cfg.is_moe_layer(i):
                 from ..models.moe import moe_forward
@@ -384,6 +413,8 @@ class RolloutEngine:
                 y, _ = moe_forward(x, m.p(pre + "router.weight"), m.p(pre + "experts.gate_up"),
                                    m.p(pre + "experts.down"), cfg.num_experts_per_tok, cfg.norm_topk_prob)
                 h = h + y
+            elif self.quantization == "fp8":
+                h = self.fp8[(i, "down")](F.swiglu(self.fp8[(i, "gate_up")](x)), residual=h)
             elif m.lora is not None:
                 h = m._lin(i, "down", F.swiglu(m._lin(i, "gate_up", x)), None, h)
             else:

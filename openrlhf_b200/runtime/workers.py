@@ -142,7 +142,8 @@ class RLWorker:
                                          max_model_len=a.data.max_len,
                                          gpu_memory_utilization=a.vllm.gpu_memory_utilization,
                                          seed=a.train.seed + s.rank, eos_token_id=self.tokenizer.eos_token_id,
-                                         use_cuda_graph=not a.vllm.enforce_eager)
+                                         use_cuda_graph=not a.vllm.enforce_eager,
+                                         quantization=getattr(a.vllm, "quantization", None))
             # vision-language models: the processor's image part turns the PIL images an agent passes into patches
             self.rollout.image_processor = getattr(self.tokenizer, "image_processor", None)
             self.async_engine = AsyncRolloutEngine(self.rollout, self.tokenizer)

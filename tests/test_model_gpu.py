@@ -217,3 +217,35 @@ def test_vlm_trains_and_rolls_out():
         h3, _ = m(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
         lp3, _ = m.logprobs(h3, pb.labels)
     assert (lp3[19:-1].cpu() - torch.tensor(out[1].outputs[0].logprob_values)).abs().max() < 0.05
+
+
+def test_rollout_fp8_decode_tracks_bf16_trainer():
+    """fp8 (per-tensor e4m3) projection weights in the decode loop: samples stay close to the bf16 trainer's
+    distribution (log-prob gap of the sampled tokens well below the gap between unrelated tokens)."""
+    from openrlhf_b200.models.packing import pack_lists
+    from openrlhf_b200.ops import _lib
+    from openrlhf_b200.rollout.engine import RolloutEngine, SamplingParams
+    cfg, m = _tiny()
+    eng = RolloutEngine(m, max_num_seqs=8, max_model_len=512, num_pages=32, seed=1, quantization="fp8")
+    torch.manual_seed(2)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,)).tolist() for n in (40, 130)]
+    outs = eng.generate(prompts, SamplingParams(temperature=1.0, max_tokens=64, n=1, logprobs=1, ignore_eos=True))
+    _lib.check_status()
+    assert len(eng.fp8) == 4 * cfg.num_hidden_layers
+    gaps = []
+    for p, o in zip(prompts, outs):
+        toks = o.outputs[0].token_ids
+        seq = torch.tensor(p + toks)
+        pb = pack_lists([seq], "cuda")
+        with torch.no_grad():
+            h, _ = m(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+            lp, _ = m.logprobs(h, pb.labels)
+        gaps.append((lp[len(p) - 1:-1].cpu() - torch.tensor(o.outputs[0].logprob_values)).abs())
+    g = torch.cat(gaps)
+    assert g.mean() < 0.1 and g.max() < 1.0, (g.mean().item(), g.max().item())
+    # weights changed -> the e4m3 copies follow
+    s0 = eng.fp8[(0, "qkv")].w_scale.item()
+    m.p("layers.0.qkv.weight").data.mul_(2.0)
+    eng.update_weights(m.flat)
+    assert abs(eng.fp8[(0, "qkv")].w_scale.item() / s0 - 2.0) < 0.05
+    m.p("layers.0.qkv.weight").data.div_(2.0)
