@@ -184,6 +184,8 @@ PRESETS: dict[str, ModelConfig] = {
     # small model with head_dim 128 so that every sm_100a kernel applies
     "tiny-qwen2": ModelConfig("qwen2", 2048, 256, 512, 2, 2, 1, head_dim=128, rope_theta=1e6, attention_bias=True,
                               tie_word_embeddings=True),
+    # 4 query / 2 kv heads: divisible by a tensor-parallel size of 2
+    "tiny-qwen2-gqa": ModelConfig("qwen2", 2048, 256, 512, 2, 4, 2, head_dim=128, rope_theta=1e6, attention_bias=True),
     "qwen2.5-1.5b": ModelConfig("qwen2", 151936, 1536, 8960, 28, 12, 2, rms_norm_eps=1e-6, rope_theta=1e6,
                                 tie_word_embeddings=True, attention_bias=True),
     "qwen2.5-7b": ModelConfig("qwen2", 152064, 3584, 18944, 28, 28, 4, rms_norm_eps=1e-6, rope_theta=1e6,

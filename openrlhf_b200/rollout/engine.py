@@ -222,7 +222,8 @@ class RolloutEngine:
             self.tp.load_shard(flat_src, self.model.flat)      # one planned copy kernel: full layout -> this TP shard
             return
         if flat_src.data_ptr() != self.model.flat.data_ptr():
-            self.model.flat.copy_(flat_src, non_blocking=True)
+            n = min(flat_src.numel(), self.model.flat.numel())      # buffers may differ in their shard padding
+            self.model.flat[:n].copy_(flat_src[:n], non_blocking=True)
         if self.quantization == "fp8":
             self._refresh_fp8()
 

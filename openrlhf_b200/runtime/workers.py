@@ -73,6 +73,16 @@ class RLWorker:
         temp = a.rollout.temperature
         if "actor" in self.roles:
             lm = load_pretrained(a.actor.model_name_or_path, device=self.device, shard_world=dp, seed=a.train.seed)
+            self._rollout_full = None
+            if s.ds_tensor_parallel_size > 1 and s.world_size > 1:
+                # --ds.tensor_parallel_size: train this rank's shard (parallel/tp_train.py); the rollout engine keeps
+                # the full model, refreshed from the gathered shards at every weight sync
+                from ..parallel.tp_train import shard_for_training
+
+                if "rollout" in self.roles:
+                    self._rollout_full = lm
+                    lm.requires_grad_(False)
+                lm = shard_for_training(lm, s.mesh.group("tp"), shard_world=dp)
             self.actor = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples,
                                freeze_visual_encoder=getattr(a.actor, "freeze_visual_encoder", False))
             if a.actor.gradient_checkpointing_enable:
@@ -96,7 +106,8 @@ class RLWorker:
                 self.ema_model = TransformerLM(lm.cfg, device="cpu", dtype=torch.float32, seed=None)
                 self.ema_model.flat.copy_(lm.flat[: self.ema_model.flat.numel()].float().cpu())
             if a.ckpt.load_enable and os.path.exists(os.path.join(a.ckpt.path, "_actor")):
-                _, self._resume_states = ckpt.load_sharded(self.actor_engine, os.path.join(a.ckpt.path, "_actor"))
+                _, self._resume_states = s.load_ckpt(SimpleNamespace(engine=self.actor_engine),
+                                                     os.path.join(a.ckpt.path, "_actor"))
             else:
                 self._resume_states = {}
         if "critic" in self.roles and a.critic.model_name_or_path:
@@ -122,6 +133,11 @@ class RLWorker:
             dev = "cpu" if a.ref.offload else self.device
             lm = load_pretrained(a.ref.model_name_or_path or a.actor.model_name_or_path, device=dev, seed=a.train.seed)
             lm.requires_grad_(False)
+            if s.ds_tensor_parallel_size > 1 and s.world_size > 1 and dev != "cpu":
+                from ..parallel.tp_train import shard_for_training
+
+                lm = shard_for_training(lm, s.mesh.group("tp"))
+                lm.requires_grad_(False)
             self.ref = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples).eval()
         if "reward" in self.roles and a.reward.model_name_or_path:
             dev = "cpu" if a.reward.offload else self.device
@@ -131,7 +147,9 @@ class RLWorker:
             self.reward = RewardModel(lm, normalize_reward=a.reward.normalize_enable,
                                       packing_samples=a.ds.packing_samples).eval()
         if "rollout" in self.roles:
-            if self.actor is not None:
+            if self.actor is not None and getattr(self, "_rollout_full", None) is not None:
+                rl_model = self._rollout_full        # tensor-parallel training: the engine owns a full copy
+            elif self.actor is not None:
                 rl_model = self.actor.model          # hybrid engine: one weight buffer for trainer and rollout
             else:
                 rl_model = load_pretrained(a.actor.model_name_or_path, device=self.device, seed=a.train.seed)
@@ -376,6 +394,11 @@ class RLWorker:
         """Actor -> rollout weights. Colocated: the engine already reads the updated buffer. Separate rollout ranks:
         broadcast the flat bf16 buffer from actor rank 0 over the global group (NCCL path, the baseline)."""
         if self.actor is not None and self.rollout is not None:
+            tpt = getattr(self.actor.model, "tp_train", None)
+            if tpt is not None:
+                full = tpt.gather_full(self.actor.model)        # all shards -> full fused layout on every rank
+                self.rollout.update_weights(full)
+                return True
             self.rollout.update_weights(self.actor.model.flat)
             return True
         if dist.is_initialized() and dist.get_world_size() > 1:

@@ -72,3 +72,10 @@ def test_hybrid_worker_zero3_and_tp_rollout():
 def test_tensor_parallel_training():
     out = _run("tp_train.py", env={"NCCL_NVLS_ENABLE": "0"})
     assert "TP_TRAIN_OK" in out
+
+
+def test_rl_launcher_with_tensor_parallel_training(tmp_path):
+    r = subprocess.run(["bash", os.path.join(HERE, "dist_scripts", "cli_ppo_tp.sh"), str(tmp_path / "out")],
+                       capture_output=True, text=True, timeout=900, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0 and "CLI_PPO_TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "global step 1" in r.stdout
