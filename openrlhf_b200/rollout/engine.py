@@ -703,6 +703,9 @@ class RolloutEngine:
 
 
 # ---------------------------------------------------------------------------------------------- decode GEMM
+_BN64_MAX_N = 2048      # widest output for which 64-column tiles (more CTAs) beat 128-column tiles at short K
+
+
 def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor, ws: torch.Tensor | None = None):
     """Split-K projection for small M whose fp32 slabs stay in the shared workspace for the next kernel to reduce.
     Returns (workspace, number of slabs). `ws`: use this buffer (a symmetric one under tensor parallelism)."""
@@ -710,7 +713,9 @@ def gemm_to_workspace(x: torch.Tensor, w: torch.Tensor, ws: torch.Tensor | None 
 
     M, K = x.shape
     N = w.shape[0]
-    bn = 64 if N <= 4096 else 128
+    # narrow N tiles give more CTAs for short K; with a long K (down_proj) 128-wide tiles halve the activation re-reads
+    # per weight byte and twice as many K splits keep all SMs streaming (14.4 us vs 16.9 us at N 1536, K 8960)
+    bn = 64 if (N <= _BN64_MAX_N and K < 4096) else 128      # small matrices only (e.g. 1536 x 1536): more CTAs
     tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
     splits = max(1, min(148 // max(tiles, 1), kb // 4))
@@ -734,7 +739,7 @@ def decode_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     N = w.shape[0]
     if M > 256:
         return gemm(x, w, bias=bias, residual=residual)
-    bn = 64 if N <= 4096 else 128
+    bn = 64 if (N <= _BN64_MAX_N and K < 4096) else 128
     tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
     splits = max(1, min(148 // max(tiles, 1), kb // 4))
