@@ -50,3 +50,28 @@ def test_sft_cli_tensor_parallel(tmp_path):
     assert torch.isfinite(a).all() and (a - b).abs().max() > 1e-4
     files = os.listdir(os.path.join(out_dir, "ckpt", "global_step8"))
     assert {"tp_00", "tp_01"} <= set(files), files
+
+
+def test_shard_plan_round_trip_with_value_head():
+    """full -> tp shards (copy plan) -> full (the inverse used for HF export) is the identity, value head included."""
+    from openrlhf_b200.models.config import ModelConfig
+    from openrlhf_b200.models.transformer import build_param_specs
+    from openrlhf_b200.parallel.reshard import build_plan, run_plan_reference, tp_param_specs
+
+    cfg = ModelConfig("qwen2", 512, 128, 256, 2, 4, 2, head_dim=64, attention_bias=True)
+    specs = build_param_specs(cfg, with_lm_head=False, with_value_head=True)
+    total = specs[-1].offset + specs[-1].numel
+    full = torch.arange(total, dtype=torch.float32)
+    back = torch.full((total,), -1.0)
+    tp = 2
+    for r in range(tp):
+        entries, size = build_plan(cfg, r, tp, with_lm_head=False, with_value_head=True)
+        shard = torch.zeros(size)
+        run_plan_reference(entries, [full], shard)
+        names = [s.name for s in tp_param_specs(cfg, r, tp, with_lm_head=False, with_value_head=True)]
+        assert "value_head.weight" in names and "lm_head.weight" not in names
+        for e in entries:
+            dst = back.as_strided((e.rows, e.row_elems), (e.src_ld, 1), e.src_off)
+            dst.copy_(shard.as_strided((e.rows, e.row_elems), (e.dst_ld, 1), e.dst_off))
+    for s in specs:          # every parameter element was restored (alignment gaps between parameters stay untouched)
+        assert torch.equal(back[s.offset:s.offset + s.numel], full[s.offset:s.offset + s.numel]), s.name
