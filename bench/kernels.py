@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m openrlhf_b200.bench_kernels --kernel gemm --m 8192 --n 8960 --k 1536``.
+"""Kernel micro-benchmarks: ``python -m bench.kernels --kernel gemm --m 8192 --n 8960 --k 1536``.
 
 Times one kernel with CUDA events (3 warm-up launches, L2 flushed between timed launches by writing a 256 MiB
 buffer) and prints achieved FLOP/s or bytes/s next to the measured peaks in MEASURED_PEAKS.json when that file is

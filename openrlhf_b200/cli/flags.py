@@ -89,7 +89,21 @@ SPMD_TRAIN = [
 ]
 
 IGNORED = ("ds.zpg", "ds.deepcompile", "ds.use_liger_kernel", "ds.overlap_comm", "ds.grad_accum_dtype",
-           "ds.attn_implementation", "ds.experts_implementation", "use_ms", "vllm.sync_with_ray", "vllm.enforce_eager")
+           "ds.attn_implementation", "ds.experts_implementation", "use_ms", "vllm.sync_with_ray", "vllm.sync_backend",
+           "ds.use_universal_ckpt", "local_rank")
+
+
+def report_ignored(parser: argparse.ArgumentParser, ns) -> list[str]:
+    """One line for every accepted-but-ignored flag that the user set to a non-default value."""
+    flat = vars(ns)
+    out = []
+    for k in IGNORED:
+        if k in flat and flat[k] != parser.get_default(k):
+            out.append(k)
+    if out:
+        print("[Info] flags accepted for launch-script compatibility and ignored by this framework: "
+              + ", ".join("--" + k for k in out))
+    return out
 
 
 def finalize(parser: argparse.ArgumentParser, argv=None):
@@ -97,6 +111,7 @@ def finalize(parser: argparse.ArgumentParser, argv=None):
     from ..utils.config import hierarchize
 
     ns = parser.parse_args(argv)
+    report_ignored(parser, ns)
     flat = vars(ns)
     for k in [k for k in flat if k.endswith("muon.no_nesterov")]:
         if flat[k]:

@@ -145,8 +145,6 @@ def validate(args):
     eff = a.actor.num_nodes * a.actor.num_gpus_per_node // a.ds.ring_attn_size // a.ds.tensor_parallel_size
     assert a.rollout.n_samples_per_prompt * a.rollout.batch_size // a.rollout.micro_batch_size >= eff, \
         "The number of sample batches must be greater than or equal to the effective number of actor processes."
-    for k in F.IGNORED:
-        pass  # accepted for compatibility; no effect in this framework
     return a
 
 

@@ -485,12 +485,8 @@ static int launch_main(const void* q, int q_rows, const void* k, const void* v, 
   if (r) return r;
   r = make_tmap_bf16_2d(&tdo, dout, q_rows, lddo, lddo, 128, 64);
   if (r) return r;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AbSmem::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> configured{0};      // one bit per device
+  if (!set_max_smem_once(configured, attn_bwd_kernel, AbSmem::TOTAL)) return -2;
   AttnBwdParams p;
   p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_k0 = tile_k0; p.lse = lse; p.delta = delta;
   p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dv_acc = dv_acc; p.acc_ld = dq_ld; p.dkv_ld = dkv_ld;

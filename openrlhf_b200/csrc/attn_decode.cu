@@ -392,12 +392,8 @@ extern "C" int b200_attn_decode(const void* q, const void* k_cache, const void* 
   if (r) return r;
   r = make_tmap_bf16_2d(&tv, v_cache, (uint64_t)num_pages * PAGE, (uint64_t)Hkv * HD, (uint64_t)Hkv * HD, PAGE, 64);
   if (r) return r;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> configured{0};      // one bit per device
+  if (!set_max_smem_once(configured, attn_decode_kernel, DecSmem::TOTAL)) return -2;
   DecodeParams p;
   p.block_table = block_table; p.seq_lens = seq_lens; p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.part_o = part_o; p.part_ml = part_ml; p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.splits = splits;
@@ -435,17 +431,19 @@ static __device__ __align__(256) float g_noalloc_scratch[B200_NOALLOC_MAX_PARTIA
 
 static float* noalloc_scratch_for_current_device(int* err) {
   constexpr int MAX_DEV = 64;
-  static float* ptrs[MAX_DEV] = {nullptr};
+  static std::atomic<float*> ptrs[MAX_DEV];      // zero-initialised; written once per device, readable from any thread
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) { *err = -21; return nullptr; }
-  if (ptrs[dev] == nullptr) {
+  float* cached = ptrs[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr) { *err = -21; return nullptr; }
-    ptrs[dev] = static_cast<float*>(p);
+    cached = static_cast<float*>(p);
+    ptrs[dev].store(cached, std::memory_order_release);   // two threads racing here store the same address
   }
   *err = 0;
-  return ptrs[dev];
+  return cached;
 }
 
 extern "C" int b200_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,

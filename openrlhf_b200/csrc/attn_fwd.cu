@@ -384,12 +384,8 @@ static int launch_attn_fwd(const void* q, int q_rows, const void* k, const void*
   if (r) return r;
   r = make_tmap_bf16_2d(&tv, v, kv_rows, v_ld, v_ld, 128, 64);
   if (r) return r;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> configured{0};      // one bit per device
+  if (!set_max_smem_once(configured, attn_fwd_kernel, AtSmem::TOTAL)) return -2;
   AttnFwdParams p;
   p.cu_seqlens = cu_seqlens; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.n_seqs = n_seqs; p.T = q_rows; p.Hq = Hq; p.Hkv = Hkv;

@@ -486,13 +486,9 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const PeerMaps& pa, const GemmParams& p, int sms,
                   cudaStream_t stream) {
   using L = SmemLayout<BN>;
-  static bool configured = false;
+  static std::atomic<unsigned long long> configured{0};      // one bit per device (per template instance)
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return -2;
-    configured = true;
-  }
+  if (!set_max_smem_once(configured, kern, L::TOTAL)) return -2;
   int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
   int tiles = m_blocks * n_blocks * (p.k_splits > 1 ? p.k_splits : 1) * (p.group_mode == 2 ? p.n_groups : 1);
   int grid = tiles < sms ? tiles : sms;

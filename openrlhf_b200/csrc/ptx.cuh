@@ -10,6 +10,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 namespace b200 {
 
 // Error codes written into the status word (first writer wins).
@@ -291,6 +293,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+
+// Host side: raise a kernel's dynamic shared-memory limit once per device. The attribute belongs to the device's
+// context, so a process that drives several GPUs must set it on each of them; `done` holds one bit per device
+// ordinal. Safe to call from several host threads (setting the attribute twice is harmless).
+template <typename K>
+inline bool set_max_smem_once(std::atomic<unsigned long long>& done, K kernel, int bytes) {
+  int dev = -1;
+  const bool known = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
+  const unsigned long long bit = known ? (1ull << dev) : 0ull;
+  if (known && (done.load(std::memory_order_acquire) & bit)) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (known) done.fetch_or(bit, std::memory_order_release);
+  return true;
+}
 
 // Host side: launch with the programmatic-stream-serialization attribute when the environment variable
 // OPENRLHF_B200_PDL is "1"; a plain launch otherwise (the default: with grids larger than one wave the early-started

@@ -78,12 +78,16 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restrict__ temperature, float temp_scalar,
               int top_k, float top_p, unsigned long long seed, const long long* __restrict__ step_ptr,
               long long step_scalar, long long* __restrict__ out_tok, float* __restrict__ out_logp,
-              const int* __restrict__ active) {
+              const int* __restrict__ active, const int* __restrict__ top_k_rows,
+              const float* __restrict__ top_p_rows) {
   __shared__ float red[32];
   __shared__ float s_best[32];
   __shared__ int s_idx[32];
   const int row = blockIdx.x;
   if (active != nullptr && active[row] == 0) return;
+  // per-request nucleus settings (one value per row) take precedence over the launch-wide scalars
+  if (top_k_rows != nullptr) top_k = top_k_rows[row];
+  if (top_p_rows != nullptr) top_p = top_p_rows[row];
   const T* z = logits + (size_t)row * ld;
   const float temp = temperature ? temperature[row] : temp_scalar;
   const bool greedy = temp <= 1e-6f;
@@ -396,16 +400,17 @@ using namespace b200;
 extern "C" int b200_sample(const void* logits, int is_bf16, int B, int V, int ld, const float* temperature,
                            float temp_scalar, int top_k, float top_p, unsigned long long seed,
                            const long long* step_ptr, long long step_scalar, long long* out_tok, float* out_logp,
-                           const int* active, void* stream_) {
+                           const int* active, const int* top_k_rows, const float* top_p_rows, void* stream_) {
   if (B <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   if (is_bf16)
     sample_kernel<__nv_bfloat16><<<B, SAMPLE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, ld, V, temperature,
                                                                temp_scalar, top_k, top_p, seed, step_ptr, step_scalar,
-                                                               out_tok, out_logp, active);
+                                                               out_tok, out_logp, active, top_k_rows, top_p_rows);
   else
     sample_kernel<float><<<B, SAMPLE_THREADS, 0, st>>>((const float*)logits, ld, V, temperature, temp_scalar, top_k,
-                                                       top_p, seed, step_ptr, step_scalar, out_tok, out_logp, active);
+                                                       top_p, seed, step_ptr, step_scalar, out_tok, out_logp, active,
+                                                       top_k_rows, top_p_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

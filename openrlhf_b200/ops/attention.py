@@ -229,6 +229,14 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     seq_lens int32 [B] (tokens already in the cache, current one included).
     """
     B, Hq, D = q.shape
+    if not q.is_cuda:
+        from . import reference
+
+        res = reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, PAGE)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
     assert D == 128 and q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     Hkv = k_cache.shape[1]
     num_pages = k_cache.shape[0] // PAGE
@@ -257,6 +265,15 @@ def rope_kvwrite(qkv: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, tabl
                  k_cache: torch.Tensor, v_cache: torch.Tensor, Hq: int, Hkv: int) -> None:
     """RoPE on q,k of qkv [T, (Hq+2Hkv)*128]; writes roped q to q_out [T,Hq,128] and k,v into cache slot `slots[t]`."""
     T = qkv.shape[0]
+    if not qkv.is_cuda:
+        from . import reference
+
+        D = q_out.shape[-1]
+        r = reference.rope(qkv, pos, table, Hq + Hkv, D)
+        q_out.copy_(r[:, : Hq * D].reshape(T, Hq, D))
+        k_cache[slots.long()] = r[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D)
+        v_cache[slots.long()] = r[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D].reshape(T, Hkv, D)
+        return
     rc = _lib.lib().b200_rope_kvwrite(
         _lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(slots), _lib.ptr(table), _lib.ptr(q_out), _lib.ptr(k_cache),
         _lib.ptr(v_cache), ctypes.c_int(T), ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_int(qkv.stride(0)),

@@ -155,8 +155,32 @@ def run_plan_reference(entries: list[CopyEntry], srcs: list[torch.Tensor], dst: 
 class ReshardPlan:
     """A plan uploaded to the device once; ``run`` is one kernel launch."""
 
+    MAX_ROW_ELEMS = 1 << 30      # the record packs rows / row_elems / leading dimensions as int32
+
+    @classmethod
+    def split_large(cls, entries: list[CopyEntry]) -> list[CopyEntry]:
+        """Cut single-row entries longer than MAX_ROW_ELEMS into chunks (a whole ZeRO shard of a 7B+ model is one
+        contiguous run of several billion elements); multi-row entries must already fit."""
+        out = []
+        for e in entries:
+            if e.rows == 1 and e.row_elems > cls.MAX_ROW_ELEMS:
+                done = 0
+                while done < e.row_elems:
+                    n = min(cls.MAX_ROW_ELEMS, e.row_elems - done)
+                    out.append(CopyEntry(e.src_off + done, e.dst_off + done, 1, n, n, n, e.src_rank))
+                    done += n
+            else:
+                out.append(e)
+        return out
+
     def __init__(self, entries: list[CopyEntry], device):
         import numpy as np
+
+        entries = self.split_large(entries)
+        lim = 2 ** 31 - 1
+        for e in entries:
+            if max(e.rows, e.row_elems, e.src_ld, e.dst_ld) > lim:
+                raise ValueError(f"copy entry exceeds the int32 fields of the device record: {e}")
 
         rec = np.zeros(len(entries), dtype=[("src_off", "<i8"), ("dst_off", "<i8"), ("rows", "<i4"), ("row_elems", "<i4"),
                                             ("src_ld", "<i4"), ("dst_ld", "<i4"), ("src_rank", "<i4"), ("pad", "<i4")])

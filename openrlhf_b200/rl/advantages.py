@@ -29,8 +29,12 @@ def group_baseline(rewards: torch.Tensor, n: int, estimator: str) -> tuple[torch
 
 
 @torch.no_grad()
-def compute_advantages_and_returns(experiences, args, kl_value: float, dist_group=None):
-    """In place on `experiences` (each batched, with .index = original sample positions). Returns the list."""
+def compute_advantages_and_returns(experiences, args, kl_value: float, dist_group=None, distributed: bool = False):
+    """In place on `experiences` (each batched, with .index = original sample positions). Returns the list.
+
+    distributed=True: the experiences are this rank's share of the rollout batch; the whitening statistics are summed
+    over `dist_group` (None = the default group) so that every rank normalises with the mean / variance of the whole
+    batch, as the reference's controller does (openrlhf/trainer/ppo_utils/experience_maker.py:314-328)."""
     est = args.algo.advantage.estimator
     n = args.rollout.n_samples_per_prompt
     apply_length_penalties(experiences, args)
@@ -64,11 +68,19 @@ def compute_advantages_and_returns(experiences, args, kl_value: float, dist_grou
         e.kl = None
 
     if est in WHITENED:
-        stats = sum(K.masked_stats(e.advantages.float(), e.action_mask.float()).cpu() for e in experiences)
-        if dist_group is not None:
+        # the statistics stay on the experiences' device: no host round trip, and NCCL can reduce them in place
+        stats = sum(K.masked_stats(e.advantages.float(), e.action_mask.float()) for e in experiences)
+        if distributed or dist_group is not None:
             import torch.distributed as dist
 
-            dist.all_reduce(stats, group=dist_group)
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size(dist_group) > 1:
+                if stats.device.type == "cpu" and dist.get_backend(dist_group) == "nccl":
+                    dev_stats = stats.cuda()
+                    dist.all_reduce(dev_stats, group=dist_group)
+                    stats = dev_stats.cpu()
+                else:
+                    stats = stats.contiguous()
+                    dist.all_reduce(stats, group=dist_group)
         for e in experiences:
             e.advantages = K.masked_whiten(e.advantages.float().contiguous(), e.action_mask.float(),
                                            std_norm=not args.algo.advantage.no_std_norm,

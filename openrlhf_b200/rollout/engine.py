@@ -87,7 +87,8 @@ class RolloutEngine:
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
                  eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None,
                  quantization: str | None = None):
-        assert model.cfg.head_dim == 128, "the decode attention kernel is specialised for head_dim 128"
+        assert model.cfg.head_dim == 128 or not model.flat.is_cuda, \
+            "the decode attention kernel is specialised for head_dim 128"
         assert quantization in (None, "fp8"), "rollout quantisation: None or 'fp8' (per-tensor e4m3)"
         self.model = model
         # fp8 decode: the projection weights are kept as e4m3 copies with one scale per matrix (re-quantised after
@@ -98,15 +99,19 @@ class RolloutEngine:
         self.tp = tp          # rollout.tp_engine.TPDecode: `model` then holds this rank's tensor-parallel shard
         self.cfg: ModelConfig = model.cfg
         self.device = model.flat.device
+        # CPU tensors run the PyTorch restatements of every kernel (scheduler, launcher and agent tests without a GPU)
+        self.on_gpu = self.device.type == "cuda"
         self.max_num_seqs = max_num_seqs
         self.max_model_len = max_model_len
         self.max_pages = (max_model_len + PAGE - 1) // PAGE
         self.seed = seed
         self.eos = self.cfg.eos_token_id if eos_token_id is None else eos_token_id
-        self.use_cuda_graph = use_cuda_graph
+        self.use_cuda_graph = use_cuda_graph and self.on_gpu
         self.check_interval = check_interval
         cfg = self.cfg
         bytes_per_page = 2 * cfg.num_hidden_layers * PAGE * cfg.kv_size * 2
+        if num_pages is None and not self.on_gpu:
+            num_pages = max(8, min(max_num_seqs * self.max_pages + 1, 2048))
         if num_pages is None:
             free, total = torch.cuda.mem_get_info(self.device)
             budget = int(total * gpu_memory_utilization) - (total - free)
@@ -129,18 +134,23 @@ class RolloutEngine:
         self.seq_lens = torch.ones(B, dtype=torch.int32, device=dev)
         self.slots = torch.zeros(B, dtype=torch.int32, device=dev)
         self.block_table = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32, device=dev)
-        self.block_table_host = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32).pin_memory()
+        self.block_table_host = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32)
+        if self.on_gpu:
+            self.block_table_host = self.block_table_host.pin_memory()
         self.active = torch.zeros(B, dtype=torch.int32, device=dev)
         self.gen_count = torch.zeros(B, dtype=torch.int32, device=dev)
         self.max_tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.min_tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.ignore_eos = torch.zeros(B, dtype=torch.bool, device=dev)
         self.temperature = torch.ones(B, dtype=torch.float32, device=dev)
+        # nucleus settings are per request (one value per row), like the sampling parameters of the reference's engine
+        self.top_k_rows = torch.full((B,), -1, dtype=torch.int32, device=dev)
+        self.top_p_rows = torch.ones(B, dtype=torch.float32, device=dev)
         self.step_counter = torch.zeros(1, dtype=torch.int64, device=dev)
         self.max_new_cap = max_model_len
         self.out_tokens = torch.zeros(B, self.max_new_cap, dtype=torch.int64, device=dev)
         self.out_logprobs = torch.zeros(B, self.max_new_cap, dtype=torch.float32, device=dev)
-        self.q_buf = torch.empty(B, cfg.num_attention_heads, 128, dtype=torch.bfloat16, device=dev)
+        self.q_buf = torch.empty(B, cfg.num_attention_heads, cfg.head_dim, dtype=model.flat.dtype, device=dev)
         self.attn_buf = torch.empty_like(self.q_buf)
         self.next_tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.next_lp = torch.zeros(B, dtype=torch.float32, device=dev)
@@ -152,18 +162,21 @@ class RolloutEngine:
         self._batch_counter = 0
         self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self.graph_launches: dict[tuple, int] = {}
-        self.top_p, self.top_k = 1.0, -1
         self.sleeping = False
         self.paused = False
         self.decode_steps = 0
-        _lib.status_word(self.device)
+        if self.on_gpu:
+            _lib.status_word(self.device)
         self.model.rope(self.device)
 
     # ------------------------------------------------------------------ memory
     def _alloc_kv(self):
         """KV cache [layers, 2, pages*128, kv_heads, 128] inside a VMM arena: its address survives sleep / wake."""
         cfg = self.cfg
-        shape = (cfg.num_hidden_layers, 2, self.num_pages * PAGE, cfg.num_key_value_heads, 128)
+        shape = (cfg.num_hidden_layers, 2, self.num_pages * PAGE, cfg.num_key_value_heads, cfg.head_dim)
+        if not self.on_gpu:
+            self.kv = torch.zeros(*shape, dtype=self.model.flat.dtype, device=self.device)
+            return
         if getattr(self, "arena", None) is None:
             try:
                 from .block_manager import VmmArena
@@ -193,7 +206,8 @@ class RolloutEngine:
         else:
             self.graphs.clear()
             self.kv = None
-            torch.cuda.empty_cache()
+            if self.on_gpu:
+                torch.cuda.empty_cache()
         self.sleeping = True
 
     def wake_up(self, tags=None):
@@ -290,7 +304,7 @@ class RolloutEngine:
         h, _ = m(ids, pos, cu, max(lens), attn_fn=attn_fn, inputs_embeds=embeds)
         m.train(was_training)
         last = (cu[1:] - 1).long()
-        logits = gemm(h[last].contiguous(), m.lm_head_weight())
+        logits = F.linear(h[last].contiguous(), m.lm_head_weight())
         # partial last page: every other row of the group gets its own copy
         for p, rows in zip(prompts, row_groups):
             n_full = len(p) // PAGE
@@ -304,7 +318,8 @@ class RolloutEngine:
     def _decode_step(self, B: int):
         """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
         cfg, m = self.cfg, self.model
-        fused = not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None and self.quantization is None
+        fused = (not cfg.qk_norm and cfg.num_experts == 0 and m.lora is None and self.quantization is None
+                 and self.on_gpu)
         if self.quantization == "fp8" and not self.fp8:
             self._refresh_fp8()
         assert fused or self.tp is None, "tensor-parallel rollout covers the dense fused decode path"
@@ -314,7 +329,7 @@ class RolloutEngine:
             logits = self._decode_layers_fused(B)
         else:
             logits = self._decode_layers_generic(B)
-        sample(logits, temperature=self.temperature[:B], top_k=self.top_k, top_p=self.top_p, seed=self.seed,
+        sample(logits, temperature=self.temperature[:B], top_k=self.top_k_rows[:B], top_p=self.top_p_rows[:B], seed=self.seed,
                step=self.step_counter, out_tokens=self.next_tok[:B], out_logprobs=self.next_lp[:B],
                active=self.active[:B])
         self._advance(B)
@@ -402,7 +417,7 @@ class RolloutEngine:
                 qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * 128:]], dim=1)
             rope_kvwrite(qkv, pos, slots, table, q_buf, self.kv[i, 0], self.kv[i, 1], Hq, Hkv)
             paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
-            ao = attn_buf.view(B, Hq * 128)
+            ao = attn_buf.view(B, Hq * cfg.head_dim)
             if self.quantization == "fp8":
                 h = self.fp8[(i, "o")](ao, residual=h)
             else:
@@ -423,7 +438,7 @@ class RolloutEngine:
                 a = F.swiglu(gu)
                 h = decode_gemm(a, m.p(pre + "down.weight"), None, h)
         x = F.rmsnorm(h, m.p("norm.weight"), cfg.rms_norm_eps)
-        return gemm(x, m.lm_head_weight())
+        return F.linear(x, m.lm_head_weight())
 
     def _advance(self, B: int):
         """Per-step bookkeeping (append token / log-prob, stop conditions, next position and KV slot): one kernel."""
@@ -464,7 +479,7 @@ class RolloutEngine:
         if not self.use_cuda_graph:
             self._decode_step(B)
             return
-        key = (B, self.top_k, self.top_p)
+        key = (B,)
         g = self.graphs.get(key)
         if g is None:
             # warm up outside capture (lazy library state, status word, rope table), then capture
@@ -576,11 +591,6 @@ class RolloutEngine:
                     raise RuntimeError("a request does not fit into the KV cache / row budget of the rollout engine")
                 break
             self.waiting.popleft()
-            if (self.top_p, self.top_k) != (float(sp.top_p), int(sp.top_k)):
-                if any(r is not None for r in self.rows) or admitted:
-                    self.waiting.appendleft((rid, prompt, sp))   # nucleus settings are per batch: wait for a drain
-                    break
-                self.top_p, self.top_k = float(sp.top_p), int(sp.top_k)
             rows = [free_rows.pop(0) for _ in range(sp.n)]
             shared = [self.blocks.alloc() for _ in range(len(prompt) // PAGE)]
             for j, r in enumerate(rows):
@@ -639,7 +649,8 @@ class RolloutEngine:
                 if len(parts) == sp.n:
                     finished.append(RequestOutput(r.request_id, list(prompt), [parts[j] for j in range(sp.n)]))
                     del self._req[r.request_id]
-        _lib.check_status(self.device)
+        if self.on_gpu:
+            _lib.check_status(self.device)
         return finished
 
     @torch.no_grad()
@@ -677,8 +688,10 @@ class RolloutEngine:
         rows = torch.tensor([r for g in groups for r in g], dtype=torch.int64, device=dev)
         lg = logits.repeat_interleave(rep, dim=0)                    # one row per sample
         temps = torch.tensor([sp.temperature for sp, g in zip(sps, groups) for _ in g], dtype=torch.float32, device=dev)
-        tok, lp = sample(lg, temperature=temps, top_k=self.top_k, top_p=self.top_p, seed=self.seed ^ 0x5DEECE66D,
-                         step=int(self.decode_steps) * 4096 + int(rows[0].item()))
+        topk = torch.tensor([int(sp.top_k) for sp, g in zip(sps, groups) for _ in g], dtype=torch.int32, device=dev)
+        topp = torch.tensor([float(sp.top_p) for sp, g in zip(sps, groups) for _ in g], dtype=torch.float32, device=dev)
+        tok, lp = sample(lg, temperature=temps, top_k=topk, top_p=topp, seed=self.seed ^ 0x5DEECE66D,
+                         step=int(self.decode_steps) * 4096 + int(groups[0][0]))
         plen = torch.tensor([len(p) for p, g in zip(prompts, groups) for _ in g], dtype=torch.int32, device=dev)
         maxt = torch.tensor([self.rows[r].max_tokens for g in groups for r in g], dtype=torch.int32, device=dev)
         mint = torch.tensor([sp.min_tokens for sp, g in zip(sps, groups) for _ in g], dtype=torch.int32, device=dev)
@@ -694,6 +707,8 @@ class RolloutEngine:
         self.min_tok[rows] = mint
         self.ignore_eos[rows] = ign
         self.temperature[rows] = temps
+        self.top_k_rows[rows] = topk
+        self.top_p_rows[rows] = topp
         self.active[rows] = (~done).int()
         page = self.block_table[rows].gather(1, (plen.long() // PAGE)[:, None]).squeeze(1)
         self.slots[rows] = (page * PAGE + (plen % PAGE)).int()
@@ -737,6 +752,8 @@ def decode_gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
 
     M, K = x.shape
     N = w.shape[0]
+    if not x.is_cuda:
+        return F.linear(x, w, bias, residual)
     if M > 256:
         return gemm(x, w, bias=bias, residual=residual)
     bn = 64 if (N <= _BN64_MAX_N and K < 4096) else 128

@@ -272,17 +272,30 @@ class RLWorker:
         for i, exp in enumerate(items):
             pending.append(exp)
             if len(pending) == gas or i == len(items) - 1:
-                tot = torch.zeros(2)
+                tot = torch.zeros(2, dtype=torch.float64)
                 for e in pending:
                     m = e.action_mask.float()
                     tot[0] += m.sum()
                     tot[1] += (m.sum(-1) > 0).sum()
-                tot = self.strategy.all_reduce(tot.double(), "sum") if self.strategy.world_size > 1 else tot
-                info = {"dp_size": self.strategy.mesh.dp, "batch_num_tokens": float(tot[0]),
-                        "global_batch_size": float(tot[1])}
+                # totals of the optimizer-step window over the data-parallel group only (context- / tensor-parallel
+                # duplicates hold the same samples and must not be counted again), divided by gas because every
+                # micro-loss is divided by gas once more before backward (openrlhf/utils/loss_utils.py:62-80)
+                tot = self._dp_sum(tot)
+                info = {"dp_size": self.strategy.mesh.dp, "batch_num_tokens": float(tot[0]) / gas,
+                        "global_batch_size": float(tot[1]) / gas}
                 for j, e in enumerate(pending):
                     yield e, info, j == len(pending) - 1
                 pending = []
+
+    def _dp_sum(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum a small CPU tensor over the data-parallel group of this worker."""
+        s = self.strategy
+        if s.world_size == 1 or not dist.is_initialized() or s.mesh.dp == 1:
+            return t
+        g = s.dp_group()
+        work = t.to(self.device) if dist.get_backend(g) == "nccl" else t.clone()
+        dist.all_reduce(work, group=g)
+        return work.to(t.device)
 
     def fit(self, kl_ctl: float = 0.0, role: str = "actor") -> dict:
         """PPO epochs over this rank's replay buffer; returns token-/sample-weighted mean metrics."""

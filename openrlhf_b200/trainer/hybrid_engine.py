@@ -280,8 +280,8 @@ class HybridRLWorker:
             b = self._batch(chunk)
             b.index = [i for e in chunk for i in e.index]
             batches.append(b)
-        compute_advantages_and_returns(batches, self.args, self.kl_ctl.value,
-                                       dist_group=self.group if self.world > 1 else None)
+        compute_advantages_and_returns(batches, self.args, self.kl_ctl.value, dist_group=self.group,
+                                       distributed=self.world > 1)
         out = []
         from ..rl.experience import remove_padding_in_sequences, split_experience_batch
 

@@ -76,7 +76,7 @@ def test_worker_environment_and_user_overrides():
 
     os.environ["NCCL_DEBUG"] = "WARN"
     try:
-        g = ActorGroup("openrlhf_b200.runtime.testing.EnvWorker", 2, backend_env={"TOKENIZERS_PARALLELISM": "true"},
+        g = ActorGroup("worker_stubs.EnvWorker", 2, backend_env={"TOKENIZERS_PARALLELISM": "true"},
                        name="env")
         try:
             envs = get(g.async_run_method("env", ["RANK", "WORLD_SIZE", "MASTER_ADDR", "NCCL_DEBUG",

@@ -50,3 +50,16 @@ def test_plan_matches_slicing(preset, tp, src_world):
             got = dst[d.offset:d.offset + d.numel].view(d.shape)
             want = _expected(cfg, specs, flat, d.name, tp_rank, tp)
             assert torch.equal(got, want.reshape(d.shape)), d.name
+
+
+def test_long_contiguous_entries_are_split_below_the_int32_limit():
+    from openrlhf_b200.parallel.reshard import CopyEntry, ReshardPlan
+
+    big = 3 * (1 << 30) + 4096            # elements: more than an int32 can hold
+    parts = ReshardPlan.split_large([CopyEntry(128, 256, 1, big, big, big, 1), CopyEntry(0, 0, 4, 64, 128, 64, 0)])
+    assert [p.row_elems for p in parts[:-1]] == [1 << 30, 1 << 30, 1 << 30, 4096]
+    assert [p.src_off for p in parts[:-1]] == [128 + i * (1 << 30) for i in range(4)]
+    assert [p.dst_off for p in parts[:-1]] == [256 + i * (1 << 30) for i in range(4)]
+    assert all(p.src_rank == 1 and p.rows == 1 for p in parts[:-1]) and parts[-1].rows == 4
+    with pytest.raises(ValueError):
+        ReshardPlan([CopyEntry(0, 0, 2, 1 << 31, 1 << 31, 1 << 31, 0)], "cpu")

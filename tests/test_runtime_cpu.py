@@ -7,7 +7,7 @@ import torch
 
 from openrlhf_b200.runtime.core import (ActorGroup, CancelledError, RemoteError, WorkerDied, WorkerHandle, get, wait)
 
-W = "openrlhf_b200.runtime.testing.EchoWorker"
+W = "worker_stubs.EchoWorker"
 
 
 def test_rpc_tensors_and_coroutines():
@@ -80,7 +80,7 @@ def test_large_reply_travels_through_shared_memory_ring():
     from openrlhf_b200.utils import st_io
     if not st_io.available():
         pytest.skip("native library not built")
-    h = WorkerHandle("openrlhf_b200.runtime.testing.EchoWorker", kwargs={"tag": "ring"}, shm_bytes=8 << 20)
+    h = WorkerHandle("worker_stubs.EchoWorker", kwargs={"tag": "ring"}, shm_bytes=8 << 20)
     try:
         h.wait_started()
         big = torch.randn(512, 1024)                      # 2 MiB reply

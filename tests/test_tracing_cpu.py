@@ -32,7 +32,7 @@ def test_runtime_rpc_instants():
     from openrlhf_b200.runtime.core import WorkerHandle
     tracer.clear()
     tracer.enable()
-    h = WorkerHandle("openrlhf_b200.runtime.testing.EchoWorker", kwargs={"tag": "t"}, name="echo")
+    h = WorkerHandle("worker_stubs.EchoWorker", kwargs={"tag": "t"}, name="echo")
     try:
         h.wait_started()
         assert h.call("whoami").result(60)[0] == "t"

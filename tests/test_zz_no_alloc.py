@@ -27,33 +27,52 @@ def _call_noalloc(lib, q, kc, vc, bt, sl, out, splits, scale, status):
               ctypes.c_void_p(status.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def _case(B, Hq, Hkv, splits, lens, num_pages, max_pages, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    D, page = 128, 128
+    kc = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16, generator=g)
+    vc = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16, generator=g)
+    bt = torch.randperm(num_pages, device="cuda", generator=g)[: B * max_pages].reshape(B, max_pages).int()
+    sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16, generator=g)
+    return q, kc, vc, bt, sl
+
+
 def test_noalloc_decode_matches_regular_entry_point_twice():
     from openrlhf_b200.ops import _lib
     from openrlhf_b200.ops.attention import paged_decode
 
     lib = _lib.lib()
-    torch.manual_seed(0)
-    D, page, num_pages, max_pages = 128, 128, 96, 10
-    Hq, Hkv = 12, 2
-    scale = 1 / math.sqrt(D)
+    scale = 1 / math.sqrt(128)
     status = _lib.status_word(torch.device("cuda"))
-    for call, (B, splits, lens) in enumerate([(4, 3, [1, 300, 1280, 640]), (6, 2, [129, 5, 1000, 128, 257, 900])]):
-        kc = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16)
-        vc = torch.randn(num_pages * page, Hkv, D, device="cuda", dtype=torch.bfloat16)
-        bt = torch.randperm(num_pages, device="cuda")[: B * max_pages].reshape(B, max_pages).int()
-        sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
-        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cases = [
+        (4, 12, 2, 3, [1, 300, 1280, 640], 96, 10),               # ragged lengths, more splits than pages in row 0
+        (6, 12, 2, 2, [129, 5, 1000, 128, 257, 900], 96, 10),     # second call reuses the scratch of the first
+        (3, 12, 2, 1, [700, 1, 256], 96, 10),                     # splits == 1: the scratch is not touched at all
+        (64, 32, 8, 4, [200] * 64, 130, 2),                       # B * Hq * splits == 8192: exactly the maximum
+    ]
+    for call, (B, Hq, Hkv, splits, lens, num_pages, max_pages) in enumerate(cases):
+        q, kc, vc, bt, sl = _case(B, Hq, Hkv, splits, lens, num_pages, max_pages, seed=call)
         expect = paged_decode(q, kc, vc, bt, sl, scale, splits=splits)
         got = torch.empty_like(q)
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # the driver's own view of device memory: a cudaMalloc inside the library would show up here, which
+        # torch.cuda.memory_allocated() (the caching allocator's bookkeeping) cannot see. The first call is excluded
+        # because it may load the kernel's module lazily.
+        free_before = torch.cuda.mem_get_info()[0]
+        torch_before = torch.cuda.memory_allocated()
         rc = _call_noalloc(lib, q, kc, vc, bt, sl, got, splits, scale, status)
         assert rc == 0, f"call {call}: rc {rc}"
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() == torch_before
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] >= free_before, f"call {call}: device memory was allocated"
         _lib.check_status()
         err = (got.float() - expect.float()).abs().max().item()
         ref = expect.float().abs().max().item()
         assert err <= 2e-2 * ref + 2e-2, f"call {call}: max err {err} (scale {ref})"
+        # same kernel, same inputs, fixed merge order: the two entry points agree bit for bit
+        assert torch.equal(got, expect), f"call {call}: outputs differ (max err {err})"
 
 
 def test_noalloc_rejects_oversized_problem():
