@@ -2,9 +2,11 @@
 controller. Flag-compatible with openrlhf/cli/train_ppo_ray.py:198-717 (the module keeps its name for launch-script
 compatibility; the workers are this framework's runtime processes, one per GPU, not Ray actors).
 
-Placement: with ``--train.colocate_all`` (hybrid engine) every GPU worker hosts all roles and the rollout engine reads
-the buffer the actor's optimizer writes. Without it, rollout engines get their own GPUs after the trainer GPUs and
-receive weights by NCCL broadcast from the actor.
+Placement (``plan_placement``): with ``--train.colocate_all`` (hybrid engine) every GPU worker hosts all roles, the
+rollout engine reads the buffer the actor's optimizer writes (or is refreshed from the ZeRO-3 / tensor-parallel shards by
+one copy kernel), and ``--vllm.tensor_parallel_size`` consecutive workers form one engine. Without it every role group
+gets its own GPUs and its own process-group world; the rollout engines receive weights from trainer rank 0 over a
+separate weight-update group, and ``--train.async_enable`` then overlaps generation with training.
 """
 from __future__ import annotations
 
@@ -148,38 +150,116 @@ def validate(args):
     return a
 
 
+def plan_placement(a, has_critic: bool, has_ref: bool, has_reward: bool) -> list[dict]:
+    """Which worker groups to start, on which GPUs, with which roles (openrlhf/cli/train_ppo_ray.py:40-142).
+
+    ``--train.colocate_all``: one group of ``actor.num_nodes x actor.num_gpus_per_node`` workers hosts every role, and
+    ``--vllm.tensor_parallel_size`` consecutive workers form one rollout engine (hybrid engine).
+    Otherwise each role gets its own GPUs in the order actor, critic, reference, reward, rollout engines, where
+    ``--train.colocate_actor_ref`` puts the reference model on the actor's workers and
+    ``--train.colocate_critic_reward`` the reward model on the critic's. Returns a list of
+    {"name", "roles", "gpus", "serves"} entries; "serves" names the roles the trainer addresses through that group."""
+    n_actor = a.actor.num_nodes * a.actor.num_gpus_per_node
+    tp = max(1, a.vllm.tensor_parallel_size)
+    if a.train.colocate_all:
+        if n_actor % tp:
+            raise ValueError(f"--vllm.tensor_parallel_size {tp} does not divide the {n_actor} hybrid-engine workers")
+        if a.vllm.num_engines * tp != n_actor:
+            print(f"[Info] hybrid engine: {n_actor // tp} rollout engines x TP {tp} on the {n_actor} workers "
+                  f"(--vllm.num_engines {a.vllm.num_engines} adjusted)")
+            a.vllm.num_engines = n_actor // tp
+        roles = ["actor", "rollout"] + (["critic"] if has_critic else []) + (["ref"] if has_ref else []) + \
+                (["reward"] if has_reward else [])
+        return [{"name": "rl", "roles": tuple(roles), "gpus": list(range(n_actor)), "serves": tuple(roles)}]
+    groups, nxt = [], 0
+
+    def take(n):
+        nonlocal nxt
+        ids = list(range(nxt, nxt + n))
+        nxt += n
+        return ids
+
+    actor_roles = ["actor"] + (["ref"] if has_ref and a.train.colocate_actor_ref else [])
+    groups.append({"name": "actor", "roles": tuple(actor_roles), "gpus": take(n_actor), "serves": tuple(actor_roles)})
+    if has_critic:
+        cr = ["critic"] + (["reward"] if has_reward and a.train.colocate_critic_reward else [])
+        groups.append({"name": "critic", "roles": tuple(cr), "gpus": take(a.critic.num_nodes * a.critic.num_gpus_per_node),
+                       "serves": tuple(cr)})
+    if has_ref and not a.train.colocate_actor_ref:
+        groups.append({"name": "ref", "roles": ("ref",), "gpus": take(a.ref.num_nodes * a.ref.num_gpus_per_node),
+                       "serves": ("ref",)})
+    if has_reward and not (has_critic and a.train.colocate_critic_reward):
+        groups.append({"name": "reward", "roles": ("reward",),
+                       "gpus": take(a.reward.num_nodes * a.reward.num_gpus_per_node), "serves": ("reward",)})
+    groups.append({"name": "rollout", "roles": ("rollout",), "gpus": take(a.vllm.num_engines * tp),
+                   "serves": ("rollout",)})
+    return groups
+
+
 def train(args):
-    from ..trainer.ppo_trainer import PPOTrainer
+    import copy
+
+    import torch
+
+    from ..runtime.core import free_port
+    from ..trainer.ppo_trainer import PPOTrainer, RoleGroups
     from ..trainer.ppo_trainer_async import PPOTrainerAsync
 
     a = args
     os.environ.setdefault("TOKENIZERS_PARALLELISM", "true")
     strategy = get_strategy(a)                      # controller-side copy: flags + CPU helpers, no process group
-    n_train = a.actor.num_nodes * a.actor.num_gpus_per_node
     has_critic = a.critic.model_name_or_path is not None
     has_ref = a.algo.kl.init_coef > 0
     has_reward = bool(a.reward.model_name_or_path) and not a.reward.remote_url
-    import torch
-
-    backend = "nccl" if torch.cuda.is_available() else "gloo"
-    # one worker per GPU; under --train.colocate_all every worker carries every role (hybrid engine)
-    roles = ["actor", "rollout"] + (["critic"] if has_critic else []) + (["ref"] if has_ref else []) + \
-            (["reward"] if has_reward else [])
-    if not a.train.colocate_all:
-        print("[Info] roles are placed on the same GPU workers; pass --train.colocate_all to make it explicit.")
-    group = ActorGroup("openrlhf_b200.runtime.workers.RLWorker", n_train,
-                       init_kwargs={"args": a, "roles": tuple(roles), "max_steps": 1000, "backend": backend},
-                       duplicate_actors=a.ds.ring_attn_size * a.ds.tensor_parallel_size, name="rl")
-    engines = group.workers[:: max(1, a.vllm.tensor_parallel_size)][: a.vllm.num_engines] or group.workers
-    cls = PPOTrainerAsync if a.train.async_enable else PPOTrainer
-    trainer = cls(a.actor.model_name_or_path, strategy, group, engines, has_critic, has_ref, has_reward)
+    on_gpu = torch.cuda.is_available()
+    backend = "nccl" if on_gpu else "gloo"
+    plan = plan_placement(a, has_critic, has_ref, has_reward)
+    need = max(max(g["gpus"]) for g in plan) + 1
+    if on_gpu and need > torch.cuda.device_count():
+        raise ValueError(f"the placement needs {need} GPUs on this node but {torch.cuda.device_count()} are visible; "
+                         "pass --train.colocate_all (hybrid engine) or lower the per-role GPU counts")
+    if a.train.async_enable and a.train.colocate_all and on_gpu:
+        print("[Info] --train.async_enable with --train.colocate_all time-slices the same GPUs; give the rollout "
+              "engines their own GPUs (drop --train.colocate_all) for generation to overlap with training.")
+    dup_train = a.ds.ring_attn_size * a.ds.tensor_parallel_size
+    tp = max(1, a.vllm.tensor_parallel_size)
+    made: dict[str, ActorGroup] = {}
     try:
+        for g in plan:
+            ga = a
+            if g["name"] in ("ref", "reward", "rollout"):
+                # inference-only worlds of their own size: no ring-attention / tensor-parallel training mesh there
+                ga = copy.deepcopy(a)
+                ga.ds.ring_attn_size = ga.ds.tensor_parallel_size = 1
+            dup = dup_train if ga is a else 1
+            made[g["name"]] = ActorGroup("openrlhf_b200.runtime.workers.RLWorker", len(g["gpus"]),
+                                         init_kwargs={"args": ga, "roles": g["roles"], "max_steps": 1000,
+                                                      "backend": backend},
+                                         gpu_ids=g["gpus"] if on_gpu else None, duplicate_actors=dup, name=g["name"])
+        by_role = {r: made[g["name"]] for g in plan for r in g["serves"]}
+        main = by_role["actor"]
+        rollout_group = by_role["rollout"]
+        groups = RoleGroups(main, by_role.get("critic"), by_role.get("ref"), by_role.get("reward"),
+                            rollout_group if rollout_group is not main else None)
+        if rollout_group is not main:
+            # weight-update group: trainer rank 0 + every rollout rank, next to the two training / rollout worlds
+            port, n = free_port(), 1 + len(rollout_group)
+            futs = [main.workers[0].call("setup_sync_group", "127.0.0.1", port, 0, n, backend)]
+            futs += [w.call("setup_sync_group", "127.0.0.1", port, 1 + i, n, backend)
+                     for i, w in enumerate(rollout_group.workers)]
+            get(futs)
+        engines = rollout_group.workers[::tp]
+        followers = [w for i, w in enumerate(rollout_group.workers) if i % tp]
+        cls = PPOTrainerAsync if a.train.async_enable else PPOTrainer
+        trainer = cls(a.actor.model_name_or_path, strategy, groups, engines, has_critic, has_ref, has_reward,
+                      rollout_followers=followers)
         trainer.fit()
-        get(group.async_run_method("save_model", role="actor"))
+        get(main.async_run_method("save_model", role="actor"))
         if has_critic and a.critic.save_value_network:
-            get(group.async_run_method("save_model", role="critic"))
+            get(groups.critic.async_run_method("save_model", role="critic"))
     finally:
-        group.shutdown()
+        for g in made.values():
+            g.shutdown()
 
 
 if __name__ == "__main__":

@@ -19,7 +19,7 @@ def train(args):
     strategy.setup_distributed()
     model = get_llm_for_sequence_regression(args.model.model_name_or_path, "reward", init_value_head=True,
                                             value_head_prefix=args.ds.value_head_prefix, device=strategy.device(),
-                                            packing_samples=args.ds.packing_samples, shard_world=strategy.mesh.dp,
+                                            packing_samples=args.ds.packing_samples, shard_world=strategy.zero_world,
                                             seed=args.train.seed, load_in_4bit=args.ds.load_in_4bit)
     tokenizer = get_tokenizer(args.model.model_name_or_path, model, "left", strategy,
                               use_fast=not args.data.disable_fast_tokenizer)

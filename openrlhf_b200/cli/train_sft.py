@@ -19,7 +19,7 @@ def train(args):
     strategy = get_strategy(args)
     strategy.setup_distributed()
     model = Actor(args.model.model_name_or_path, device=strategy.device(), packing_samples=args.ds.packing_samples,
-                  shard_world=strategy.mesh.dp, seed=args.train.seed, lora_rank=args.ds.lora.rank,
+                  shard_world=strategy.zero_world, seed=args.train.seed, lora_rank=args.ds.lora.rank,
                   lora_alpha=args.ds.lora.alpha, target_modules=args.ds.lora.target_modules,
                   lora_dropout=args.ds.lora.dropout, load_in_4bit=args.ds.load_in_4bit)
     tokenizer = get_tokenizer(args.model.model_name_or_path, model.model, "right", strategy,

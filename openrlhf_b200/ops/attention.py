@@ -77,16 +77,18 @@ def _query_tiles(cu_seqlens: torch.Tensor, T: int, n_seqs: int, rows: int = 128)
     return seq.int().contiguous(), q0.int().contiguous(), n
 
 
-def attn_fwd_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, scale: float):
+def attn_fwd_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, scale: float,
+                     tiles=None):
     """tcgen05 causal varlen forward. q [T,Hq,128], k/v [T,Hkv,128] (views with a common row stride are fine).
-    Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32)."""
+    Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32). `tiles` = (tile_seq, tile_q0, n): run only these query tiles
+    (rows of other tiles keep whatever `out` held); see attention_with_prefix."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     assert D == 128 and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D
     assert k.stride(1) == D and v.stride(1) == D and k.stride(2) == 1 and v.stride(2) == 1
     n_seqs = cu_seqlens.numel() - 1
     rows = 128 if (Hq // Hkv) % 2 == 0 else 256     # two heads per CTA, or two 128-row halves of one head
-    tile_seq, tile_q0, n = _query_tiles_cached(cu_seqlens, T, n_seqs, rows)
+    tile_seq, tile_q0, n = tiles if tiles is not None else _query_tiles_cached(cu_seqlens, T, n_seqs, rows)
     out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
     rc = _lib.lib().b200_attn_fwd(
@@ -215,6 +217,61 @@ def attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale):
             return _AttnVarlen.apply(q, k, v, cu_seqlens, max_seqlen, scale)
         return attn_fwd_tcgen05(q, k, v, cu_seqlens, scale)[0]
     return _library_varlen(q, k, v, cu_seqlens, max_seqlen, scale)
+
+
+def query_tile_rows(Hq: int, Hkv: int) -> int:
+    """Rows per query tile of the forward kernel: two heads of an even GQA group share 128 rows, otherwise one head
+    takes two 128-row halves."""
+    return 128 if (Hq // Hkv) % 2 == 0 else 256
+
+
+def attention_with_prefix(q_new: torch.Tensor, k_all: torch.Tensor, v_all: torch.Tensor, cu_all: list[int],
+                          starts: list[int], scale: float) -> torch.Tensor:
+    """Causal attention of the NEW tokens of every sequence over its cached prefix plus the new tokens.
+
+    k_all / v_all [Ta, Hkv, D]: keys / values of every sequence in full (prefix rows first), packed with boundaries
+    cu_all (host ints). Sequence i has starts[i] prefix rows; q_new [Tn, Hq, D] holds the queries of the remaining rows
+    in the same packed order. Used by chunked prefill, prefix-cache hits and the re-prefill of preempted rows.
+
+    On the GPU the forward kernel runs unchanged: the queries are scattered to their global rows of a [Ta] buffer and
+    only the query tiles that contain new rows are put on the tile list, so prefix rows cost no attention work."""
+    Hq, D = q_new.shape[1], q_new.shape[2]
+    Hkv = k_all.shape[1]
+    n = len(starts)
+    new_rows = torch.cat([torch.arange(cu_all[i] + starts[i], cu_all[i + 1]) for i in range(n)])
+    if not q_new.is_cuda:
+        rep = Hq // Hkv
+        out = torch.empty_like(q_new)
+        o = 0
+        for i in range(n):
+            a, b, s0 = cu_all[i], cu_all[i + 1], starts[i]
+            L, m = b - a, b - a - s0
+            qs = q_new[o:o + m].float().transpose(0, 1)
+            ks = k_all[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
+            vs = v_all[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
+            att = (qs @ ks.transpose(1, 2)) * scale
+            keep = torch.arange(L)[None, :] <= (torch.arange(m)[:, None] + s0)
+            att = att.masked_fill(~keep, float("-inf")).softmax(-1)
+            out[o:o + m] = (att @ vs).transpose(0, 1).to(q_new.dtype)
+            o += m
+        return out
+    dev = q_new.device
+    Ta = k_all.shape[0]
+    rows = query_tile_rows(Hq, Hkv)
+    seq_l, q0_l = [], []
+    for i in range(n):
+        L = cu_all[i + 1] - cu_all[i]
+        for q0 in range(starts[i] // rows * rows, L, rows):
+            seq_l.append(i)
+            q0_l.append(q0)
+    tiles = (torch.tensor(seq_l, dtype=torch.int32, device=dev), torch.tensor(q0_l, dtype=torch.int32, device=dev),
+             len(seq_l))
+    q_full = torch.zeros(Ta, Hq, D, dtype=q_new.dtype, device=dev)
+    idx = new_rows.to(dev)
+    q_full.index_copy_(0, idx, q_new)
+    cu = torch.tensor(cu_all, dtype=torch.int32, device=dev)
+    out, _ = attn_fwd_tcgen05(q_full, k_all.contiguous(), v_all.contiguous(), cu, scale, tiles=tiles)
+    return out.index_select(0, idx)
 
 
 _decode_ws: dict = {}

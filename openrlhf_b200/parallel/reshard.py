@@ -117,8 +117,20 @@ def build_plan(cfg: ModelConfig, tp_rank: int = 0, tp: int = 1, src_world: int =
                         p += m
                 done += n
             return
-        for i in range(rows):      # strided source rows: each row may sit in a different slice
-            emit(src_off + i * src_ld, dst_off + i * dst_ld, 1, row_elems, row_elems, row_elems)
+        # strided source rows: runs of rows that lie entirely inside one slice stay one strided block; a row that
+        # straddles a slice boundary is cut there
+        i = 0
+        while i < rows:
+            a = src_off + i * src_ld
+            r = a // S
+            if (a + row_elems - 1) // S != r:
+                emit(a, dst_off + i * dst_ld, 1, row_elems, row_elems, row_elems)
+                i += 1
+                continue
+            # last row j >= i whose end is still inside slice r
+            j = min(rows - 1, i + ((r + 1) * S - a - row_elems) // src_ld)
+            entries.append(CopyEntry(a - r * S, dst_off + i * dst_ld, j - i + 1, row_elems, src_ld, dst_ld, r))
+            i = j + 1
 
     for s, d in zip(src_specs, dst_specs):
         if len(s.shape) == 3 or len(s.shape) == 1 and tp == 1:

@@ -69,8 +69,15 @@ class LRScheduler:
 class ZeroEngine:
     def __init__(self, model, lr: float = 1e-6, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  max_norm: float = 1.0, zero_stage: int = 2, group=None, scheduler: LRScheduler | None = None,
-                 train: bool = True, use_symm: bool | None = None, symm=None):
+                 train: bool = True, use_symm: bool | None = None, symm=None, adam_offload: bool = False):
+        """use_symm: run the multi-rank optimizer step with the peer-memory kernels of ``parallel/symm.py``. None picks
+        them whenever they apply (CUDA, more than one rank, all ranks on this node, no tensor-parallel shard); the
+        model's flat buffer is then moved into symmetric memory and every parameter re-bound to it, so build the
+        engine before anything that keeps views of the parameters. ``OPENRLHF_B200_SYMM=0`` selects NCCL.
+        adam_offload: keep master weights and moments in pinned host memory between optimizer steps
+        (``--ds.adam_offload``, openrlhf/utils/deepspeed/deepspeed_utils.py:24-28)."""
         self.model = model
+        self.adam_offload = bool(adam_offload) and train
         self.flat = model.flat
         self.device = self.flat.device
         self.group = group
@@ -104,6 +111,8 @@ class ZeroEngine:
             self.tp_rep_mask = self.tp.replicated_mask(model, self.lo, self.hi, self.device)
         on_gpu = self.flat.is_cuda
         self.symm = symm if (symm is not None and on_gpu and self.world > 1) else None
+        if self.symm is None and self._want_symm(use_symm, on_gpu):
+            self.symm = self._move_to_symmetric_memory()
         if self.symm is not None:
             assert self.symm.param.data_ptr() == self.flat.data_ptr(), "the model must be built on symm.param"
             self.grad_flat = self.symm.grad
@@ -123,8 +132,36 @@ class ZeroEngine:
                 if s.decay and model.p(s.name).requires_grad:      # frozen parameters (no gradient) must not decay
                     mask[s.offset:s.offset + s.numel] = True
             self.decay_mask = mask[sl].clone()
+        if self.adam_offload:
+            self.offload_states()
 
     # ------------------------------------------------------------------ allocation helpers
+    def _want_symm(self, use_symm, on_gpu: bool) -> bool:
+        import os
+
+        if not on_gpu or self.world == 1 or self.tp is not None or self.zero_stage < 1:
+            if use_symm:
+                raise ValueError("the peer-memory optimizer step needs CUDA, more than one rank, ZeRO stage >= 1 and no "
+                                 "tensor-parallel shard")
+            return False
+        if use_symm is None:
+            local = int(os.environ.get("LOCAL_WORLD_SIZE", dist.get_world_size()))
+            use_symm = os.environ.get("OPENRLHF_B200_SYMM", "1") == "1" and local >= dist.get_world_size()
+        return bool(use_symm)
+
+    def _move_to_symmetric_memory(self):
+        """Re-home the flat parameter buffer in symmetric memory (peers can then address it) and re-bind the views."""
+        from .symm import SymmBuffers
+
+        symm = SymmBuffers(self.group, self.padded, self.device)
+        n = min(self.flat.numel(), self.padded)
+        symm.param[:n].copy_(self.flat[:n])
+        for s_, p in self.model.named_specs():
+            p.data = symm.param[s_.offset:s_.offset + s_.numel].view(s_.shape)
+        self.model.flat = symm.param
+        self.flat = symm.param
+        return symm
+
     @staticmethod
     def padded_numel(total_numel: int, world: int) -> int:
         per = ((total_numel + world - 1) // world + 255) // 256 * 256
@@ -153,6 +190,8 @@ class ZeroEngine:
         """One optimizer step. `grad_scale` multiplies the accumulated gradient (1 / accumulation steps)."""
         self.opt_step += 1
         lr = self.current_lr()
+        if self.adam_offload:
+            self.reload_states()
         if self.tp is not None:
             self.tp.sync_replicated_grads(self.model)
         if self.symm is not None:
@@ -163,6 +202,8 @@ class ZeroEngine:
             self._step_reference(lr, grad_scale)
         if self.scheduler is not None:
             self.scheduler.step()
+        if self.adam_offload:
+            self.offload_states()
 
     def _reduce_grads(self) -> torch.Tensor:
         """Mean of gradients over data-parallel ranks; returns this rank's fp32 shard."""
@@ -268,11 +309,16 @@ class ZeroEngine:
         """Move optimizer shards to pinned host memory (hybrid-engine sleep: openrlhf/utils/deepspeed/deepspeed_utils.py:151-211)."""
         if not self.trainable or getattr(self, "_offloaded", False):
             return
-        self._host = [t.to("cpu", non_blocking=False).pin_memory() if t.is_cuda else t for t in
-                      (self.master, self.exp_avg, self.exp_avg_sq)]
+        keep = getattr(self, "_host_bufs", None)
+        if keep is None:
+            keep = self._host_bufs = [torch.empty(t.shape, dtype=t.dtype, device="cpu",
+                                                  pin_memory=t.is_cuda) for t in (self.master, self.exp_avg, self.exp_avg_sq)]
+        for h, t in zip(keep, (self.master, self.exp_avg, self.exp_avg_sq)):
+            h.copy_(t, non_blocking=False)
+        self._host = keep
         self.master = self.exp_avg = self.exp_avg_sq = None
         self._offloaded = True
-        if self.flat.is_cuda:
+        if self.flat.is_cuda and not self.adam_offload:
             torch.cuda.empty_cache()
 
     def reload_states(self):
@@ -284,11 +330,24 @@ class ZeroEngine:
 
     # ------------------------------------------------------------------ state for checkpoints
     def shard_state(self) -> dict:
+        if getattr(self, "_offloaded", False):
+            m, a, b = self._host
+            return {"master": m, "exp_avg": a, "exp_avg_sq": b, "lo": self.lo, "hi": self.hi,
+                    "opt_step": self.opt_step, "world": self.world, "total_numel": self.model.total_numel,
+                    "shard_size": self.shard_size}
         return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
                 "lo": self.lo, "hi": self.hi, "opt_step": self.opt_step, "world": self.world,
                 "total_numel": self.model.total_numel, "shard_size": self.shard_size}
 
     def load_shard_state(self, master, exp_avg, exp_avg_sq, opt_step):
+        was_off = getattr(self, "_offloaded", False)
+        if was_off:
+            self.reload_states()
+        self._load_shard_state(master, exp_avg, exp_avg_sq, opt_step)
+        if was_off:
+            self.offload_states()
+
+    def _load_shard_state(self, master, exp_avg, exp_avg_sq, opt_step):
         self.master.copy_(master)
         self.exp_avg.copy_(exp_avg)
         self.exp_avg_sq.copy_(exp_avg_sq)

@@ -40,8 +40,13 @@ def _round(n: int, m: int) -> int:
 class Zero3Engine:
     def __init__(self, model: TransformerLM, lr: float = 1e-6, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.0, max_norm: float = 1.0, group=None, scheduler: LRScheduler | None = None,
-                 expert_range: tuple[int, int] | None = None):
+                 expert_range: tuple[int, int] | None = None, train: bool = True):
+        """train=False: a frozen model (reference policy, reward model). Only the bf16 parameter slice and the working
+        buffer with its two layer slots exist; forward passes gather layer by layer exactly as in training (the
+        reference shards its frozen models the same way with a stage-3 inference engine,
+        openrlhf/utils/deepspeed/deepspeed.py:460-487)."""
         self.model = model
+        self.trainable = train
         # expert parallelism: this rank only computes experts [lo, hi) of every MoE layer, so only those are gathered
         self.expert_range = expert_range
         initialised = dist.is_available() and dist.is_initialized()
@@ -92,9 +97,11 @@ class Zero3Engine:
             self.param_shard = symm_mem.empty(self.per, dtype=torch.bfloat16, device=self.device)
             self._hp = symm_mem.rendezvous(self.param_shard, self.group)
             self.param_ptrs = list(self._hp.buffer_ptrs)
-            self.grad_work = symm_mem.empty(self.work_size, dtype=torch.float32, device=self.device)
-            self._hg = symm_mem.rendezvous(self.grad_work, self.group)
-            self.grad_ptrs = list(self._hg.buffer_ptrs)
+            self.grad_work = self.grad_ptrs = None
+            if train:
+                self.grad_work = symm_mem.empty(self.work_size, dtype=torch.float32, device=self.device)
+                self._hg = symm_mem.rendezvous(self.grad_work, self.group)
+                self.grad_ptrs = list(self._hg.buffer_ptrs)
             self.pad = symm_mem.empty(1024, dtype=torch.int32, device=self.device)
             self.pad.zero_()
             self._hs = symm_mem.rendezvous(self.pad, self.group)
@@ -102,16 +109,18 @@ class Zero3Engine:
             self.bar_epoch = 0
         else:
             self.param_shard = torch.empty(self.per, dtype=full.dtype, device=self.device)
-            self.grad_work = torch.zeros(self.work_size, dtype=torch.float32, device=self.device)
+            self.grad_work = torch.zeros(self.work_size, dtype=torch.float32, device=self.device) if train else None
         self.param_shard.copy_(full[self.lo:self.hi])
-        self.grad_work.zero_()
-        self.master = self.param_shard.float().clone()
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad_shard = torch.zeros_like(self.master)
+        self.master = self.exp_avg = self.exp_avg_sq = self.grad_shard = None
+        if train:
+            self.grad_work.zero_()
+            self.master = self.param_shard.float().clone()
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
+            self.grad_shard = torch.zeros_like(self.master)
         self.scalars = torch.zeros(4, dtype=torch.float32, device=self.device)
         self.decay_mask = None
-        if weight_decay != 0.0:
+        if train and weight_decay != 0.0:
             mask = torch.zeros(self.padded, dtype=torch.bool, device=self.device)
             for s in specs:
                 if s.decay:
@@ -126,7 +135,8 @@ class Zero3Engine:
             w_off = self.res_map[s.name] if i < 0 else self.slot_base[i % 2] + (s.offset - self.layer_rng[i][0])
             self.work_off[s.name] = w_off
             p.data = self.work[w_off:w_off + s.numel].view(s.shape)
-            p.main_grad = self.grad_work[w_off:w_off + s.numel].view(s.shape)
+            if train:
+                p.main_grad = self.grad_work[w_off:w_off + s.numel].view(s.shape)
         model.flat = self.work          # the logical flat buffer no longer exists on this rank
         model.z3 = self
         del full
@@ -134,7 +144,8 @@ class Zero3Engine:
         self._inflight: dict = {}       # layer -> event of its gather on the side stream
         self._side = None
         self._plans: dict = {}
-        self._tmp = torch.empty(min(self.per, _round(slot, 256)), dtype=torch.float32, device=self.device)
+        self._tmp = torch.empty(min(self.per, _round(slot, 256)) if train else 0, dtype=torch.float32,
+                                device=self.device)
         self._pending_zero = -1
         self._sync()
         self.gather_resident()
@@ -303,6 +314,7 @@ class Zero3Engine:
 
     # ------------------------------------------------------------------------------------------------ training API
     def backward(self, loss: torch.Tensor):
+        assert self.trainable, "this engine holds a frozen model"
         loss.backward()
         self.micro_steps += 1
         if not self.on_gpu:
@@ -346,6 +358,7 @@ class Zero3Engine:
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0) -> None:
+        assert self.trainable, "this engine holds a frozen model"
         self.opt_step += 1
         lr = self.current_lr()
         g = self.grad_shard
@@ -388,6 +401,30 @@ class Zero3Engine:
         self.gather_resident()
         if self.scheduler is not None:
             self.scheduler.step()
+
+    # ------------------------------------------------------------------------------------------------ sleep
+    def offload_states(self):
+        """Optimizer slices (master weights, moments, gradient slice) to pinned host memory: --ds.enable_sleep."""
+        if not self.trainable or getattr(self, "_host", None) is not None:
+            return
+        names = ("master", "exp_avg", "exp_avg_sq", "grad_shard")
+        self._host = {}
+        for n in names:
+            t = getattr(self, n)
+            h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=t.is_cuda)
+            h.copy_(t)
+            self._host[n] = h
+            setattr(self, n, None)
+        if self.on_gpu:
+            torch.cuda.empty_cache()
+
+    def reload_states(self):
+        host = getattr(self, "_host", None)
+        if host is None:
+            return
+        for n, h in host.items():
+            setattr(self, n, h.to(self.device, non_blocking=True))
+        self._host = None
 
     # ------------------------------------------------------------------------------------------------ full views
     @torch.no_grad()

@@ -19,7 +19,11 @@ logger = logging.getLogger(__name__)
 
 class RemoteExperienceMaker:
     def __init__(self, group, kl_controller, strategy, tokenizer, has_critic: bool, has_ref: bool, has_reward: bool):
-        self.group, self.kl_ctl, self.strategy, self.args = group, kl_controller, strategy, strategy.args
+        from ..trainer.ppo_trainer import RoleGroups
+
+        self.groups = group if isinstance(group, RoleGroups) else RoleGroups(group)
+        self.group = self.groups.actor
+        self.kl_ctl, self.strategy, self.args = kl_controller, strategy, strategy.args
         self.tokenizer = tokenizer
         self.has_critic, self.has_ref, self.has_reward = has_critic, has_ref, has_reward
         self.advantage_estimator = self.args.algo.advantage.estimator
@@ -56,14 +60,15 @@ class RemoteExperienceMaker:
                   attention_mask=[s.attention_mask for s in samples], role=[role] * len(samples))
         if role != "critic" and any(any(m for m in (s.mm_train_inputs or [])) for s in samples):
             kw["mm_train_inputs"] = [s.mm_train_inputs for s in samples]      # per-sample image inputs of each batch
-        futs = self.group.async_run_method_batch("forward", **kw)
+        g = self.groups.of(role)
+        futs = g.async_run_method_batch("forward", **kw)
         if sync:
             get(futs)
-            get(self.group.async_run_method("empty_cache"))
+            get(g.async_run_method("empty_cache"))
         return futs
 
-    def _flatten(self, futs):
-        dup = self.group.duplicate_actors
+    def _flatten(self, futs, role: str = "actor"):
+        dup = self.groups.of(role).duplicate_actors
         return [x for chunk in get(futs)[::dup] for x in chunk]
 
     @torch.no_grad()
@@ -75,7 +80,7 @@ class RemoteExperienceMaker:
         if samples[0].rewards is None:
             if not self.has_reward:
                 raise ValueError("samples carry no rewards (reward function failed?) and no reward model is configured")
-            r_futs = self.group.async_run_method_batch(
+            r_futs = self.groups.reward.async_run_method_batch(
                 "forward_reward", sequences=[s.sequences for s in samples],
                 attention_mask=[s.attention_mask for s in samples], pad_sequence=[True] * len(samples))
             if colocated:
@@ -83,11 +88,11 @@ class RemoteExperienceMaker:
         lp_futs = self._forward("actor", samples, colocated or a.train.colocate_actor_ref)
         v_futs = self._forward("critic", samples, colocated or a.train.colocate_critic_reward) if self.has_critic else None
         b_futs = self._forward("ref", samples, colocated or a.train.colocate_actor_ref) if self.has_ref else None
-        logps = self._flatten(lp_futs)
-        base = self._flatten(b_futs) if b_futs is not None else [None] * len(samples)
-        vals = self._flatten(v_futs) if v_futs is not None else [None] * len(samples)
+        logps = self._flatten(lp_futs, "actor")
+        base = self._flatten(b_futs, "ref") if b_futs is not None else [None] * len(samples)
+        vals = self._flatten(v_futs, "critic") if v_futs is not None else [None] * len(samples)
         if r_futs is not None:
-            for s, r in zip(samples, self._flatten(r_futs)):
+            for s, r in zip(samples, self._flatten(r_futs, "reward")):
                 s.rewards = r
                 s.info["reward"] = r
         if not (len(samples) == len(logps) == len(base) == len(vals)):

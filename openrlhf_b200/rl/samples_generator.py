@@ -70,8 +70,12 @@ def response_to_experience(response: dict, max_len: int) -> Experience:
 
 
 class SamplesGenerator:
-    def __init__(self, engines: list, strategy, tokenizer, prompts_dataloader, eval_dataloader=None):
-        self.engines = engines               # WorkerHandle objects that hold the rollout role
+    def __init__(self, engines: list, strategy, tokenizer, prompts_dataloader, eval_dataloader=None,
+                 followers: list | None = None):
+        self.engines = engines               # WorkerHandle objects that hold the rollout role (leaders under TP)
+        # members of tensor-parallel rollout engines other than their leader: they mirror the leader for the length
+        # of a generation phase (rollout/tp_engine.py::TPLockstepEngine)
+        self.followers = list(followers or [])
         self.strategy, self.args = strategy, strategy.args
         self.tokenizer = tokenizer
         self.prompts_dataloader, self.eval_dataloader = prompts_dataloader, eval_dataloader
@@ -80,7 +84,28 @@ class SamplesGenerator:
 
     # ------------------------------------------------------------------ engine helpers
     def _call_all(self, method: str, *a, **kw):
+        if method in ("wake_up", "sleep"):       # memory management concerns every member of an engine
+            return get([e.call(method, *a, **kw) for e in self.engines + self.followers])
         return get([e.call(method, *a, **kw) for e in self.engines])
+
+    class _Phase:
+        """Generation phase: followers enter their mirror loop, the leaders release them on exit."""
+
+        def __init__(self, gen):
+            self.gen = gen
+
+        def __enter__(self):
+            self.futs = [f.call("follow_generation") for f in self.gen.followers]
+            return self
+
+        def __exit__(self, *exc):
+            if self.gen.followers:
+                get([e.call("end_generation") for e in self.gen.engines])
+                get(self.futs)
+            return False
+
+    def generation_phase(self):
+        return SamplesGenerator._Phase(self)
 
     def _dispatch(self, prompts, labels, images=None, **gen):
         sp = SamplingParams(temperature=gen.get("temperature", 1.0), top_p=gen.get("top_p", 1.0),
@@ -109,9 +134,10 @@ class SamplesGenerator:
         if self.args.vllm.enable_sleep:
             self._call_all("wake_up")
         out = []
-        for _, prompts, labels, images in self.eval_dataloader:
-            for res in get(self._dispatch(list(prompts), list(labels), list(images), **gen)):
-                out += [response_to_experience(r, gen.get("max_len", 2048)) for r in res]
+        with self.generation_phase():
+            for _, prompts, labels, images in self.eval_dataloader:
+                for res in get(self._dispatch(list(prompts), list(labels), list(images), **gen)):
+                    out += [response_to_experience(r, gen.get("max_len", 2048)) for r in res]
         if self.args.vllm.enable_sleep:
             self._call_all("sleep")
         return out
@@ -129,7 +155,9 @@ class SamplesGenerator:
             if a.vllm.enable_sleep:
                 self._call_all("wake_up")
             n_prompts = getattr(a.rollout, "vllm_generate_batch_size", None) or a.rollout.batch_size
-            exps, consumed, done = self._generate(self._dataloader_iter, n_prompts, a.algo.dynamic_filtering_enable, **gen)
+            with self.generation_phase():
+                exps, consumed, done = self._generate(self._dataloader_iter, n_prompts,
+                                                      a.algo.dynamic_filtering_enable, **gen)
             if a.vllm.enable_sleep:
                 self._call_all("sleep")
             if a.algo.dynamic_filtering_enable and consumed:

@@ -76,17 +76,34 @@ class RequestOutput:
 class _Row:
     request_id: int
     sample_index: int
-    prompt_len: int
-    max_tokens: int
+    prompt_len: int              # tokens in front of the first token this row still has to generate (prompt, plus the
+                                 # tokens generated before a preemption)
+    max_tokens: int              # total tokens the sample may generate
     pages: list
-    gen: int = 0  # tokens generated so far as far as the host knows (upper bound for finished rows)
+    gen: int = 0                 # tokens generated so far as far as the host knows (upper bound for finished rows)
+    base: int = 0                # tokens generated before this row was (re)admitted: restored after a preemption
+    order: int = 0               # admission order (the newest rows are preempted first)
+    prefilled: int = -1          # chunked prefill: context tokens whose KV is in the cache; -1 once decoding
+
+
+@dataclass
+class _Pending:
+    """A queued request, or one preempted sample waiting to be recomputed (`done_*` hold what it had generated)."""
+    request_id: object
+    prompt: list
+    sp: "SamplingParams"
+    mm: dict | None = None
+    sample_index: int | None = None       # set for a preempted sample (one row); None: a fresh request with sp.n rows
+    done_tokens: list = field(default_factory=list)
+    done_logprobs: list = field(default_factory=list)
 
 
 class RolloutEngine:
     def __init__(self, model: TransformerLM, max_num_seqs: int = 256, max_model_len: int = 4096,
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
                  eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None,
-                 quantization: str | None = None):
+                 quantization: str | None = None, enable_prefix_caching: bool = False,
+                 max_prefill_tokens: int = 16384):
         assert model.cfg.head_dim == 128 or not model.flat.is_cuda, \
             "the decode attention kernel is specialised for head_dim 128"
         assert quantization in (None, "fp8"), "rollout quantisation: None or 'fp8' (per-tensor e4m3)"
@@ -130,7 +147,6 @@ class RolloutEngine:
         self.mrope = cfg.is_vlm
         self.rope_delta = torch.zeros(B, dtype=torch.int32, device=dev)
         self.rope_pos = torch.zeros(B, dtype=torch.int32, device=dev)
-        self._mm: dict = {}                     # request id -> {"pixel_values", "image_grid_thw"}
         self.seq_lens = torch.ones(B, dtype=torch.int32, device=dev)
         self.slots = torch.zeros(B, dtype=torch.int32, device=dev)
         self.block_table = torch.full((B, self.max_pages), self.dummy_page, dtype=torch.int32, device=dev)
@@ -158,6 +174,9 @@ class RolloutEngine:
         from collections import deque
 
         self.waiting = deque()
+        self._prefilling: list = []             # admitted requests whose context is not fully prefilled yet
+        self._table_dirty = False
+        self._stale_rows: list = []
         self._req: dict = {}
         self._batch_counter = 0
         self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
@@ -165,6 +184,16 @@ class RolloutEngine:
         self.sleeping = False
         self.paused = False
         self.decode_steps = 0
+        # scheduler state: admission order, chunked-prefill budget, prefix cache, preemption counters
+        self.max_prefill_tokens = max(int(max_prefill_tokens), PAGE)
+        self._order = 0
+        self.enable_prefix_caching = bool(enable_prefix_caching)
+        from collections import OrderedDict
+
+        self._cache: "OrderedDict[int, int]" = OrderedDict()   # chain hash of a full page of tokens -> page (LRU order)
+        self._cache_hash: dict[int, int] = {}                  # page -> its hash
+        self._cache_users: dict[int, int] = {}                 # page -> live rows reading it
+        self.stats = {"preemptions": 0, "prefix_hit_tokens": 0, "prefill_tokens": 0, "prefill_chunks": 0}
         if self.on_gpu:
             _lib.status_word(self.device)
         self.model.rope(self.device)
@@ -218,6 +247,13 @@ class RolloutEngine:
         self.sleeping = False
 
     def reset_prefix_cache(self):
+        """Forget every cached prefix (their KV was computed with weights that have been replaced). Pages that live
+        rows still read stay allocated until those rows finish."""
+        for page in list(self._cache_hash):
+            self.blocks.free(page)                 # the cache's own reference
+        self._cache.clear()
+        self._cache_hash.clear()
+        self._cache_users.clear()
         return True
 
     def pause_generation(self):
@@ -227,13 +263,18 @@ class RolloutEngine:
         self.paused = False
 
     def get_num_unfinished_requests(self) -> int:
-        return sum(r is not None for r in self.rows)
+        return sum(r is not None for r in self.rows) + len(self.waiting)
 
     @torch.no_grad()
     def update_weights(self, flat_src: torch.Tensor):
         """Copy a new set of weights (same flat layout) into the engine's buffer; a no-op when they alias."""
+        if self._cache_hash:
+            self.reset_prefix_cache()
         if self.tp is not None:
-            self.tp.load_shard(flat_src, self.model.flat)      # one planned copy kernel: full layout -> this TP shard
+            if flat_src is None:
+                self.tp.refresh(self.model.flat)               # from the configured source (ZeRO-3 slices, ...)
+            else:
+                self.tp.load_shard(flat_src, self.model.flat)  # one planned copy kernel: full layout -> this TP shard
             return
         if flat_src.data_ptr() != self.model.flat.data_ptr():
             n = min(flat_src.numel(), self.model.flat.numel())      # buffers may differ in their shard padding
@@ -255,65 +296,82 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ model execution
     @torch.no_grad()
-    def _prefill(self, prompts: list[list[int]], row_groups: list[list[int]], mms: list | None = None):
-        """Run the prompts through the model once each, fill their KV pages, and return last-position logits [P, V].
-        mms: per prompt None or {"pixel_values", "image_grid_thw"}; sets the rows' rotary offsets."""
+    def _prefill(self, items: list, mms: list | None = None):
+        """Run one prefill pass. items: list of (tokens, start, row) where `tokens` is the whole context of the row so
+        far (prompt, plus generated tokens of a preempted sample), `start` the number of leading tokens whose KV already
+        sits in the row's pages (prefix-cache hit or earlier chunks) and the rest, tokens[start:], is computed now and
+        written to the pages of `row`. Returns the logits [len(items), V] at the last position of every item.
+        mms: per item None or {"pixel_values", "image_grid_thw"} (only with start == 0); sets the rotary offsets."""
         cfg, m = self.cfg, self.model
         dev = self.device
-        lens = [len(p) for p in prompts]
-        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=dev)
-        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
-        cu = torch.zeros(len(prompts) + 1, dtype=torch.int32)
-        cu[1:] = torch.cumsum(torch.tensor(lens, dtype=torch.int32), 0)
-        cu = cu.to(dev)
-        # slot of every prompt token in the first row of its group (full pages are shared with the other rows)
-        slot_list = []
-        for p, rows in zip(prompts, row_groups):
-            pages = self.rows[rows[0]].pages
-            for t in range(len(p)):
-                slot_list.append(pages[t // PAGE] * PAGE + t % PAGE)
-        slots = torch.tensor(slot_list, dtype=torch.int64, device=dev)
-        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        n_items = len(items)
+        new_lens = [len(t) - s0 for t, s0, _ in items]
+        starts = [s0 for _, s0, _ in items]
+        ids = torch.tensor([x for t, s0, _ in items for x in t[s0:]], dtype=torch.int64, device=dev)
+        pos = torch.cat([torch.arange(s0, s0 + n, dtype=torch.int32) for s0, n in zip(starts, new_lens)]).to(dev)
+        cu_new = [0]
+        for n in new_lens:
+            cu_new.append(cu_new[-1] + n)
+        cu = torch.tensor(cu_new, dtype=torch.int32, device=dev)
+
+        def slots_of(row, a, b):
+            pages = self.rows[row].pages
+            return [pages[t // PAGE] * PAGE + t % PAGE for t in range(a, b)]
+
+        slots = torch.tensor([x for (t, s0, row) in items for x in slots_of(row, s0, len(t))], dtype=torch.int64,
+                             device=dev)
+        with_prefix = any(starts)
+        if with_prefix:
+            # rows of the full (prefix + new) stream: where each sequence's cached keys live, and where the new ones go
+            cu_all = [0]
+            for t, _, _ in items:
+                cu_all.append(cu_all[-1] + len(t))
+            pre_slots = torch.tensor([x for (t, s0, row) in items for x in slots_of(row, 0, s0)], dtype=torch.int64,
+                                     device=dev)
+            pre_rows = torch.cat([torch.arange(cu_all[i], cu_all[i] + starts[i]) for i in range(n_items)]).to(dev)
+            new_rows = torch.cat([torch.arange(cu_all[i] + starts[i], cu_all[i + 1]) for i in range(n_items)]).to(dev)
+            scale = 1.0 / math.sqrt(cfg.head_dim)
 
         def attn_fn(i, q, k, v):
             self.kv[i, 0].index_copy_(0, slots, k)
             self.kv[i, 1].index_copy_(0, slots, v)
-            return F.attention_varlen(q, k, v, cu, max(lens))
+            if not with_prefix:
+                return F.attention_varlen(q, k, v, cu, max(new_lens))
+            from ..ops.attention import attention_with_prefix
+
+            k_all = torch.empty(cu_all[-1], k.shape[1], k.shape[2], dtype=k.dtype, device=dev)
+            v_all = torch.empty_like(k_all)
+            k_all.index_copy_(0, pre_rows, self.kv[i, 0].index_select(0, pre_slots))
+            v_all.index_copy_(0, pre_rows, self.kv[i, 1].index_select(0, pre_slots))
+            k_all.index_copy_(0, new_rows, k)
+            v_all.index_copy_(0, new_rows, v)
+            return attention_with_prefix(q, k_all, v_all, cu_all, starts, scale)
 
         was_training = m.training
         m.eval()
         embeds = None
         if self.mrope:
-            deltas = [0] * len(prompts)
+            deltas = [0] * n_items
             if mms and any(mms):
                 from ..models.vision import mrope_positions
 
+                assert not with_prefix, "image prompts are prefilled in one piece"
                 pv = torch.cat([mm["pixel_values"] for mm in mms if mm]).to(dev)
                 thw = torch.cat([torch.as_tensor(mm["image_grid_thw"]).view(-1, 3) for mm in mms if mm])
-                cu_list = [0]
-                for n in lens:
-                    cu_list.append(cu_list[-1] + n)
-                embeds, pos = m.multimodal_inputs(ids, cu_list, pv, thw)
+                embeds, pos = m.multimodal_inputs(ids, cu_new, pv, thw)
                 merge = cfg.vision_config().spatial_merge_size
-                for k, (p, mm) in enumerate(zip(prompts, mms)):
+                for k_, ((t, _, _), mm) in enumerate(zip(items, mms)):
                     if mm:
                         grids = [tuple(g) for g in torch.as_tensor(mm["image_grid_thw"]).view(-1, 3).tolist()]
-                        deltas[k] = mrope_positions(p, grids, cfg.image_token_id, merge, cfg.video_token_id)[1]
-            for d, rows in zip(deltas, row_groups):
-                self.rope_delta[rows] = d
-        h, _ = m(ids, pos, cu, max(lens), attn_fn=attn_fn, inputs_embeds=embeds)
+                        deltas[k_] = mrope_positions(t, grids, cfg.image_token_id, merge, cfg.video_token_id)[1]
+            for d, (_, _, row) in zip(deltas, items):
+                self.rope_delta[row] = d
+        h, _ = m(ids, pos, cu, max(new_lens), attn_fn=attn_fn, inputs_embeds=embeds)
         m.train(was_training)
         last = (cu[1:] - 1).long()
-        logits = F.linear(h[last].contiguous(), m.lm_head_weight())
-        # partial last page: every other row of the group gets its own copy
-        for p, rows in zip(prompts, row_groups):
-            n_full = len(p) // PAGE
-            if len(p) % PAGE and len(rows) > 1:
-                src = self.rows[rows[0]].pages[n_full]
-                for r in rows[1:]:
-                    dst = self.rows[r].pages[n_full]
-                    self.kv[:, :, dst * PAGE:(dst + 1) * PAGE].copy_(self.kv[:, :, src * PAGE:(src + 1) * PAGE])
-        return logits
+        self.stats["prefill_tokens"] += int(cu_new[-1])
+        self.stats["prefill_chunks"] += 1
+        return F.linear(h[last].contiguous(), m.lm_head_weight())
 
     def _decode_step(self, B: int):
         """One token for rows [0, B). Pure device work on static buffers: safe to capture in a CUDA graph."""
@@ -322,7 +380,6 @@ class RolloutEngine:
                  and self.on_gpu)
         if self.quantization == "fp8" and not self.fp8:
             self._refresh_fp8()
-        assert fused or self.tp is None, "tensor-parallel rollout covers the dense fused decode path"
         if self.mrope:
             torch.add(self.pos[:B], self.rope_delta[:B], out=self.rope_pos[:B])
         if fused:
@@ -418,7 +475,11 @@ class RolloutEngine:
             rope_kvwrite(qkv, pos, slots, table, q_buf, self.kv[i, 0], self.kv[i, 1], Hq, Hkv)
             paged_decode(q_buf, self.kv[i, 0], self.kv[i, 1], bt, sl, scale, out=attn_buf)
             ao = attn_buf.view(B, Hq * cfg.head_dim)
-            if self.quantization == "fp8":
+            if self.tp is not None:
+                # row-parallel shard outside the fused path (qk-norm / MoE models, CPU ranks): partial product, sum
+                # over the tensor-parallel group, residual once
+                h = h + self.tp.all_reduce(decode_gemm(ao, m.p(pre + "o.weight")))
+            elif self.quantization == "fp8":
                 h = self.fp8[(i, "o")](ao, residual=h)
             else:
                 h = m._lin(i, "o", ao, None, h) if m.lora is not None else decode_gemm(ao, m.p(pre + "o.weight"), None, h)
@@ -433,6 +494,9 @@ class RolloutEngine:
                 h = self.fp8[(i, "down")](F.swiglu(self.fp8[(i, "gate_up")](x)), residual=h)
             elif m.lora is not None:
                 h = m._lin(i, "down", F.swiglu(m._lin(i, "gate_up", x)), None, h)
+            elif self.tp is not None:
+                a = F.swiglu(decode_gemm(x, m.p(pre + "gate_up.weight")))
+                h = h + self.tp.all_reduce(decode_gemm(a, m.p(pre + "down.weight")))
             else:
                 gu = decode_gemm(x, m.p(pre + "gate_up.weight"))
                 a = F.swiglu(gu)
@@ -511,30 +575,118 @@ class RolloutEngine:
         for t, s in zip(self._state_tensors(), saved):
             t.copy_(s)
 
-    # ------------------------------------------------------------------ scheduling
+    # ------------------------------------------------------------------ scheduling: pages
     def _bucket(self, n: int) -> int:
         b = 1
         while b < n:
             b *= 2
         return min(b, self.max_num_seqs)
 
+    def _evictable(self) -> int:
+        return sum(1 for p, u in self._cache_users.items() if u == 0)
+
+    def _free_pages(self) -> int:
+        """Pages obtainable right now: free ones plus cached prefixes no live row is reading."""
+        return self.blocks.num_free() + self._evictable()
+
+    def _alloc_page(self) -> int:
+        if self.blocks.num_free() == 0:
+            for h, page in self._cache.items():          # least recently used first
+                if self._cache_users.get(page, 0) == 0:
+                    del self._cache[h]
+                    del self._cache_hash[page]
+                    del self._cache_users[page]
+                    self.blocks.free(page)
+                    break
+        return self.blocks.alloc()
+
+    def _sync_block_table(self):
+        """Host block table -> device. Rows that are still being prefilled show the dummy page on the device: the
+        decode kernels run over all rows of a bucket, and an inactive row writes its (meaningless) K/V at whatever
+        slot its table row and stale position give - that must never be a page of a live context."""
+        self._table_dirty = False
+        if self._stale_rows:
+            # a released row keeps running in the decode kernels as an inactive row: park its write slot on the dummy
+            # page, or its next (meaningless) K/V write would land in a page that now belongs to another context
+            idx = torch.tensor(self._stale_rows, dtype=torch.int64, device=self.device)
+            self.slots[idx] = self.dummy_page * PAGE
+            self.pos[idx] = 0
+            self.seq_lens[idx] = 1
+            self._stale_rows = []
+        hold = [r for _, rows, _ in self._prefilling for r in rows]
+        if hold:
+            tmp = self.block_table_host.clone()
+            tmp[hold] = self.dummy_page
+            self.block_table.copy_(tmp)
+        else:
+            self.block_table.copy_(self.block_table_host, non_blocking=True)
+
+    def _pages_short(self, row: int, upto_pos: int) -> int:
+        need = min(upto_pos, self.max_model_len - 1) // PAGE + 1
+        return max(0, need - len(self.rows[row].pages))
+
     def _ensure_pages(self, row: int, upto_pos: int):
         r = self.rows[row]
         need = min(upto_pos, self.max_model_len - 1) // PAGE + 1
         changed = False
         while len(r.pages) < need:
-            pg = self.blocks.alloc()
+            pg = self._alloc_page()
             r.pages.append(pg)
             self.block_table_host[row, len(r.pages) - 1] = pg
             changed = True
         return changed
 
-    def _release_row(self, row: int):
-        r = self.rows[row]
-        for pg in r.pages:
+    def _release_pages(self, pages: list):
+        for pg in pages:
+            if pg in self._cache_users:
+                self._cache_users[pg] -= 1
             self.blocks.free(pg)
+
+    def _release_row(self, row: int):
+        self._release_pages(self.rows[row].pages)
         self.rows[row] = None
         self.block_table_host[row].fill_(self.dummy_page)
+        self._table_dirty = True
+        self._stale_rows.append(row)
+
+    # ------------------------------------------------------------------ scheduling: prefix cache
+    @staticmethod
+    def _page_hashes(tokens: list, n_pages: int) -> list:
+        """Chain hashes of the first n_pages full pages of a token list (a page's hash covers everything before it)."""
+        out, h = [], 0
+        for i in range(n_pages):
+            h = hash((h, tuple(tokens[i * PAGE:(i + 1) * PAGE])))
+            out.append(h)
+        return out
+
+    def _cache_lookup(self, tokens: list) -> list:
+        """Pages holding the KV of the longest cached prefix of `tokens` (whole pages; at least one token is left to
+        compute so that the prefill yields logits)."""
+        if not self.enable_prefix_caching:
+            return []
+        hits = []
+        for h in self._page_hashes(tokens, (len(tokens) - 1) // PAGE):
+            page = self._cache.get(h)
+            if page is None:
+                break
+            hits.append(page)
+        return hits
+
+    def _cache_insert(self, tokens: list, pages: list, n_full: int):
+        """Offer the first n_full pages of a row (whose KV is complete) to the cache; it keeps its own reference."""
+        if not self.enable_prefix_caching:
+            return
+        for idx, (h, page) in enumerate(zip(self._page_hashes(tokens, n_full), pages[:n_full])):
+            if h in self._cache or page in self._cache_hash:
+                if h in self._cache:
+                    self._cache.move_to_end(h)
+                continue
+            self.blocks.share(page)
+            self._cache[h] = page
+            self._cache_hash[page] = h
+            # live rows that read this page (the samples of one request hold their shared pages at the same index)
+            self._cache_users[page] = sum(1 for r in self.rows
+                                          if r is not None and len(r.pages) > idx and r.pages[idx] == page)
 
     # ------------------------------------------------------------------ request API (continuous batching)
     def add_request(self, request_id, prompt_token_ids: list[int], sampling_params: SamplingParams,
@@ -543,10 +695,15 @@ class RolloutEngine:
         multi_modal_data: {"pixel_values": [N, patch_dim], "image_grid_thw": [n, 3]} for prompts that contain image
         placeholder tokens (vision-language models), or {"image": [PIL images]} when an image processor is attached
         (``self.image_processor``)."""
+        mm = None
         if multi_modal_data:
             assert self.mrope, "this model takes no image inputs"
-            self._mm[request_id] = self._mm_tensors(multi_modal_data)
-        self.waiting.append((request_id, list(prompt_token_ids), sampling_params))
+            mm = self._mm_tensors(multi_modal_data)
+        prompt = list(prompt_token_ids)
+        if len(prompt) >= self.max_model_len:
+            assert mm is None, "a prompt with images exceeds max_model_len (truncation would cut an image)"
+            prompt = prompt[-(self.max_model_len - 1):]
+        self.waiting.append(_Pending(request_id, prompt, sampling_params, mm))
 
     image_processor = None
 
@@ -566,61 +723,139 @@ class RolloutEngine:
         m = sp.max_tokens if sp.max_tokens is not None else max(1, self.max_model_len - len(prompt))
         return max(1, min(m, self.max_model_len - len(prompt)))
 
+    # ------------------------------------------------------------------ admission, chunked prefill, preemption
+    def _admit(self):
+        """Move queued requests into rows while rows and pages last. Pages are taken for the context only (not for
+        the tokens still to be generated: decode bursts allocate as they go and preempt when the pool runs dry); one
+        page of headroom per live row keeps a freshly admitted request from being preempted straight away."""
+        free_rows = [i for i, r in enumerate(self.rows) if r is None]
+        admitted = False
+        while self.waiting:
+            e: _Pending = self.waiting[0]
+            n = 1 if e.sample_index is not None else e.sp.n
+            tokens = e.prompt + e.done_tokens
+            hits = self._cache_lookup(tokens) if e.mm is None else []
+            n_full = len(tokens) // PAGE
+            own_full = max(0, n_full - len(hits))
+            live = sum(r is not None for r in self.rows)
+            need = own_full + n                       # shared full pages still to compute + one open page per row
+            # hit pages that nobody reads count as obtainable in _free_pages(); pinning them takes them out of it
+            pinned = sum(1 for pg in hits if self._cache_users.get(pg, 0) == 0)
+            if len(free_rows) < n or self._free_pages() - pinned < need + live + 1:
+                if live == 0 and not admitted:
+                    self.waiting.popleft()
+                    raise RuntimeError("a request does not fit into the KV cache / row budget of the rollout engine")
+                break
+            self.waiting.popleft()
+            for pg in hits:                            # pin before any allocation can evict them
+                self._cache_users[pg] += n
+                self._cache.move_to_end(self._cache_hash[pg])
+            rows = [free_rows.pop(0) for _ in range(n)]
+            shared = [self.blocks.share(pg) for pg in hits] + [self._alloc_page() for _ in range(own_full)]
+            max_new = self._max_new(e.prompt, e.sp)
+            for j, r in enumerate(rows):
+                if j > 0:
+                    for pg in shared:
+                        self.blocks.share(pg)
+                self._order += 1
+                self.rows[r] = _Row(e.request_id, e.sample_index if e.sample_index is not None else j, len(tokens),
+                                    max_new, list(shared), gen=len(e.done_tokens), base=len(e.done_tokens),
+                                    order=self._order, prefilled=len(hits) * PAGE)
+                self.block_table_host[r].fill_(self.dummy_page)
+                for t, pg in enumerate(shared):
+                    self.block_table_host[r, t] = pg
+                self._ensure_pages(r, len(tokens))
+            if e.sample_index is None:
+                self._req[e.request_id] = (e.prompt, e.sp, {})
+            self.stats["prefix_hit_tokens"] += len(hits) * PAGE
+            self._prefilling.append((e, rows, tokens))
+            admitted = True
+
+    def _prefill_work(self):
+        """Spend up to max_prefill_tokens on the admitted-but-not-yet-decoding requests, oldest first. A context longer
+        than the budget is prefilled in chunks over several calls (decode bursts of the live rows run in between);
+        once its last chunk is done the rows of the request are started with their first sampled token."""
+        budget = self.max_prefill_tokens
+        batch, finishing = [], []
+        for entry in self._prefilling:
+            e, rows, tokens = entry
+            lead = self.rows[rows[0]]
+            left = len(tokens) - lead.prefilled
+            if budget <= 0 or (e.mm is not None and left > budget and batch):
+                break
+            take = left if e.mm is not None else min(left, budget)     # image prompts are not cut
+            upto = lead.prefilled + take
+            batch.append((tokens[:upto], lead.prefilled, rows[0]))
+            budget -= take
+            if upto == len(tokens):
+                finishing.append((len(batch) - 1, entry))
+            else:
+                lead.prefilled = upto
+                break                                   # an unfinished context uses up the pass
+        if not batch:
+            return
+        logits = self._prefill(batch, [en[0].mm if (en[0].mm is not None and b[1] == 0) else None
+                                       for en, b in zip(self._prefilling, batch)])
+        if finishing:
+            done = {id(en) for _, en in finishing}
+            self._prefilling = [en for en in self._prefilling if id(en) not in done]
+            self._sync_block_table()                   # the finished rows' pages become visible to the decode kernels
+            self._start_rows(logits[[k for k, _ in finishing]], [en for _, en in finishing])
+        else:
+            self._sync_block_table()
+
+    def _preempt(self, row: int):
+        """Take a decoding row out: keep what it generated, give its pages back, queue it for recomputation."""
+        r = self.rows[row]
+        prompt, sp, _ = self._req[r.request_id]
+        n = int(self.gen_count[row].item())
+        toks = self.out_tokens[row, :n].tolist()
+        lps = self.out_logprobs[row, :n].tolist()
+        self.active[row] = 0
+        self._release_row(row)
+        self.waiting.appendleft(_Pending(r.request_id, prompt, sp, None, r.sample_index, toks, lps))
+        self.stats["preemptions"] += 1
+
     @torch.no_grad()
     def step(self) -> list[RequestOutput]:
-        """Admit waiting requests (prefill), run a burst of decode steps for all live rows, retire finished rows.
-        Returns the requests whose samples have all finished."""
+        """Admit waiting requests, run prefill work (chunked), run a burst of decode steps for all decoding rows
+        (preempting the newest rows when the page pool cannot cover the burst), retire finished rows. Returns the
+        requests whose samples have all finished."""
         if self.sleeping:
             self.wake_up()
         finished: list[RequestOutput] = []
         if self.paused:
             return finished
-        # ---- admission
-        admitted, groups = [], []
-        free_rows = [i for i, r in enumerate(self.rows) if r is None]
-        while self.waiting:
-            rid, prompt, sp = self.waiting[0]
-            if len(prompt) >= self.max_model_len:
-                assert rid not in self._mm, "a prompt with images exceeds max_model_len (truncation would cut an image)"
-                prompt = prompt[-(self.max_model_len - 1):]
-            max_new = self._max_new(prompt, sp)
-            pages_needed = sp.n * ((len(prompt) + max_new) // PAGE + 1)
-            if len(free_rows) < sp.n or self.blocks.num_free() < pages_needed + 1:
-                if not any(r is not None for r in self.rows) and not admitted:
-                    self.waiting.popleft()
-                    raise RuntimeError("a request does not fit into the KV cache / row budget of the rollout engine")
-                break
-            self.waiting.popleft()
-            rows = [free_rows.pop(0) for _ in range(sp.n)]
-            shared = [self.blocks.alloc() for _ in range(len(prompt) // PAGE)]
-            for j, r in enumerate(rows):
-                if j > 0:
-                    for pg in shared:
-                        self.blocks.share(pg)
-                self.rows[r] = _Row(rid, j, len(prompt), max_new, list(shared))
-                self.block_table_host[r].fill_(self.dummy_page)
-                for t, pg in enumerate(shared):
-                    self.block_table_host[r, t] = pg
-                self._ensure_pages(r, len(prompt))
-            self._req[rid] = (prompt, sp, {})
-            admitted.append((prompt, sp))
-            groups.append(rows)
-        if admitted:
-            self._start_rows([a[0] for a in admitted], groups, [a[1] for a in admitted],
-                             [self._mm.pop(r, None) for r in (self.rows[g[0]].request_id for g in groups)])
-        live = [i for i, r in enumerate(self.rows) if r is not None]
+        self._admit()
+        self._prefill_work()
+        live = [i for i, r in enumerate(self.rows) if r is not None and r.prefilled < 0]
         if not live:
+            if self.on_gpu:
+                _lib.check_status(self.device)
             return finished
         # ---- decode burst
-        B = self._bucket(max(live) + 1)
         left = [self.rows[i].max_tokens - self.rows[i].gen for i in live if self.rows[i].max_tokens > self.rows[i].gen]
         steps = max(1, min([self.check_interval] + left)) if left else 0
+        if steps:
+            def short(k):
+                return sum(self._pages_short(i, self.rows[i].prompt_len + (self.rows[i].gen - self.rows[i].base) + k)
+                           for i in live)
+
+            while steps > 1 and short(steps) > self._free_pages():
+                steps = max(1, steps // 2)
+            while len(live) > 1 and short(steps) > self._free_pages():
+                victim = max(live, key=lambda i: self.rows[i].order)
+                self._preempt(victim)
+                live.remove(victim)
+            if short(steps) > self._free_pages():
+                raise RuntimeError("the KV cache cannot hold a single sequence of this length; raise num_pages")
+        B = self._bucket(max(live) + 1)
         changed = False
         for i in live:
             r = self.rows[i]
-            changed |= self._ensure_pages(i, r.prompt_len + r.gen + steps)
-        if changed:
-            self.block_table.copy_(self.block_table_host, non_blocking=True)
+            changed |= self._ensure_pages(i, r.prompt_len + (r.gen - r.base) + steps)
+        if changed or self._table_dirty:
+            self._sync_block_table()
         for _ in range(steps):
             self._run_decode(B)
         self.decode_steps += steps
@@ -645,6 +880,11 @@ class RolloutEngine:
                 lp_out = [{t: Logprob(l)} for t, l in zip(tl, lpl)] if sp.logprobs is not None else None
                 parts[r.sample_index] = CompletionOutput(r.sample_index, tl, lp_out, reason,
                                                          cumulative_logprob=float(sum(lpl)), logprob_values=lpl)
+                if self.enable_prefix_caching and not self.mrope:
+                    # the KV of every token but the last sampled one is in the row's pages: a follow-up request
+                    # that re-sends this conversation (multi-turn agents) finds its whole pages in the cache
+                    ctx = list(prompt) + tl
+                    self._cache_insert(ctx, r.pages, (len(ctx) - 1) // PAGE)
                 self._release_row(i)
                 if len(parts) == sp.n:
                     finished.append(RequestOutput(r.request_id, list(prompt), [parts[j] for j in range(sp.n)]))
@@ -679,30 +919,53 @@ class RolloutEngine:
             outs.append(ro)
         return outs
 
-    def _start_rows(self, prompts, groups, sps, mms=None):
-        """Prefill admitted prompts and initialise the device state of their rows with the first sampled token."""
+    def _start_rows(self, logits: torch.Tensor, entries: list):
+        """Contexts whose prefill is complete: copy the open page to the other samples of each request, draw the first
+        token of every row from the last-position logits and initialise the rows' device state."""
         dev = self.device
-        self.block_table.copy_(self.block_table_host, non_blocking=True)
-        logits = self._prefill(prompts, groups, mms)                 # [P, V]
+        groups = [rows for _, rows, _ in entries]
+        sps = [e.sp for e, _, _ in entries]
+        lens = [len(tokens) for _, _, tokens in entries]
+        for (e, rows, tokens) in entries:
+            n_full = len(tokens) // PAGE
+            if self.enable_prefix_caching and e.mm is None:
+                self._cache_insert(tokens, self.rows[rows[0]].pages, n_full)
+            if len(tokens) % PAGE and len(rows) > 1:
+                src = self.rows[rows[0]].pages[n_full]
+                for r in rows[1:]:
+                    dst = self.rows[r].pages[n_full]
+                    self.kv[:, :, dst * PAGE:(dst + 1) * PAGE].copy_(self.kv[:, :, src * PAGE:(src + 1) * PAGE])
+            if self.mrope and len(rows) > 1:
+                self.rope_delta[rows[1:]] = self.rope_delta[rows[0]]
         rep = torch.tensor([len(g) for g in groups], device=dev)
         rows = torch.tensor([r for g in groups for r in g], dtype=torch.int64, device=dev)
         lg = logits.repeat_interleave(rep, dim=0)                    # one row per sample
-        temps = torch.tensor([sp.temperature for sp, g in zip(sps, groups) for _ in g], dtype=torch.float32, device=dev)
-        topk = torch.tensor([int(sp.top_k) for sp, g in zip(sps, groups) for _ in g], dtype=torch.int32, device=dev)
-        topp = torch.tensor([float(sp.top_p) for sp, g in zip(sps, groups) for _ in g], dtype=torch.float32, device=dev)
+        per_row = lambda f, dt: torch.tensor([f(sp, e) for (e, g, _), sp in zip(entries, sps) for _ in g], dtype=dt,
+                                             device=dev)
+        temps = per_row(lambda sp, e: sp.temperature, torch.float32)
+        topk = per_row(lambda sp, e: int(sp.top_k), torch.int32)
+        topp = per_row(lambda sp, e: float(sp.top_p), torch.float32)
         tok, lp = sample(lg, temperature=temps, top_k=topk, top_p=topp, seed=self.seed ^ 0x5DEECE66D,
                          step=int(self.decode_steps) * 4096 + int(groups[0][0]))
-        plen = torch.tensor([len(p) for p, g in zip(prompts, groups) for _ in g], dtype=torch.int32, device=dev)
+        plen = torch.tensor([n for n, g in zip(lens, groups) for _ in g], dtype=torch.int32, device=dev)
+        base = per_row(lambda sp, e: len(e.done_tokens), torch.int32)
         maxt = torch.tensor([self.rows[r].max_tokens for g in groups for r in g], dtype=torch.int32, device=dev)
-        mint = torch.tensor([sp.min_tokens for sp, g in zip(sps, groups) for _ in g], dtype=torch.int32, device=dev)
-        ign = torch.tensor([sp.ignore_eos for sp, g in zip(sps, groups) for _ in g], dtype=torch.bool, device=dev)
-        self.out_tokens[rows, 0] = tok
-        self.out_logprobs[rows, 0] = lp
-        done = ((tok == self.eos) & ~ign & (mint <= 1)) | (maxt <= 1)
+        mint = per_row(lambda sp, e: sp.min_tokens, torch.int32)
+        ign = per_row(lambda sp, e: sp.ignore_eos, torch.bool)
+        for (e, g, _) in entries:                                    # what a preempted sample had generated before
+            if e.done_tokens:
+                k = len(e.done_tokens)
+                self.out_tokens[g[0], :k] = torch.tensor(e.done_tokens, dtype=torch.int64, device=dev)
+                self.out_logprobs[g[0], :k] = torch.tensor(e.done_logprobs, dtype=torch.float32, device=dev)
+        bl = base.long()
+        self.out_tokens[rows, bl] = tok
+        self.out_logprobs[rows, bl] = lp
+        gc = base + 1
+        done = ((tok == self.eos) & ~ign & (mint <= gc)) | (maxt <= gc)
         self.tok[rows] = tok
         self.pos[rows] = plen
         self.seq_lens[rows] = plen + 1
-        self.gen_count[rows] = 1
+        self.gen_count[rows] = gc
         self.max_tok[rows] = maxt
         self.min_tok[rows] = mint
         self.ignore_eos[rows] = ign
@@ -714,7 +977,8 @@ class RolloutEngine:
         self.slots[rows] = (page * PAGE + (plen % PAGE)).int()
         for g in groups:
             for r in g:
-                self.rows[r].gen = 1
+                self.rows[r].gen = self.rows[r].base + 1
+                self.rows[r].prefilled = -1
 
 
 # ---------------------------------------------------------------------------------------------- decode GEMM

@@ -44,6 +44,13 @@ from ..utils.utils import get_tokenizer
 ALL_ROLES = ("actor", "critic", "ref", "reward", "rollout")
 
 
+def _bcast_opts(root: int):
+    o = dist.BroadcastOptions()
+    o.rootRank = root
+    o.rootTensor = 0
+    return o
+
+
 def _cpu(x):
     return x.detach().to("cpu") if isinstance(x, torch.Tensor) else x
 
@@ -59,40 +66,63 @@ def _mm_kwargs(mm_train_inputs, device) -> dict:
 
 
 class RLWorker:
-    def __init__(self, args: SimpleNamespace, roles=ALL_ROLES, max_steps: int = 1000, backend: str | None = None):
+    """One process per GPU hosting the roles placed there. Every parallelism / memory flag takes effect here or raises:
+
+    * ``--ds.zero_stage 3``: actor and critic train under ``Zero3Engine`` (parameters, gradients and optimizer state
+      sharded, layer gathers and per-layer gradient reductions as peer-memory kernels); the frozen reference and reward
+      models hold parameter slices only and gather layer by layer as well. Stages 1 / 2 run the ``ZeroEngine`` whose
+      multi-rank optimizer step is the fused reduce + AdamW + parameter-store kernel pair over symmetric memory.
+    * ``--ds.ring_attn_size``: every forward / training pass receives the context-parallel group.
+    * ``--ds.tensor_parallel_size``: tensor-parallel training shards (parallel/tp_train.py).
+    * ``--vllm.tensor_parallel_size``: consecutive ranks form one tensor-parallel rollout engine that the controller
+      drives through its leader (rollout/tp_engine.py::TPLockstepEngine).
+    * ``--ds.adam_offload``: optimizer state lives in pinned host memory between steps (stages 1 / 2).
+    """
+
+    def __init__(self, args: SimpleNamespace, roles=ALL_ROLES, max_steps: int = 1000, backend: str | None = None,
+                 engine_opts: dict | None = None):
         self.args = args
         self.roles = set(roles)
         self.strategy: Strategy = get_strategy(args)
         self.strategy.setup_distributed(backend=backend)
         self.device = self.strategy.device()
         s = self.strategy
-        dp = s.mesh.dp
         self.actor = self.actor_engine = self.critic = self.critic_engine = None
         self.ref = self.reward = self.rollout = self.async_engine = self.ema_model = None
+        self._sync_fn = None
+        self._sync_pg = None
+        self._rollout_source = None
         a = args
         temp = a.rollout.temperature
-        if "actor" in self.roles:
-            lm = load_pretrained(a.actor.model_name_or_path, device=self.device, shard_world=dp, seed=a.train.seed)
-            self._rollout_full = None
-            if s.ds_tensor_parallel_size > 1 and s.world_size > 1:
-                # --ds.tensor_parallel_size: train this rank's shard (parallel/tp_train.py); the rollout engine keeps
-                # the full model, refreshed from the gathered shards at every weight sync
-                from ..parallel.tp_train import shard_for_training
+        seed = a.train.seed
+        eo = dict(engine_opts or {})
+        if getattr(a.ds, "adam_offload", False) and int(a.ds.zero_stage) == 3 and s.zero_world > 1:
+            raise ValueError("--ds.adam_offload is available with ZeRO stages 1 / 2; stage 3 already shards the "
+                             "optimizer state over the ranks")
+        # tensor-parallel rollout engines: group creation is collective, so every rank of the world takes part even
+        # when it hosts no rollout role
+        self.rollout_tp = int(getattr(a.vllm, "tensor_parallel_size", 1) or 1)
+        self._tp_groups = (None, None, None)
+        if self.rollout_tp > 1:
+            if s.world_size % self.rollout_tp:
+                raise ValueError(f"--vllm.tensor_parallel_size {self.rollout_tp} does not divide the {s.world_size} "
+                                 "workers that host rollout engines")
+            if a.train.async_enable and "actor" in self.roles:
+                raise ValueError("--train.async_enable with colocated tensor-parallel rollout engines is not "
+                                 "supported: followers mirror their leader for whole generation phases")
+            from .roles import rollout_tp_groups
 
-                if "rollout" in self.roles:
-                    self._rollout_full = lm
-                    lm.requires_grad_(False)
-                lm = shard_for_training(lm, s.mesh.group("tp"), shard_world=dp)
+            self._tp_groups = rollout_tp_groups(s.world_size, self.rollout_tp, s.rank)
+        if "actor" in self.roles:
+            from .roles import build_trainable
+
+            lm, self.actor_engine, self._rollout_source = build_trainable(
+                s, a.actor.model_name_or_path, a.actor, device=self.device, max_steps=max_steps, seed=seed,
+                use_symm=eo.get("use_symm"))
             self.actor = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples,
                                freeze_visual_encoder=getattr(a.actor, "freeze_visual_encoder", False))
             if a.actor.gradient_checkpointing_enable:
                 self.actor.gradient_checkpointing_enable()
-            sched = LRScheduler(a.actor.adam.lr, max_steps, a.actor.lr_warmup_ratio, a.actor.min_lr_ratio,
-                                a.actor.lr_scheduler)
-            self.actor_engine = ZeroEngine(lm, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas),
-                                           eps=a.actor.adam.eps, weight_decay=a.actor.adam.weight_decay,
-                                           max_norm=a.actor.max_norm, zero_stage=a.ds.zero_stage, group=s.dp_group(),
-                                           scheduler=sched)
             lo, hi = a.actor.eps_clip_low_high
             self.policy_loss = PolicyLoss(lo, hi, a.actor.dual_clip, policy_loss_type=a.actor.policy_loss_type,
                                           enable_vllm_is_correction=a.algo.advantage.is_correction_enable,
@@ -101,69 +131,69 @@ class RLWorker:
             self.actor_buffer = NaiveReplayBuffer(a.train.micro_batch_size, 0, True, a.ds.packing_samples,
                                                   a.train.dynamic_batch_enable)
             if a.train.enable_ema:
-                from ..models.transformer import TransformerLM
-
-                self.ema_model = TransformerLM(lm.cfg, device="cpu", dtype=torch.float32, seed=None)
-                self.ema_model.flat.copy_(lm.flat[: self.ema_model.flat.numel()].float().cpu())
+                if self._rollout_source[0] != "alias":
+                    raise ValueError("--train.enable_ema needs the full parameter buffer on every rank (ZeRO stage "
+                                     "<= 2 without tensor-parallel training)")
+                # the moving average lives on the device in fp32 and is updated by one fused elementwise pass
+                n = lm.total_numel
+                self.ema_flat = lm.flat[:n].float().clone()
+                self.ema_model = True
             if a.ckpt.load_enable and os.path.exists(os.path.join(a.ckpt.path, "_actor")):
                 _, self._resume_states = s.load_ckpt(SimpleNamespace(engine=self.actor_engine),
                                                      os.path.join(a.ckpt.path, "_actor"))
             else:
                 self._resume_states = {}
         if "critic" in self.roles and a.critic.model_name_or_path:
-            lm = load_pretrained(a.critic.model_name_or_path, device=self.device, with_lm_head=False,
-                                 with_value_head=True, shard_world=dp, seed=a.train.seed + 1,
-                                 value_head_prefix=a.ds.value_head_prefix)
+            from .roles import build_trainable
+
+            lm, self.critic_engine, _ = build_trainable(
+                s, a.critic.model_name_or_path, a.critic, device=self.device, max_steps=max_steps, seed=seed + 1,
+                with_lm_head=False, with_value_head=True, value_head_prefix=a.ds.value_head_prefix,
+                use_symm=eo.get("use_symm"))
             self.critic = CriticModel(lm, normalize_reward=a.reward.normalize_enable,
                                       packing_samples=a.ds.packing_samples)
             if a.actor.gradient_checkpointing_enable:
                 self.critic.gradient_checkpointing_enable()
-            sched = LRScheduler(a.critic.adam.lr, max_steps, a.critic.lr_warmup_ratio, a.critic.min_lr_ratio,
-                                a.critic.lr_scheduler)
-            self.critic_engine = ZeroEngine(lm, lr=a.critic.adam.lr, betas=tuple(a.critic.adam.betas),
-                                            eps=a.critic.adam.eps, weight_decay=a.critic.adam.weight_decay,
-                                            max_norm=a.critic.max_norm, zero_stage=a.ds.zero_stage,
-                                            group=s.dp_group(), scheduler=sched)
             self.value_loss = ValueLoss(a.critic.value_clip)
             self.critic_buffer = NaiveReplayBuffer(a.train.micro_batch_size, 0, True, a.ds.packing_samples,
                                                    a.train.dynamic_batch_enable)
             if a.ckpt.load_enable and os.path.exists(os.path.join(a.ckpt.path, "_critic")):
                 ckpt.load_sharded(self.critic_engine, os.path.join(a.ckpt.path, "_critic"))
         if "ref" in self.roles and a.algo.kl.init_coef > 0:
-            dev = "cpu" if a.ref.offload else self.device
-            lm = load_pretrained(a.ref.model_name_or_path or a.actor.model_name_or_path, device=dev, seed=a.train.seed)
-            lm.requires_grad_(False)
-            if s.ds_tensor_parallel_size > 1 and s.world_size > 1 and dev != "cpu":
-                from ..parallel.tp_train import shard_for_training
+            from .roles import build_frozen
 
-                lm = shard_for_training(lm, s.mesh.group("tp"))
-                lm.requires_grad_(False)
+            lm = build_frozen(s, a.ref.model_name_or_path or a.actor.model_name_or_path, device=self.device, seed=seed,
+                              offload=a.ref.offload)
             self.ref = Actor(lm, temperature=temp, packing_samples=a.ds.packing_samples).eval()
         if "reward" in self.roles and a.reward.model_name_or_path:
-            dev = "cpu" if a.reward.offload else self.device
-            lm = load_pretrained(a.reward.model_name_or_path, device=dev, with_lm_head=False, with_value_head=True,
-                                 seed=a.train.seed + 2, value_head_prefix=a.ds.value_head_prefix)
-            lm.requires_grad_(False)
+            from .roles import build_frozen
+
+            lm = build_frozen(s, a.reward.model_name_or_path, device=self.device, seed=seed + 2, with_lm_head=False,
+                              with_value_head=True, value_head_prefix=a.ds.value_head_prefix, offload=a.reward.offload)
             self.reward = RewardModel(lm, normalize_reward=a.reward.normalize_enable,
                                       packing_samples=a.ds.packing_samples).eval()
         if "rollout" in self.roles:
-            if self.actor is not None and getattr(self, "_rollout_full", None) is not None:
-                rl_model = self._rollout_full        # tensor-parallel training: the engine owns a full copy
-            elif self.actor is not None:
-                rl_model = self.actor.model          # hybrid engine: one weight buffer for trainer and rollout
-            else:
-                rl_model = load_pretrained(a.actor.model_name_or_path, device=self.device, seed=a.train.seed)
-                rl_model.requires_grad_(False)
+            from ..models.config import ModelConfig
+            from .roles import build_rollout
+
             self.tokenizer = get_tokenizer(a.actor.model_name_or_path, None, "left", s,
                                            use_fast=not a.data.disable_fast_tokenizer)
-            self.rollout = RolloutEngine(rl_model, max_num_seqs=getattr(a.vllm, "max_num_seqs", 256),
-                                         max_model_len=a.data.max_len,
-                                         gpu_memory_utilization=a.vllm.gpu_memory_utilization,
-                                         seed=a.train.seed + s.rank, eos_token_id=self.tokenizer.eos_token_id,
-                                         use_cuda_graph=not a.vllm.enforce_eager,
-                                         quantization=getattr(a.vllm, "quantization", None))
+            source = self._rollout_source or ("load", a.actor.model_name_or_path)
+            cfg = self.actor.cfg if self.actor is not None else ModelConfig.from_pretrained(a.actor.model_name_or_path)
+            if self._rollout_source is not None and self._rollout_source[0] == "tp_train":
+                cfg = self._rollout_source[1].tp_train.full_cfg
+            if self.rollout_tp > 1 and source[0] == "load":
+                full = load_pretrained(a.actor.model_name_or_path, device=self.device, seed=seed)
+                full.requires_grad_(False)
+                self._staging = full
+                source = ("alias", full)
+            self.rollout, self.rollout_model, self._sync_fn = build_rollout(
+                s, cfg, source, device=self.device, seed=seed, tokenizer=self.tokenizer, tp_groups=self._tp_groups,
+                max_num_seqs=eo.get("max_num_seqs", getattr(a.vllm, "max_num_seqs", 256)),
+                num_pages=eo.get("num_pages"), use_cuda_graph=eo.get("use_cuda_graph", not a.vllm.enforce_eager))
             # vision-language models: the processor's image part turns the PIL images an agent passes into patches
             self.rollout.image_processor = getattr(self.tokenizer, "image_processor", None)
+            self.is_rollout_leader = self._tp_groups[2] is None or s.rank == self._tp_groups[2][0]
             self.async_engine = AsyncRolloutEngine(self.rollout, self.tokenizer)
             if a.train.agent_func_path:
                 cls = load_python_object(a.train.agent_func_path, "AgentExecutor")
@@ -205,6 +235,16 @@ class RLWorker:
     def get_num_unfinished_requests(self) -> int:
         return self.async_engine.get_num_unfinished_requests()
 
+    def follow_generation(self) -> int:
+        """Follower of a tensor-parallel rollout engine: mirror the leader's steps until it ends the phase."""
+        return self.rollout.follow()
+
+    def end_generation(self) -> bool:
+        """Leader of a tensor-parallel rollout engine: release the followers at the end of a generation phase."""
+        if hasattr(self.rollout, "stop_followers"):
+            self.rollout.stop_followers()
+        return True
+
     def sleep(self, level: int = 1):
         self.rollout.sleep(level)
 
@@ -224,23 +264,26 @@ class RLWorker:
     @torch.no_grad()
     def forward(self, sequences, action_mask, attention_mask, role: str = "actor", mm_train_inputs=None, **_unused):
         seq, am, att = sequences.to(self.device), action_mask.to(self.device), attention_mask.to(self.device)
+        cp = self.strategy.ring_attn_group
         if role == "critic":
             self.critic.eval()
-            out = self.critic(seq, am, att)
+            out = self.critic(seq, am, att, ring_attn_group=cp)
             self.critic.train()
         else:
             model = self.actor if role == "actor" else self.ref
             dev = next(model.parameters()).device
             was = model.training
             model.eval()
-            out = model(seq.to(dev), am.to(dev), att.to(dev), **_mm_kwargs(mm_train_inputs, dev))
+            out = model(seq.to(dev), am.to(dev), att.to(dev), ring_attn_group=cp if dev.type == "cuda" else None,
+                        **_mm_kwargs(mm_train_inputs, dev))
             model.train(was)
         return _cpu(out)
 
     @torch.no_grad()
     def forward_reward(self, sequences, attention_mask, pad_sequence=True, **_unused):
         dev = next(self.reward.parameters()).device
-        return _cpu(self.reward(sequences.to(dev), attention_mask.to(dev)))
+        cp = self.strategy.ring_attn_group if dev.type == "cuda" else None
+        return _cpu(self.reward(sequences.to(dev), attention_mask.to(dev), ring_attn_group=cp))
 
     # ------------------------------------------------------------------ training
     def append(self, experience: Experience, role: str = "actor"):
@@ -315,6 +358,7 @@ class RLWorker:
                 mask = exp.action_mask.float()
                 logp, out = self.actor(exp.sequences, exp.action_mask, exp.attention_mask, return_output=True,
                                        return_entropy=a.actor.entropy_coef is not None,
+                                       ring_attn_group=self.strategy.ring_attn_group,
                                        **_mm_kwargs(getattr(exp, "mm_train_inputs", None), self.device))
                 norm = {k: info[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size")}
                 loss, clip_ratio, ppo_kl, vllm_kl = self.policy_loss(logp, exp.action_log_probs, exp.advantages, mask,
@@ -343,10 +387,9 @@ class RLWorker:
                 if last:
                     eng.step()
                     if self.ema_model is not None:
-                        with torch.no_grad():
-                            n = self.ema_model.flat.numel()
-                            self.ema_model.flat.mul_(a.train.ema_beta).add_(
-                                self.actor.model.flat[:n].float().cpu(), alpha=1 - a.train.ema_beta)
+                        with torch.no_grad():     # on the device: no host copy of the parameters per step
+                            n = self.ema_flat.numel()
+                            self.ema_flat.lerp_(self.actor.model.flat[:n].float(), 1 - a.train.ema_beta)
                 ntok, nsmp = float(mask.sum()), float(mask.shape[0])
                 for k, v in st.items():
                     sums[k] = sums.get(k, 0.0) + float(v) * ntok
@@ -383,7 +426,8 @@ class RLWorker:
             for exp, info, last in self._windows(buf, loader):
                 exp.to_device(self.device)
                 mask = exp.action_mask.float()
-                values = self.critic(exp.sequences, exp.action_mask, exp.attention_mask)
+                values = self.critic(exp.sequences, exp.action_mask, exp.attention_mask,
+                                     ring_attn_group=self.strategy.ring_attn_group)
                 norm = {k: info[k] for k in ("dp_size", "batch_num_tokens", "global_batch_size")}
                 loss = self.value_loss(values, exp.values, exp.returns, mask, **norm)
                 gas = 1 if a.train.dynamic_batch_enable else self.strategy.accumulated_gradient
@@ -403,21 +447,74 @@ class RLWorker:
                 "critic_grad_norm": eng.grad_norm()}
 
     # ------------------------------------------------------------------ weight sync / state management
-    def broadcast_to_vllm(self):
-        """Actor -> rollout weights. Colocated: the engine already reads the updated buffer. Separate rollout ranks:
-        broadcast the flat bf16 buffer from actor rank 0 over the global group (NCCL path, the baseline)."""
-        if self.actor is not None and self.rollout is not None:
-            tpt = getattr(self.actor.model, "tp_train", None)
-            if tpt is not None:
-                full = tpt.gather_full(self.actor.model)        # all shards -> full fused layout on every rank
-                self.rollout.update_weights(full)
-                return True
-            self.rollout.update_weights(self.actor.model.flat)
-            return True
-        if dist.is_initialized() and dist.get_world_size() > 1:
-            flat = (self.actor.model.flat if self.actor is not None else self.rollout.model.flat)
-            dist.broadcast(flat, src=0)
+    def setup_sync_group(self, host: str, port: int, rank: int, world: int, backend: str | None = None) -> bool:
+        """Join the weight-update group of a placement with separate rollout GPUs: trainer rank 0 plus every rollout
+        rank (openrlhf/trainer/ray/ppo_actor.py:163-217 builds the same group next to the training world)."""
+        from ..utils.distributed_util import stateless_process_group
+
+        backend = backend or ("nccl" if self.device.type == "cuda" else "gloo")
+        self._sync_pg = stateless_process_group(host, port, rank, world, backend, self.device)
+        self._sync_rank, self._sync_world = rank, world
         return True
+
+    @torch.no_grad()
+    def broadcast_to_vllm(self):
+        """Actor -> rollout weights.
+
+        Colocated (hybrid engine): stages 1 / 2 at rollout TP 1 share one buffer, nothing moves; every other case is
+        one launch of the copy kernel (ZeRO-3 slices -> full copy, full buffer or ZeRO-3 slices -> tensor-parallel
+        shard, tensor-parallel training shards -> full copy). Separate rollout GPUs: trainer rank 0 broadcasts the
+        flat bf16 buffer over the weight-update group and every rollout rank cuts its own shard out of it."""
+        if self.actor is not None and self.rollout is not None:
+            if self._sync_fn is not None:
+                self._sync_fn()
+            return True
+        pg = self._sync_pg
+        if pg is None:
+            if self.actor is not None and self.rollout is None:
+                # separate rollout GPUs, and this is not the broadcasting trainer rank: take part in assembling the
+                # full buffer where that is a collective (gloo ranks under ZeRO-3, tensor-parallel training shards)
+                kind, obj = self._rollout_source
+                if kind == "zero3" and self.device.type != "cuda":
+                    obj.gather_full()
+                elif kind == "tp_train":
+                    obj.tp_train.gather_full(obj)
+            return True
+        if self.actor is not None:
+            if self._sync_rank != 0:
+                return True
+            # the logical parameter range only: shard padding differs between the trainer's and the engines' buffers
+            src = self._full_actor_flat()[: self._logical_numel()]
+            pg.broadcast([src], _bcast_opts(0)).wait()
+        else:
+            buf = getattr(self, "_staging", None)
+            dst = (buf.flat if buf is not None else self.rollout_model.flat)[: self._logical_numel()]
+            pg.broadcast([dst], _bcast_opts(0)).wait()
+            if buf is not None:
+                self.rollout.update_weights(buf.flat)
+            elif self.rollout.quantization == "fp8":
+                self.rollout._refresh_fp8()
+        return True
+
+    def _logical_numel(self) -> int:
+        """Elements of the full flat parameter layout of the policy (without shard padding)."""
+        from ..models.transformer import ALIGN, build_param_specs
+
+        if self.actor is not None:
+            kind, obj = self._rollout_source
+            cfg = obj.tp_train.full_cfg if kind == "tp_train" else self.actor.cfg
+        else:
+            cfg = getattr(self, "_staging", self.rollout_model).cfg
+        last = build_param_specs(cfg)[-1]
+        return last.offset + (last.numel + ALIGN - 1) // ALIGN * ALIGN
+
+    def _full_actor_flat(self) -> torch.Tensor:
+        kind, obj = self._rollout_source
+        if kind == "zero3":
+            return obj.gather_full()
+        if kind == "tp_train":
+            return obj.tp_train.gather_full(obj)
+        return obj.flat
 
     def offload_states(self, role: str = "actor"):
         (self.actor_engine if role == "actor" else self.critic_engine).offload_states()
@@ -433,7 +530,15 @@ class RLWorker:
         if role == "actor":
             lm = self.actor.model
             if self.ema_model is not None:
-                lm = self.ema_model
+                # export the moving average through the actor's own layout, then put the live weights back
+                n = self.ema_flat.numel()
+                live = lm.flat[:n].clone()
+                lm.flat[:n].copy_(self.ema_flat.to(lm.flat.dtype))
+                try:
+                    self.strategy.save_model(lm, getattr(self, "tokenizer", None), a.ckpt.output_dir)
+                finally:
+                    lm.flat[:n].copy_(live)
+                return
             self.strategy.save_model(lm, getattr(self, "tokenizer", None), a.ckpt.output_dir)
         elif a.critic.save_value_network:
             self.strategy.save_model(self.critic, getattr(self, "tokenizer", None), a.ckpt.output_dir + "_critic")

@@ -1,12 +1,16 @@
-"""Hybrid-engine RL worker: one process per GPU hosts every role that lives on that GPU.
+"""Hybrid-engine RL worker driven SPMD: one process per GPU hosts every role that lives on that GPU and runs whole RL
+steps on its own share of the prompts.
+
+``HybridRLWorker`` IS the launcher's worker (``runtime.workers.RLWorker``: same constructor path, same engines, same
+weight sync) plus ``rl_step``: generate -> rewards -> old / reference log-probs (+ values) -> advantages -> PPO epochs
+over micro-batches -> weight sync, the unit the reference times in ``PPOTrainer.train_step``
+(openrlhf/trainer/ppo_trainer.py:213-264). Under ``python -m openrlhf.cli.train_ppo_ray`` a controller drives the same
+worker through RPCs instead (agents, remote rewards, dynamic filtering); under torchrun (``bench.py``, tests) every
+rank calls ``rl_step`` itself and the ranks meet only in the collectives of the engines.
 
 The reference's hybrid engine (``--train.colocate_all``: openrlhf/cli/train_ppo_ray.py:40-50,84-142) packs a vLLM
 engine, a DeepSpeed actor, and optionally reference / critic / reward models onto the same GPUs as fractional Ray
-actors and moves weights between them with CUDA IPC. Here the roles are plain objects of one process: the rollout
-engine reads the very buffer the ZeRO engine updates (weight sync at TP=1 is a no-op), and phase changes are method
-calls. ``rl_step`` is one synchronous RL step: generate -> rewards -> old/ref log-probs (+values) -> advantages ->
-PPO epochs over micro-batches -> weight sync, the unit the reference times in ``PPOTrainer.train_step``
-(openrlhf/trainer/ppo_trainer.py:213-264).
+actors and moves weights between them with CUDA IPC. Here the roles are plain objects of one process.
 """
 from __future__ import annotations
 
@@ -18,137 +22,95 @@ import torch
 import torch.distributed as dist
 
 from ..models.actor import Actor
-from ..models.config import ModelConfig
+from ..models.config import PRESETS, ModelConfig
 from ..models.packing import pack_lists
-from ..models.transformer import TransformerLM
 from ..ops import rl as K
-from ..parallel.zero import LRScheduler, ZeroEngine
 from ..rl.advantages import compute_advantages_and_returns
 from ..rl.experience import Experience
 from ..rl.kl_controller import FixedKLController
-from ..rollout.engine import RolloutEngine, SamplingParams
+from ..rollout.engine import SamplingParams
+from ..runtime.workers import RLWorker
 
 
 def default_rl_args(**over) -> SimpleNamespace:
-    """The subset of the train_ppo_ray flag tree this worker reads, with the reference's defaults."""
-    a = SimpleNamespace(
-        algo=SimpleNamespace(
-            advantage=SimpleNamespace(estimator="reinforce_baseline", gamma=1.0, lambd=0.95, no_std_norm=False,
-                                      is_correction_enable=False, is_correction_type="tis",
-                                      is_correction_threshold=(0.5, 5.0)),
-            kl=SimpleNamespace(init_coef=0.0, estimator="k1", use_loss=False, target=None, horizon=10000)),
-        rollout=SimpleNamespace(n_samples_per_prompt=8, max_new_tokens=2048, temperature=1.0, top_p=1.0,
-                                micro_batch_size=8),
-        train=SimpleNamespace(micro_batch_size=4, batch_size=128, max_epochs=1),
-        actor=SimpleNamespace(eps_clip_low_high=(0.2, 0.2), dual_clip=None, entropy_coef=None, policy_loss_type="ppo",
-                              adam=SimpleNamespace(lr=1e-6, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0),
-                              max_norm=1.0, lr_scheduler="cosine_with_min_lr", lr_warmup_ratio=0.03, min_lr_ratio=0.1,
-                              gradient_checkpointing_enable=False, aux_loss_coef=0.0),
-        critic=SimpleNamespace(value_clip=0.5, adam=SimpleNamespace(lr=9e-6, betas=(0.9, 0.95), eps=1e-8,
-                                                                     weight_decay=0.0), max_norm=1.0),
-        reward=SimpleNamespace(clip_range=(-10.0, 10.0), overlong_buffer_len=None, stop_properly_penalty_coef=None),
-        data=SimpleNamespace(max_len=4096),
-        ds=SimpleNamespace(zero_stage=2),
-    )
+    """The flag tree of ``train_ppo_ray`` with its defaults (hybrid engine, packed samples, REINFORCE++-baseline
+    without a KL term), then the dotted overrides, e.g. ``default_rl_args(**{"ds.zero_stage": 3})``."""
+    from ..cli import flags as F
+    from ..cli.train_ppo_ray import build_parser
+
+    a = F.finalize(build_parser(), ["--train.colocate_all", "--ds.packing_samples", "--reward.remote_url", "function",
+                                    "--algo.advantage.estimator", "reinforce_baseline", "--algo.kl.init_coef", "0",
+                                    "--rollout.n_samples_per_prompt", "8", "--rollout.max_new_tokens", "2048",
+                                    "--rollout.micro_batch_size", "8", "--train.micro_batch_size", "4",
+                                    "--data.max_len", "4096", "--train.seed", "0"])
+    a.algo.advantage.lambd = 0.95
+    a.rollout.ignore_eos = False
     for k, v in over.items():
         node = a
         parts = k.split(".")
         for p in parts[:-1]:
+            if not hasattr(node, p):
+                setattr(node, p, SimpleNamespace())
             node = getattr(node, p)
         setattr(node, parts[-1], v)
     return a
 
 
-class HybridRLWorker:
+class HybridRLWorker(RLWorker):
     def __init__(self, model_cfg: ModelConfig | str, args: SimpleNamespace | None = None, device=None,
-                 reward_fn: Callable | None = None, max_steps: int = 1000, seed: int = 0, group=None,
+                 reward_fn: Callable | None = None, max_steps: int = 1000, seed: int | None = None, group=None,
                  max_num_seqs: int = 256, num_pages: int | None = None, use_cuda_graph: bool = True,
-                 with_critic: bool | None = None, use_symm: bool = False, reward_model=None):
-        self.args = args or default_rl_args()
-        a = self.args
-        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
-        self.group = group
-        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if self.world > 1 else 0
-        cfg = ModelConfig.from_pretrained(model_cfg) if isinstance(model_cfg, str) else model_cfg
-        self.cfg = cfg
-        self.symm = None
-        flat = None
-        if use_symm and self.world > 1:
-            from ..parallel.symm import SymmBuffers
-            from ..models.transformer import build_param_specs, ALIGN
+                 with_critic: bool | None = None, use_symm: bool | None = None, reward_model=None,
+                 reward_model_path: str | None = None):
+        """model_cfg: a preset name / checkpoint directory, or a ModelConfig (random init). The process group, when
+        there is more than one rank, is the default one (torchrun environment); `group` is accepted for older callers
+        and must be None or the default group."""
+        from ..cli.train_ppo_ray import validate
 
-            specs = build_param_specs(cfg)
-            total = specs[-1].offset + (specs[-1].numel + ALIGN - 1) // ALIGN * ALIGN
-            self.symm = SymmBuffers(group, ZeroEngine.padded_numel(total, self.world), self.device)
-            flat = self.symm.param
-        self.model = TransformerLM(cfg, device=self.device, seed=seed, shard_world=self.world, flat=flat)
-        self.actor = Actor(self.model, temperature=a.rollout.temperature)
-        if a.actor.gradient_checkpointing_enable:
-            self.actor.gradient_checkpointing_enable()
-        sched = LRScheduler(a.actor.adam.lr, max_steps, a.actor.lr_warmup_ratio, a.actor.min_lr_ratio,
-                            a.actor.lr_scheduler)
-        self.zero3 = a.ds.zero_stage == 3 and self.world > 1 and not use_symm
-        self.rollout_model = self.model
-        ref_init = None
-        if self.zero3:
-            # stage 3: the trainer keeps only its slice of the parameters (plus two layer slots); the rollout engine
-            # gets a full copy of its own that the weight sync refreshes from the owners' slices (one copy kernel)
-            from ..parallel.zero3 import Zero3Engine
-
-            self.rollout_model = TransformerLM(cfg, device=self.device, seed=None, shard_world=self.world)
-            self.rollout_model.requires_grad_(False)
-            self.rollout_model.flat.copy_(self.model.flat[: self.rollout_model.flat.numel()])
-            ref_init = self.rollout_model.flat
-            self.engine = Zero3Engine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas),
-                                      eps=a.actor.adam.eps, weight_decay=a.actor.adam.weight_decay,
-                                      max_norm=a.actor.max_norm, group=group, scheduler=sched)
+        a = args or default_rl_args()
+        if isinstance(model_cfg, ModelConfig):
+            name = f"_config_{id(model_cfg)}"
+            PRESETS[name] = model_cfg
         else:
-            self.engine = ZeroEngine(self.model, lr=a.actor.adam.lr, betas=tuple(a.actor.adam.betas),
-                                     eps=a.actor.adam.eps, weight_decay=a.actor.adam.weight_decay,
-                                     max_norm=a.actor.max_norm, zero_stage=a.ds.zero_stage, group=group,
-                                     scheduler=sched, symm=self.symm)
-        self.ref = None
-        if a.algo.kl.init_coef > 0:
-            ref_model = TransformerLM(cfg, device=self.device, seed=None)
-            ref_model.flat.copy_((ref_init if ref_init is not None else self.model.flat)[: ref_model.flat.numel()])
-            ref_model.requires_grad_(False)
-            self.ref = Actor(ref_model, temperature=a.rollout.temperature)
-        self.critic = self.critic_engine = None
+            name = model_cfg
+        a.actor.model_name_or_path = name
+        if seed is not None:
+            a.train.seed = seed
         use_critic = with_critic if with_critic is not None else a.algo.advantage.estimator == "gae"
-        if use_critic:
-            cm = TransformerLM(cfg, device=self.device, seed=seed + 1, with_lm_head=False, with_value_head=True,
-                               shard_world=self.world)
-            self.critic = cm
-            self.critic_engine = ZeroEngine(cm, lr=a.critic.adam.lr, betas=tuple(a.critic.adam.betas),
-                                            eps=a.critic.adam.eps, weight_decay=a.critic.adam.weight_decay,
-                                            max_norm=a.critic.max_norm, zero_stage=a.ds.zero_stage, group=group,
-                                            scheduler=LRScheduler(a.critic.adam.lr, max_steps, 0.03, 0.1))
-        self.reward_model = reward_model      # models.model.RewardModel: scores full sequences when no reward_fn is set
+        a.critic.model_name_or_path = name if use_critic else None
+        a.reward.model_name_or_path = reward_model_path
+        if reward_model_path:
+            a.reward.remote_url = None
+        if getattr(a.actor, "eps_clip_low_high", None) is None:
+            a.actor.eps_clip_low_high = (a.actor.eps_clip, a.actor.eps_clip)
+        a.actor.eps_clip_low_high = tuple(a.actor.eps_clip_low_high)
+        a.vllm.num_engines = a.vllm.num_engines or 1
+        if int(getattr(a.ds, "ring_attn_size", 1) or 1) > 1:
+            raise ValueError("context parallelism runs through the launcher's controller (train_ppo_ray), where the "
+                             "members of a context-parallel group receive the same samples")
+        assert group is None or group is dist.group.WORLD, "the SPMD worker spans the default process group"
+        world = int(__import__("os").environ.get("WORLD_SIZE", "1"))
+        a.actor.num_nodes, a.actor.num_gpus_per_node = 1, world
+        roles = ["actor", "rollout"] + (["critic"] if use_critic else []) + \
+                (["ref"] if a.algo.kl.init_coef > 0 else []) + (["reward"] if reward_model_path else [])
+        del validate
+        super().__init__(a, roles=tuple(roles), max_steps=max_steps, backend=None,
+                         engine_opts={"max_num_seqs": max_num_seqs, "num_pages": num_pages,
+                                      "use_cuda_graph": use_cuda_graph, "use_symm": use_symm})
+        s = self.strategy
+        self.world, self.rank = s.mesh.dp, s.mesh.dp_rank
+        self.group = s.dp_group()
+        self.cfg = self.actor.cfg
+        self.model = self.actor.model
+        self.engine = self.actor_engine
+        self.symm = getattr(self.actor_engine, "symm", None)
+        self.zero3 = self._rollout_source[0] == "zero3"
+        self.tp_group = self._tp_groups[0]
+        if self.tp_group is not None:
+            self.rollout.spmd()             # every member issues the same generate() calls: no control channel
+        self.reward_model = reward_model if reward_model is not None else self.reward
         self.reward_fn = reward_fn
         self.kl_ctl = FixedKLController(a.algo.kl.init_coef)
-        self.rollout_tp = int(getattr(getattr(a, "vllm", None), "tensor_parallel_size", 1) or 1)
-        self.tp_group = None
-        if self.rollout_tp > 1 and self.world > 1:
-            # consecutive ranks form one tensor-parallel rollout engine: same requests on every member, weights sliced
-            # from this rank's full trainer buffer by the weight-sync copy plan at every sync
-            from ..rollout.tp_engine import make_tp_engine
-
-            assert self.world % self.rollout_tp == 0
-            for k in range(self.world // self.rollout_tp):
-                ranks = list(range(k * self.rollout_tp, (k + 1) * self.rollout_tp))
-                g_ = dist.new_group(ranks)
-                if self.rank in ranks:
-                    self.tp_group = g_
-            self.rollout = make_tp_engine(self.cfg, self.rollout_model.flat, self.tp_group,
-                                          max_num_seqs=max_num_seqs * self.rollout_tp, max_model_len=a.data.max_len,
-                                          num_pages=(num_pages * self.rollout_tp) if num_pages else None,
-                                          seed=seed + 1000 * (self.rank // self.rollout_tp),
-                                          use_cuda_graph=use_cuda_graph)
-        else:
-            self.rollout = RolloutEngine(self.rollout_model, max_num_seqs=max_num_seqs, max_model_len=a.data.max_len,
-                                         num_pages=num_pages, seed=seed + 1000 * self.rank,
-                                         use_cuda_graph=use_cuda_graph)
         self.timing: dict[str, float] = {}
         self.global_step = 0
 
@@ -211,8 +173,9 @@ class HybridRLWorker:
         for s in range(0, len(seqs), micro):
             chunk = seqs[s:s + micro]
             pb = pack_lists(chunk, self.device)
-            h, _ = self.critic(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
-            v = self.critic.values(h)
+            cm = self.critic.model
+            h, _ = cm(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+            v = cm.values(h)
             cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
             for i in range(len(chunk)):
                 out.append(v[cu[i]:cu[i + 1] - 1])
@@ -360,8 +323,8 @@ class HybridRLWorker:
             for m0 in range(0, len(window), micro):
                 mb = window[m0:m0 + micro]
                 pb = pack_lists([e.sequences for e in mb], self.device)
-                h, _ = self.critic(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
-                v_t = self.critic.values(h)
+                h, _ = self.critic.model(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+                v_t = self.critic.model.values(h)
                 cu = pb.cu_list if pb.cu_list is not None else pb.cu_seqlens.tolist()   # host copy: no device sync
                 sel = torch.cat([torch.arange(cu[i], cu[i + 1] - 1, device=self.device) for i in range(len(mb))])
                 cat = lambda f: torch.cat([getattr(e, f) for e in mb])
@@ -375,45 +338,52 @@ class HybridRLWorker:
                 "critic_grad_norm": self.critic_engine.grad_norm()}
 
     def sync_weights(self):
-        """Actor -> rollout weight hand-off. Trainer and rollout engine read the same buffer on this GPU, so after the
-        optimizer step (which all-gathers updated shards into every rank's buffer) there is nothing left to move."""
-        if self.zero3:
-            self.engine.gather_full(self.rollout_model.flat)     # K-SYNC from the owners' parameter slices
-            if self.tp_group is not None:
-                self.rollout.update_weights(self.rollout_model.flat)
-            return
-        self.rollout.update_weights(self.model.flat)
+        """Actor -> rollout weight hand-off (``RLWorker.broadcast_to_vllm``): nothing to move when trainer and rollout
+        engine read the same buffer, otherwise one launch of the copy kernel (ZeRO-3 slices -> full copy or
+        tensor-parallel shard, full buffer -> tensor-parallel shard)."""
+        self.broadcast_to_vllm()
 
     # ------------------------------------------------------------------ the RL step
     def rl_step(self, prompts: list[list[int]] | torch.Tensor) -> dict:
         """One synchronous RL step on this rank's prompts. `prompts` may be a pinned (P, L) CPU tensor."""
-        ev = {k: torch.cuda.Event(enable_timing=True) for k in ("t0", "gen", "exp", "train", "sync")}
-        ev["t0"].record()
+        on_gpu = self.device.type == "cuda"
+        marks: dict = {}
+
+        def mark(k):
+            if on_gpu:
+                marks[k] = torch.cuda.Event(enable_timing=True)
+                marks[k].record()
+            else:
+                marks[k] = time.perf_counter()
+
+        def between(a, b):
+            return marks[a].elapsed_time(marks[b]) / 1e3 if on_gpu else marks[b] - marks[a]
+
+        mark("t0")
         if isinstance(prompts, torch.Tensor):
             prompts = prompts.to(self.device, non_blocking=True).tolist()
         from ..utils.tracing import tracer
 
         with tracer.span("generation", cat="rl_step", step=self.global_step):
             exps = self.generate(prompts)
-        ev["gen"].record()
+        mark("gen")
         with tracer.span("make_experience", cat="rl_step", step=self.global_step):
             exps = self.make_experience(exps)
             exps = self.compute_advantages(exps)
-        ev["exp"].record()
+        mark("exp")
         status = {}
         with tracer.span("ppo_train", cat="rl_step", step=self.global_step):
             if self.critic is not None:
                 status.update(self.train_critic(exps))
             status.update(self.train(exps))
-        ev["train"].record()
+        mark("train")
         with tracer.span("broadcast", cat="rl_step", step=self.global_step):
             self.sync_weights()
-        ev["sync"].record()
-        torch.cuda.synchronize(self.device)
-        self.timing = {"timing/generation": ev["t0"].elapsed_time(ev["gen"]) / 1e3,
-                       "timing/make_experience": ev["gen"].elapsed_time(ev["exp"]) / 1e3,
-                       "timing/ppo_train": ev["exp"].elapsed_time(ev["train"]) / 1e3,
-                       "timing/broadcast": ev["train"].elapsed_time(ev["sync"]) / 1e3}
+        mark("sync")
+        if on_gpu:
+            torch.cuda.synchronize(self.device)
+        self.timing = {"timing/generation": between("t0", "gen"), "timing/make_experience": between("gen", "exp"),
+                       "timing/ppo_train": between("exp", "train"), "timing/broadcast": between("train", "sync")}
         self.timing["timing/step_total"] = sum(self.timing.values())
         status.update(self.timing)
         rw = torch.stack([e.rewards.to(self.device) for e in exps])

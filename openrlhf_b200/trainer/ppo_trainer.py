@@ -83,8 +83,38 @@ def compute_eval_metrics(eval_dataloader, samples_list, n_samples_per_prompt: in
     return logs
 
 
+class RoleGroups:
+    """Which worker group serves which role. Under ``--train.colocate_all`` one group hosts everything; otherwise the
+    launcher builds one group per placement (openrlhf/cli/train_ppo_ray.py:40-142) and the trainer addresses each
+    role through its own group."""
+
+    def __init__(self, actor, critic=None, ref=None, reward=None, rollout=None):
+        self.actor = actor
+        self.critic = critic if critic is not None else actor
+        self.ref = ref if ref is not None else actor
+        self.reward = reward if reward is not None else actor
+        self.rollout = rollout               # None: the rollout engines live on the actor group's workers
+
+    def of(self, role: str):
+        return getattr(self, role)
+
+    def distinct(self) -> list:
+        seen, out = set(), []
+        for g in (self.actor, self.critic, self.ref, self.reward, self.rollout):
+            if g is not None and id(g) not in seen:
+                seen.add(id(g))
+                out.append(g)
+        return out
+
+    def shutdown(self):
+        for g in self.distinct():
+            g.shutdown()
+
+
 class BasePPOTrainer:
     def __init__(self, strategy, group, has_critic: bool, has_ref: bool, has_reward: bool, tokenizer):
+        self.groups = group if isinstance(group, RoleGroups) else RoleGroups(group)
+        group = self.groups.actor
         self.strategy, self.args, self.group, self.tokenizer = strategy, strategy.args, group, tokenizer
         self.has_critic = has_critic
         a = self.args
@@ -92,8 +122,8 @@ class BasePPOTrainer:
             self.kl_ctl = AdaptiveKLController(a.algo.kl.init_coef, a.algo.kl.target, a.algo.kl.horizon)
         else:
             self.kl_ctl = FixedKLController(a.algo.kl.init_coef)
-        self.experience_maker = RemoteExperienceMaker(group, self.kl_ctl, strategy, tokenizer, has_critic, has_ref,
-                                                      has_reward)
+        self.experience_maker = RemoteExperienceMaker(self.groups, self.kl_ctl, strategy, tokenizer, has_critic,
+                                                      has_ref, has_reward)
         self.loggers = build_loggers(a, True)
         self.best_eval_metric_key = getattr(a.ckpt, "best_metric_key", "") or ""
         self.best_eval_metric_value = float("-inf")
@@ -118,7 +148,8 @@ class BasePPOTrainer:
             experiences = balance_experiences(experiences, a)
         get(self.group.async_run_method_batch("append", experience=experiences, role=["actor"] * len(experiences)))
         if self.has_critic:
-            get(self.group.async_run_method_batch("append", experience=experiences, role=["critic"] * len(experiences)))
+            get(self.groups.critic.async_run_method_batch("append", experience=experiences,
+                                                          role=["critic"] * len(experiences)))
         t1 = time.time()
         status = self.ppo_train(global_step)
         t_train = time.time() - t1
@@ -136,24 +167,37 @@ class BasePPOTrainer:
         a = self.args
         status = {}
         sleep = getattr(a.ds, "enable_sleep", False)
+        cg = self.groups.critic
+        critic_futs = None
         if self.has_critic:
             if sleep:
-                get(self.group.async_run_method("reload_states", role="critic"))
-            status.update(get(self.group.async_run_method("fit", role="critic"))[0])
-            if sleep:
-                get(self.group.async_run_method("offload_states", role="critic"))
+                get(cg.async_run_method("reload_states", role="critic"))
+            critic_futs = cg.async_run_method("fit", role="critic")
+            if cg is self.group:              # same workers: the critic trains first, then the actor
+                status.update(get(critic_futs)[0])
+                critic_futs = None
+                if sleep:
+                    get(cg.async_run_method("offload_states", role="critic"))
         if global_step >= getattr(a.critic, "freezing_steps", 0) or not self.has_critic:
             if sleep:
                 get(self.group.async_run_method("reload_states", role="actor"))
             status.update(get(self.group.async_run_method("fit", kl_ctl=self.kl_ctl.value, role="actor"))[0])
             if sleep:
                 get(self.group.async_run_method("offload_states", role="actor"))
+        if critic_futs is not None:           # critic on its own GPUs: it trained concurrently with the actor
+            status.update(get(critic_futs)[0])
+            if sleep:
+                get(cg.async_run_method("offload_states", role="critic"))
         return status
 
     def broadcast_to_vllm(self):
+        rg = self.groups.rollout
         if self.args.vllm.enable_sleep:
-            get(self.group.async_run_method("wake_up", tags=["weights"]))
-        get(self.group.async_run_method("broadcast_to_vllm"))
+            get((rg or self.group).async_run_method("wake_up", tags=["weights"]))
+        futs = self.group.async_run_method("broadcast_to_vllm")
+        if rg is not None:                    # rollout engines on their own GPUs receive over the weight-update group
+            futs = futs + rg.async_run_method("broadcast_to_vllm")
+        get(futs)
 
     @staticmethod
     def _compute_rollout_stats(experiences) -> dict:
@@ -188,8 +232,8 @@ class BasePPOTrainer:
                                            metric_value=metric_value, metric_key=metric_key)
         get(futs)
         if self.has_critic:
-            get(self.group.async_run_method("save_checkpoint", tag=tag, role="critic", metric_value=metric_value,
-                                            metric_key=metric_key))
+            get(self.groups.critic.async_run_method("save_checkpoint", tag=tag, role="critic",
+                                                    metric_value=metric_value, metric_key=metric_key))
 
     def save_best_checkpoint(self, eval_metrics: dict, global_step: int, client_states=None):
         if not eval_metrics:
@@ -233,12 +277,13 @@ class BasePPOTrainer:
 class PPOTrainer(BasePPOTrainer):
     """Synchronous trainer: generation and training alternate on the same workers."""
 
-    def __init__(self, pretrain: str, strategy, group, rollout_engines, has_critic, has_ref, has_reward):
+    def __init__(self, pretrain: str, strategy, group, rollout_engines, has_critic, has_ref, has_reward,
+                 rollout_followers=None):
         tokenizer = get_tokenizer(pretrain, None, "left", strategy, use_fast=not strategy.args.data.disable_fast_tokenizer)
         super().__init__(strategy, group, has_critic, has_ref, has_reward, tokenizer)
         self.prompts_dataloader, self.eval_dataloader, self.max_steps = prepare_datasets(strategy, tokenizer)
         self.samples_generator = SamplesGenerator(rollout_engines, strategy, tokenizer, self.prompts_dataloader,
-                                                  self.eval_dataloader)
+                                                  self.eval_dataloader, followers=rollout_followers)
 
     def get_max_steps(self) -> int:
         return self.max_steps

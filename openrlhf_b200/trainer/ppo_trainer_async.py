@@ -75,12 +75,12 @@ class PPOTrainerAsync(PPOTrainer):
     def broadcast_to_vllm(self):
         with self.engine_lock:
             if self.partial:
-                get(self.group.async_run_method("pause_generation"))
+                get((self.groups.rollout or self.group).async_run_method("pause_generation"))
             try:
                 super().broadcast_to_vllm()
             finally:
                 if self.partial:
-                    get(self.group.async_run_method("resume_generation"))
+                    get((self.groups.rollout or self.group).async_run_method("resume_generation"))
 
     def fit(self, global_step: int = 0) -> None:
         a = self.args

@@ -112,10 +112,21 @@ def _jsonable(x):
     if isinstance(x, (list, tuple)):
         return [_jsonable(v) for v in x]
     if isinstance(x, torch.Tensor):
-        return x.tolist()
+        # kept as a tensor through the round trip (a dataloader's generator state must come back as a ByteTensor)
+        return {"__tensor__": x.detach().cpu().tolist(), "dtype": str(x.dtype).replace("torch.", "")}
     if isinstance(x, (int, float, str, bool)) or x is None:
         return x
     return repr(x)
+
+
+def _from_jsonable(x):
+    if isinstance(x, dict):
+        if set(x) == {"__tensor__", "dtype"}:
+            return torch.tensor(x["__tensor__"], dtype=getattr(torch, x["dtype"]))
+        return {k: _from_jsonable(v) for k, v in x.items()}
+    if isinstance(x, list):
+        return [_from_jsonable(v) for v in x]
+    return x
 
 
 def resolve_tag(load_dir: str, tag: str | None) -> str | None:
@@ -158,11 +169,12 @@ def load_sharded(engine, load_dir: str, tag: str | None = None, load_optimizer_s
                 if k != "master" and not load_optimizer_states:
                     continue
                 bufs[k][x - lo:y - lo] = h.get_slice(k)[x - a:y - a]
-    dev = engine.master.device
+    cur = engine.shard_state()               # tensors on the device, or on the host while the states are offloaded
+    dev = engine.device
     engine.load_shard_state(bufs["master"].to(dev),
-                            bufs["exp_avg"].to(dev) if load_optimizer_states else engine.exp_avg,
-                            bufs["exp_avg_sq"].to(dev) if load_optimizer_states else engine.exp_avg_sq,
+                            bufs["exp_avg"].to(dev) if load_optimizer_states else cur["exp_avg"].to(dev),
+                            bufs["exp_avg_sq"].to(dev) if load_optimizer_states else cur["exp_avg_sq"].to(dev),
                             man["opt_step"] if load_optimizer_states else engine.opt_step)
     if load_lr_scheduler_states and engine.scheduler is not None and man.get("scheduler"):
         engine.scheduler.load_state_dict(man["scheduler"])
-    return d, man.get("client_state", {})
+    return d, _from_jsonable(man.get("client_state", {}))

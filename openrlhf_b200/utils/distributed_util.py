@@ -32,3 +32,25 @@ def init_process_group(backend: str | None = None, timeout_minutes: int = 60) ->
             kw["device_id"] = torch.device(f"cuda:{local}")
         dist.init_process_group(backend, timeout=datetime.timedelta(minutes=timeout_minutes), **kw)
     return rank, local, world
+
+
+def stateless_process_group(host: str, port: int, rank: int, world: int, backend: str = "gloo", device=None,
+                            timeout_s: int = 1800):
+    """A process group next to (and independent of) the default one, over its own TCP store.
+
+    The trainer world and the rollout world of a placement with separate rollout GPUs are two torch.distributed
+    worlds; the weight-update group that spans trainer rank 0 and all rollout ranks is built with this helper
+    (the reference builds the same kind of extra group: openrlhf/utils/distributed_util.py:17-26,
+    openrlhf/trainer/ray/ppo_actor.py:163-217). Returns a backend object with ``broadcast([tensor], opts)``."""
+    to = datetime.timedelta(seconds=timeout_s)
+    store = dist.TCPStore(host, int(port), world, is_master=(rank == 0), timeout=to)
+    store = dist.PrefixStore("weight_update", store)
+    if backend == "gloo":
+        return dist.ProcessGroupGloo(store, rank, world, to)
+    if backend == "nccl":
+        if device is not None and torch.device(device).type == "cuda":
+            torch.cuda.set_device(device)
+        opts = dist.ProcessGroupNCCL.Options()
+        opts._timeout = to
+        return dist.ProcessGroupNCCL(store, rank, world, opts)
+    raise ValueError(f"unknown backend {backend}")

@@ -50,6 +50,11 @@ class RankMesh:
             return [(dp_r * self.sp + s) * self.tp + tp_r for s in range(self.sp)]
         if dim == "dp":
             return [(d * self.sp + sp_r) * self.tp + tp_r for d in range(self.dp)]
+        if dim == "zero":
+            # every rank that holds the same tensor-parallel shard: data-parallel replicas and their context-parallel
+            # members. Gradients are averaged, and ZeRO state is sharded, over this set (a context-parallel rank's
+            # gradient is `sp` times the partial gradient of its rows, so the mean over the set is the full gradient).
+            return [(d * self.sp + s_) * self.tp + tp_r for d in range(self.dp) for s_ in range(self.sp)]
         raise KeyError(dim)
 
     def group(self, dim: str):
@@ -160,7 +165,7 @@ class Strategy:
         if torch.cuda.is_available():
             torch.cuda.set_device(self.local_rank)
         self.mesh = RankMesh(self.world_size, self.ring_attn_size, self.ds_tensor_parallel_size, self.rank)
-        for dim in ("dp", "sp", "tp"):
+        for dim in ("dp", "sp", "tp") + (("zero",) if self.ring_attn_size > 1 else ()):
             self.mesh.group(dim)
         dp = self.mesh.dp
         self.accumulated_gradient = max(1, self.train_batch_size * self.ring_attn_size * self.ds_tensor_parallel_size
@@ -181,6 +186,14 @@ class Strategy:
 
     def dp_group(self):
         return self.mesh.group("dp")
+
+    def zero_group(self):
+        """Ranks over which gradients are averaged and ZeRO state is sharded (dp x ring-attention members)."""
+        return self.mesh.group("zero") if self.ring_attn_size > 1 else self.mesh.group("dp")
+
+    @property
+    def zero_world(self) -> int:
+        return self.mesh.dp * self.mesh.sp
 
     def device(self):
         return torch.device("cuda", self.local_rank) if torch.cuda.is_available() else torch.device("cpu")
@@ -204,7 +217,7 @@ class Strategy:
             full = _inner_lm(module)
             if getattr(full, "tp_train", None) is not None:
                 return module
-            shard = shard_for_training(full, self.mesh.group("tp"), shard_world=self.mesh.dp)
+            shard = shard_for_training(full, self.mesh.group("tp"), shard_world=self.zero_world)
             return _replace_inner_lm(module, shard)
 
         for arg in models_or_model_optim_pairs:
@@ -223,19 +236,21 @@ class Strategy:
                     eng = MuonEngine(lm, muon_lr=mu.get("lr", 0.02), momentum=mu.get("momentum", 0.95),
                                      adam_lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
-                                     max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched,
+                                     max_norm=self.max_norm, group=self.zero_group(), scheduler=sched,
                                      ns_steps=mu.get("ns_steps", 5), nesterov=mu.get("nesterov", True))
-                elif (self.stage == 3 and self.world_size > 1 and self.ring_attn_size == 1 and tp == 1
-                      and getattr(lm, "lora", None) is None):
+                elif self.stage == 3 and self.zero_world > 1:
                     from ..parallel.zero3 import Zero3Engine
 
+                    if tp > 1 or getattr(lm, "lora", None) is not None:
+                        raise ValueError("--ds.zero_stage 3 is not combined with --ds.tensor_parallel_size > 1 or LoRA "
+                                         "adapters; use stage 2 for those runs")
                     eng = Zero3Engine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                       eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
-                                      max_norm=self.max_norm, group=self.mesh.group("dp"), scheduler=sched)
+                                      max_norm=self.max_norm, group=self.zero_group(), scheduler=sched)
                 else:
                     eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
-                                     max_norm=self.max_norm, zero_stage=self.stage, group=self.mesh.group("dp"),
+                                     max_norm=self.max_norm, zero_stage=self.stage, group=self.zero_group(),
                                      scheduler=sched, use_symm=False if tp > 1 else cfg.get("use_symm"))
                 out.append(_Prepared(module, eng))
             else:
