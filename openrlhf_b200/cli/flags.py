@@ -53,6 +53,9 @@ ENGINE = [
     ("--ds.experts_implementation", str, None), ("--ds.use_liger_kernel", BOOL, False),
     ("--ds.grad_accum_dtype", str, None), ("--ds.overlap_comm", BOOL, False), ("--ds.deepcompile", BOOL, False),
     ("--ds.tensor_parallel_size", int, 1), ("--ds.ring_attn_size", int, 1), ("--ds.ring_attn_head_stride", int, 1),
+    # expert parallelism for mixture-of-experts models: this many consecutive data-parallel ranks split the experts of
+    # every MoE layer between them (dispatch / combine over peer memory); the reference has no counterpart
+    ("--ds.expert_parallel_size", int, 1),
     ("--ds.load_in_4bit", BOOL, False), ("--ds.lora.rank", int, 0), ("--ds.lora.alpha", int, 16),
     ("--ds.lora.target_modules", str, "all-linear", {"nargs": "*"}), ("--ds.lora.dropout", float, 0),
     ("--ds.packing_samples", BOOL, False), ("--ds.use_universal_ckpt", BOOL, False),

@@ -6,6 +6,8 @@ from __future__ import annotations
 import argparse
 
 import torch
+from fastapi import FastAPI, Request          # module level: the route's `request: Request` annotation is resolved
+from fastapi.responses import JSONResponse    # against the module globals
 
 from ..models.model import get_llm_for_sequence_regression
 from ..utils.utils import get_tokenizer
@@ -41,9 +43,6 @@ class RewardModelProxy:
 
 
 def build_app(proxy: RewardModelProxy):
-    from fastapi import FastAPI, Request
-    from fastapi.responses import JSONResponse
-
     app = FastAPI()
 
     @app.post("/get_reward")

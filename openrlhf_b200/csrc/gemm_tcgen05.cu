@@ -37,6 +37,7 @@ struct GemmParams {
   int n_peer_c;         //   them with red.add over NVLink (row-parallel linear: GEMM + all-reduce in one kernel)
   int ag_world;         // >0: A is row-sharded over ag_world ranks (all-gather fused into the A-tile loads)
   int ag_rows;          //   rows held by each rank (multiple of 128)
+  int rs_rows;          // >0 with peer_c: reduce-scatter epilogue, rank r owns output rows [r*rs_rows, (r+1)*rs_rows)
   // grouped (mixture-of-experts) extensions
   int group_mode;            // 0 plain; 1: every 128-row M tile belongs to one group and multiplies that group's B
                              // (rows of A / C sorted by group, each group padded to a multiple of 128 rows);
@@ -56,6 +57,19 @@ struct GemmParams {
   int sw_half;
   __nv_bfloat16* C2;
   int ldc2;
+  // LM-head epilogues (K-LMHEAD): the product is logits[tokens, vocabulary], never written as such.
+  //   lp_mode 1 (forward): every tile reduces its BN columns to per-row softmax partials
+  //       lp_partial[(n_blk * M + row) * 8 + {0: max z, 1: sum exp((z - max) / T), 2: sum exp(z - max),
+  //                   3: sum exp(z - max) (z - max), 4: label logit, 5: 1 if the label's column is in this tile}]
+  //       (a merge kernel folds the n_blocks partials of a row into log-prob, log-sum-exp and entropy);
+  //   lp_mode 2 (backward recomputation): C receives d logits = g / T * (onehot(label) - exp(z / T - lse)) as bf16.
+  int lp_mode;
+  const long long* lp_labels;   // [M] label token of each row (outside [0, N): no one-hot term, vocabulary shards)
+  float lp_inv_t;               // 1 / temperature
+  float* lp_partial;            // mode 1
+  const float* lp_lse;          // mode 2: [M] log-sum-exp of z / T
+  const float* lp_dlogp;        // mode 2: [M] upstream gradient of the log-prob
+  int lp_entropy;               // mode 1: also accumulate the entropy terms (slots 2, 3)
 };
 
 // Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
@@ -240,6 +254,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // fp32 outputs: rows and slabs 32-byte aligned (8 floats)
     const bool wide_f = p.out_f32 && (p.ldc % 8 == 0) && (p.split_stride % 8 == 0) && (p.group_c_stride % 8 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
+    // 16-byte vector reductions (wgrad accumulation, tensor-parallel pushes): rows, slabs and bases 16-byte aligned
+    const bool v4_ok = p.out_f32 && (p.ldc % 4 == 0) && (p.split_stride % 4 == 0) && (p.group_c_stride % 4 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const bool wide_c2 = p.C2 != nullptr && (p.ldc2 % 16 == 0) && (p.sw_half % 16 == 0) &&
                          ((reinterpret_cast<uintptr_t>(p.C2) & 31) == 0);
     int local = 0;
@@ -256,7 +273,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool has_work = kb1 > kb0;
       const float alpha = p.alpha_dev != nullptr ? p.alpha * *p.alpha_dev : p.alpha;
-      if (p.swiglu) {
+      if (p.lp_mode == 1) {
+        // ---- fused LM head, forward: softmax partials of this tile's columns; thread = token row
+        const long long label = row_ok ? p.lp_labels[row] : -1;
+        const int colbase = n_blk * BN;
+        constexpr float LOG2E = 1.4426950408889634f;
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {                  // pass 1: row maximum over the tile
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = colbase + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) mx = fmaxf(mx, __uint_as_float(r[j]) * alpha);
+        }
+        float s = 0.f, s1 = 0.f, sz = 0.f, lab = 0.f, has = 0.f;
+        const float kt = p.lp_inv_t * LOG2E;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {                  // pass 2: sums relative to the tile maximum
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = colbase + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.N) {
+              const float d = __uint_as_float(r[j]) * alpha - mx;
+              s += exp2f(d * kt);
+              if (p.lp_entropy) {
+                const float e = exp2f(d * LOG2E);
+                s1 += e;
+                sz += e * d;
+              }
+              if ((long long)(col0 + j) == label) { lab = d + mx; has = 1.f; }
+            }
+          }
+        }
+        if (row_ok && has_work) {
+          float4* dst = reinterpret_cast<float4*>(p.lp_partial + ((size_t)n_blk * p.M + row) * 8);
+          dst[0] = make_float4(mx, s, s1, sz);
+          dst[1] = make_float4(lab, has, 0.f, 0.f);
+        }
+      } else if (p.swiglu) {
         // TMEM columns [0, BN/2) hold the gate products, [BN/2, BN) the up products of the same output columns
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
@@ -348,19 +408,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 float4 v = make_float4(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha,
                                        __uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
                 if (p.n_peer_c > 0) {
-                  const size_t off = (size_t)row * p.ldc + col0 + j;
-                  for (int pr = 0; pr < p.n_peer_c; ++pr) {
-                    float* dst = p.peer_c[pr] + off;
-                    atomicAdd(dst, v.x);
-                    atomicAdd(dst + 1, v.y);
-                    atomicAdd(dst + 2, v.z);
-                    atomicAdd(dst + 3, v.w);
+                  if (p.rs_rows > 0) {
+                    // reduce-scatter: rank r owns rows [r * rs_rows, (r + 1) * rs_rows) of the output; a tile goes
+                    // only to the owner of its rows, at the row's index inside the owner's [rs_rows, ldc] buffer, as
+                    // one 16-byte reduction per four columns. (tp - 1) / tp of the tiles cross NVLink, once.
+                    const int owner = row / p.rs_rows;
+                    float* dst = p.peer_c[owner] + (size_t)(row - owner * p.rs_rows) * p.ldc + col0 + j;
+                    if (v4_ok) red_add_v4(dst, v.x, v.y, v.z, v.w);
+                    else { atomicAdd(dst, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w); }
+                  } else {
+                    const size_t off = (size_t)row * p.ldc + col0 + j;
+                    for (int pr = 0; pr < p.n_peer_c; ++pr) {      // all-reduce by push: every peer gets the tile
+                      float* dst = p.peer_c[pr] + off;
+                      if (v4_ok) red_add_v4(dst, v.x, v.y, v.z, v.w);
+                      else { atomicAdd(dst, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w); }
+                    }
                   }
                 } else if (p.accumulate) {
-                  atomicAdd(crow + j, v.x);
-                  atomicAdd(crow + j + 1, v.y);
-                  atomicAdd(crow + j + 2, v.z);
-                  atomicAdd(crow + j + 3, v.w);
+                  if (v4_ok) red_add_v4(crow + j, v.x, v.y, v.z, v.w);
+                  else { atomicAdd(crow + j, v.x); atomicAdd(crow + j + 1, v.y); atomicAdd(crow + j + 2, v.z); atomicAdd(crow + j + 3, v.w); }
                 } else {
                   *reinterpret_cast<float4*>(crow + j) = v;
                 }
@@ -378,6 +444,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   float v[8];
 #pragma unroll
                   for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[jj + q]) * alpha;
+                  if (p.lp_mode == 2) {
+                    // d logits of the log-prob: g / T * (onehot - softmax(z / T)), from the recomputed logits
+                    const float g = p.lp_dlogp[row] * p.lp_inv_t, lse = p.lp_lse[row];
+                    const long long label = p.lp_labels[row];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                      const float o = -g * __expf(v[q] * p.lp_inv_t - lse);
+                      v[q] = ((long long)(col0 + jj + q) == label) ? o + g : o;
+                    }
+                  }
                   if (p.bias != nullptr) {
                     uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + jj);
                     const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
@@ -594,6 +670,99 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
 }
 
 
+// ------------------------------------------------------------------------------------------------------------------
+// Fused LM head (K-LMHEAD). Forward: logits = H W^T are reduced tile by tile to softmax partials inside the GEMM
+// epilogue (lp_mode 1) and a merge kernel folds a row's partials into log p(label), log-sum-exp and entropy; the
+// [tokens, vocabulary] logits are never written. Backward: the logits are recomputed and the epilogue writes
+// d logits directly (lp_mode 2), ready to be the operand of the dH and dW GEMMs.
+// Stands in for lm_head -> logits.float() -> log_softmax -> gather (+ entropy) of the reference
+// (openrlhf/models/actor.py:265-296, openrlhf/models/utils.py:139-186).
+constexpr int LMHEAD_BN = 256;
+
+extern "C" int b200_lmhead_num_blocks(int V) { return (V + LMHEAD_BN - 1) / LMHEAD_BN; }
+
+static int lmhead_launch(const void* H, const void* W, int T, int V, int K, int ldh, int ldw, GemmParams& p,
+                         cudaStream_t stream) {
+  if (T <= 0 || V <= 0 || K <= 0) return 0;
+  if ((ldh % 8) || (ldw % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(H) | reinterpret_cast<uintptr_t>(W)) & 15) return -12;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16_2d(&ta, H, T, K, ldh, BM, BK);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tb, W, V, K, ldw, LMHEAD_BN, BK);
+  if (r) return r;
+  p.M = T; p.N = V; p.K = K; p.k_splits = 1; p.alpha = 1.f;
+  static PeerMaps no_peers;
+  return launch<LMHEAD_BN, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
+}
+
+// partial: fp32 [b200_lmhead_num_blocks(V), T, 8]
+extern "C" int b200_lmhead_partials(const void* H, const void* W, const long long* labels, float inv_t, int want_entropy,
+                                    float* partial, int T, int V, int K, int ldh, int ldw, int* status, void* stream_) {
+  if ((reinterpret_cast<uintptr_t>(partial) & 15) != 0) return -12;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.status = status; p.ldc = 8; p.out_f32 = 1;
+  p.lp_mode = 1; p.lp_labels = labels; p.lp_inv_t = inv_t; p.lp_partial = partial; p.lp_entropy = want_entropy;
+  return lmhead_launch(H, W, T, V, K, ldh, ldw, p, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// dlogits: bf16 [T, ldc] (ldc >= V, multiple of 8)
+extern "C" int b200_lmhead_dlogits(const void* H, const void* W, void* dlogits, const long long* labels, const float* lse,
+                                   const float* dlogp, float inv_t, int T, int V, int K, int ldh, int ldw, int ldc,
+                                   int* status, void* stream_) {
+  if ((ldc % 8) || (V % 8) || (reinterpret_cast<uintptr_t>(dlogits) & 15)) return -10;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.status = status; p.C = dlogits; p.ldc = ldc; p.out_f32 = 0;
+  p.lp_mode = 2; p.lp_labels = labels; p.lp_inv_t = inv_t; p.lp_lse = lse; p.lp_dlogp = dlogp;
+  return lmhead_launch(H, W, T, V, K, ldh, ldw, p, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+namespace b200 {
+// One thread per token row: fold the row's n_blocks tile partials (see GemmParams::lp_mode) into
+//   logp = z_label / T - logsumexp(z / T),  lse = logsumexp(z / T),  entropy = H(softmax(z)) (untempered).
+__global__ void __launch_bounds__(256)
+lmhead_merge_kernel(const float* __restrict__ partial, int n_blocks, int T, float inv_t, float* __restrict__ out_logp,
+                    float* __restrict__ out_entropy, float* __restrict__ out_lse) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T) return;
+  float M = -INFINITY;
+  for (int b = 0; b < n_blocks; ++b) M = fmaxf(M, partial[((size_t)b * T + row) * 8]);
+  float S = 0.f, S1 = 0.f, SZ = 0.f, lab = 0.f, has = 0.f;
+  for (int b = 0; b < n_blocks; ++b) {
+    const float4 a = *reinterpret_cast<const float4*>(partial + ((size_t)b * T + row) * 8);
+    const float4 c = *reinterpret_cast<const float4*>(partial + ((size_t)b * T + row) * 8 + 4);
+    const float d = a.x - M;                       // <= 0
+    S += a.y * __expf(d * inv_t);
+    if (out_entropy != nullptr) {
+      const float e = __expf(d);
+      S1 += a.z * e;
+      SZ += (a.w + a.z * d) * e;                   // sum e^{z-M} (z-M) = e^{m-M} (sum e^{z-m} (z-m) + (m-M) sum e^{z-m})
+    }
+    if (c.y > 0.5f) { lab = c.x; has = 1.f; }
+  }
+  const float logS = __logf(S);
+  if (out_lse != nullptr) out_lse[row] = M * inv_t + logS;
+  if (out_logp != nullptr) out_logp[row] = has > 0.5f ? (lab - M) * inv_t - logS : -(M * inv_t + logS);
+  if (out_entropy != nullptr) out_entropy[row] = __logf(S1) - SZ / S1;
+}
+}  // namespace b200
+
+extern "C" int b200_lmhead_merge(const float* partial, int n_blocks, int T, float inv_t, float* out_logp,
+                                 float* out_entropy, float* out_lse, void* stream_) {
+  if (T <= 0) return 0;
+  b200::lmhead_merge_kernel<<<(T + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      partial, n_blocks, T, inv_t, out_logp, out_entropy, out_lse);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+
 // Y[M, I] = silu(A W_gate^T) * (A W_up^T) with W = [gate rows | up rows] ([2I, K], K-major); GU (optional, [M, ldgu])
 // receives the bf16 gate / up products for the backward pass. I must be a multiple of bn / 2.
 extern "C" int b200_gemm_bf16_swiglu(const void* A, const void* W, void* Y, void* GU, int M, int I, int K, int lda,
@@ -630,13 +799,17 @@ extern "C" int b200_gemm_bf16_swiglu(const void* A, const void* W, void* Y, void
 // Tensor-parallel linear layers of the rollout engine as single kernels (plain tiled TMA on peer memory for loads,
 // red.add over NVLink for the reduction; no collective launch in between).
 //  * row-parallel (o_proj / down_proj): C_partial = A[M, K/tp] * B[N, K/tp]^T is added, tile by tile from the epilogue,
-//    into the fp32 buffer `peer_c[r]` of every TP rank r: afterwards each rank holds the all-reduced sum.
+//    into the fp32 buffer `peer_c[r]` of every TP rank r: afterwards each rank holds the all-reduced sum. Mode 2 is
+//    the reduce-scatter form: rank r owns output rows [r*rows_per_rank, (r+1)*rows_per_rank) and every tile goes only
+//    to the owner of its rows ((tp-1)/tp of the output crosses NVLink once; the gather-A GEMM that follows reads the
+//    row shards from their owners).
 //  * column-parallel with sequence-parallel input (qkv / gate_up): A is row-sharded over the TP ranks
 //    (`a_shards[r]` = rank r's [rows_per_rank, K] block); the A-tile loads fetch the rows from their owner, i.e. the
 //    all-gather is fused into the operand loads. Output is bf16 C[M_total, N_local] (+ bias).
 extern "C" int b200_gemm_bf16_tp(const void* A, const void* const* a_shards, const void* B, void* C,
                                  const void* const* peer_c, const void* bias, int M, int N, int K, int lda, int ldb,
-                                 int ldc, int tp, int rows_per_rank, int mode /*0: push-reduce, 1: gather-A*/, int bn,
+                                 int ldc, int tp, int rows_per_rank,
+                                 int mode /*0: push all-reduce, 1: gather-A, 2: reduce-scatter by rows*/, int bn,
                                  int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -657,8 +830,12 @@ extern "C" int b200_gemm_bf16_tp(const void* A, const void* const* a_shards, con
   p.n_peer_c = 0; p.ag_world = 0; p.ag_rows = 0;
   for (int i = 0; i < 8; ++i) p.peer_c[i] = nullptr;
   int r;
-  if (mode == 0) {
+  if (mode == 0 || mode == 2) {
     if (ldc % 4 || N % 4) return -10;
+    if (mode == 2) {
+      if (rows_per_rank <= 0 || rows_per_rank * tp < M) return -10;
+      p.rs_rows = rows_per_rank;
+    }
     r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
     if (r) return r;
     p.C = const_cast<void*>(peer_c[0]);

@@ -275,25 +275,57 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 
 # ---------------------------------------------------------------------------------------------- LM head -> log-probs
+def _lmhead_fusable(h: torch.Tensor, w: torch.Tensor) -> bool:
+    return (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and h.stride(1) == 1 and w.stride(1) == 1
+            and h.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and w.shape[0] % 8 == 0
+            and h.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 class _FusedLogprob(torch.autograd.Function):
-    """log p(label) (and optionally entropy) per token from hidden states, vocabulary streamed in row chunks so the
-    full [T, V] logits never exist; backward recomputes each chunk."""
+    """log p(label) (and optionally entropy) per token from hidden states without ever writing [T, V] logits.
+
+    Forward: one tcgen05 GEMM whose epilogue reduces every 128 x 256 logits tile to per-row softmax partials (32 bytes
+    per row and tile instead of 512 bytes of bf16 logits), then a merge kernel over a row's tiles. Backward: the
+    logits are recomputed in row chunks by the same GEMM with an epilogue that writes d logits = g/T (onehot -
+    softmax) directly as the bf16 operand of the dH and dW GEMMs (no separate pass over the chunk)."""
 
     @staticmethod
     def forward(ctx, h, w, labels, temperature, want_entropy, chunk):
-        T = h.shape[0]
+        T, K = h.shape
         V = w.shape[0]
-        logp = torch.empty(T, dtype=torch.float32, device=h.device)
-        ent = torch.empty(T, dtype=torch.float32, device=h.device) if want_entropy else None
-        lse = torch.empty(T, dtype=torch.float32, device=h.device)
-        for s in range(0, T, chunk):
-            e = min(T, s + chunk)
-            logits = gemm(h[s:e], w)
-            rc = _L().b200_logprob_rows(_lib.ptr(logits), _c_int(1), _c_int(e - s), _c_int(V), _c_int(logits.stride(0)),
-                                        _lib.ptr(labels[s:e]), _c_f(temperature), _lib.ptr(logp[s:e]),
-                                        _lib.ptr(ent[s:e]) if ent is not None else None, _lib.ptr(lse[s:e]),
-                                        _lib.stream_ptr())
-            _lib.check_rc(rc, "logprob_rows")
+        dev = h.device
+        logp = torch.empty(T, dtype=torch.float32, device=dev)
+        ent = torch.empty(T, dtype=torch.float32, device=dev) if want_entropy else None
+        lse = torch.empty(T, dtype=torch.float32, device=dev)
+        L = _L()
+        inv_t = 1.0 / temperature
+        if _lmhead_fusable(h, w):
+            nb = int(L.b200_lmhead_num_blocks(_c_int(V)))
+            rows_max = max(128, min(T, (1 << 28) // (nb * 8)))            # partial buffer of at most 1 GiB
+            partial = torch.empty(nb * min(T, rows_max) * 8, dtype=torch.float32, device=dev)
+            st = _lib.status_word(dev)
+            for s in range(0, T, rows_max):
+                e = min(T, s + rows_max)
+                rc = L.b200_lmhead_partials(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(labels[s:e]), _c_f(inv_t),
+                                            _c_int(int(want_entropy)), _lib.ptr(partial), _c_int(e - s), _c_int(V),
+                                            _c_int(K), _c_int(h.stride(0)), _c_int(w.stride(0)), _lib.ptr(st),
+                                            _lib.stream_ptr())
+                _lib.check_rc(rc, "lmhead_partials")
+                rc = L.b200_lmhead_merge(_lib.ptr(partial), _c_int(nb), _c_int(e - s), _c_f(inv_t), _lib.ptr(logp[s:e]),
+                                         _lib.ptr(ent[s:e]) if ent is not None else None, _lib.ptr(lse[s:e]),
+                                         _lib.stream_ptr())
+                _lib.check_rc(rc, "lmhead_merge")
+            ctx.fused = True
+        else:
+            for s in range(0, T, chunk):
+                e = min(T, s + chunk)
+                logits = gemm(h[s:e], w)
+                rc = L.b200_logprob_rows(_lib.ptr(logits), _c_int(1), _c_int(e - s), _c_int(V), _c_int(logits.stride(0)),
+                                         _lib.ptr(labels[s:e]), _c_f(temperature), _lib.ptr(logp[s:e]),
+                                         _lib.ptr(ent[s:e]) if ent is not None else None, _lib.ptr(lse[s:e]),
+                                         _lib.stream_ptr())
+                _lib.check_rc(rc, "logprob_rows")
+            ctx.fused = False
         ctx.save_for_backward(h, w, labels, lse)
         ctx.temperature, ctx.chunk, ctx.w_ref = temperature, chunk, w
         ctx.want_entropy = want_entropy
@@ -306,21 +338,32 @@ class _FusedLogprob(torch.autograd.Function):
     def backward(ctx, dlogp, _dent):
         h, w, labels, lse = ctx.saved_tensors
         T, V = h.shape[0], w.shape[0]
+        K = h.shape[1]
         inv_t = 1.0 / ctx.temperature
         dh = torch.empty_like(h)
         mg = getattr(ctx.w_ref, "main_grad", None)
         dw_buf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
         dlogp = dlogp.float().contiguous()
+        L = _L()
+        st = _lib.status_word(h.device)
         for s in range(0, T, ctx.chunk):
             e = min(T, s + ctx.chunk)
-            logits = gemm(h[s:e], w)
-            # d logits = g/T * (onehot - softmax(z/T))
-            rc = _L().b200_logprob_bwd_rows(_lib.ptr(logits), _c_int(e - s), _c_int(V), _c_int(logits.stride(0)),
-                                            _lib.ptr(labels[s:e]), _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]),
-                                            _c_f(inv_t), _lib.stream_ptr())
-            _lib.check_rc(rc, "logprob_bwd_rows")
-            gemm(logits, w, b_mn=True, out=dh[s:e])
-            gemm(logits, h[s:e], a_mn=True, b_mn=True, out=dw_buf, accumulate=True)
+            if ctx.fused:
+                dz = torch.empty(e - s, V, dtype=torch.bfloat16, device=h.device)
+                rc = L.b200_lmhead_dlogits(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(dz), _lib.ptr(labels[s:e]),
+                                           _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]), _c_f(inv_t), _c_int(e - s),
+                                           _c_int(V), _c_int(K), _c_int(h.stride(0)), _c_int(w.stride(0)), _c_int(V),
+                                           _lib.ptr(st), _lib.stream_ptr())
+                _lib.check_rc(rc, "lmhead_dlogits")
+            else:
+                dz = gemm(h[s:e], w)
+                # d logits = g/T * (onehot - softmax(z/T))
+                rc = L.b200_logprob_bwd_rows(_lib.ptr(dz), _c_int(e - s), _c_int(V), _c_int(dz.stride(0)),
+                                             _lib.ptr(labels[s:e]), _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]),
+                                             _c_f(inv_t), _lib.stream_ptr())
+                _lib.check_rc(rc, "logprob_bwd_rows")
+            gemm(dz, w, b_mn=True, out=dh[s:e])
+            gemm(dz, h[s:e], a_mn=True, b_mn=True, out=dw_buf, accumulate=True)
         return dh, (None if mg is not None else dw_buf.to(w.dtype)), None, None, None, None
 
 

@@ -1,8 +1,9 @@
 """Tensor-parallel linear layers whose collective is fused into the GEMM kernel (rollout engine, TP > 1).
 
 * ``row_parallel``: o_proj / down_proj. Each rank multiplies its K-slice; the GEMM epilogue adds every output tile
-  into the fp32 accumulation buffer of *all* TP ranks with ``red.add`` over NVLink, so when the flag barrier that
-  follows has passed, every rank holds the all-reduced result (vLLM runs a GEMM and then a custom all-reduce:
+  into the fp32 accumulation buffer of *all* TP ranks with 16-byte ``red.add`` over NVLink, so when the flag barrier
+  that follows has passed, every rank holds the all-reduced result. ``row_parallel_scatter`` is the reduce-scatter
+  form: a tile goes only to the rank that owns its rows (vLLM runs a GEMM and then a custom all-reduce:
   the reference reaches it through ``--vllm.tensor_parallel_size``, openrlhf/trainer/ray/vllm_engine.py:270).
 * ``column_parallel_gathered``: qkv / gate_up with sequence-parallel input. The activation rows live sharded over
   the ranks in a symmetric buffer; the A-tile TMA loads of the GEMM fetch each row block from its owner.
@@ -72,6 +73,27 @@ class TPContext:
         _lib.check_rc(rc, "gemm_tp_push")
         self.barrier(3)                          # all pushes have landed everywhere
         return self.acc[b][: M * N].view(M, N)
+
+    def row_parallel_scatter(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Reduce-scatter form of row_parallel: x [M, K_local], w [N, K_local] -> fp32 [M / tp, N], this rank's rows of
+        sum over TP ranks of x @ w.T. Each output tile crosses NVLink once, to the owner of its rows only; feed the
+        result (after the norm) to column_parallel_gathered, which reads the row shards from their owners."""
+        M, K = x.shape
+        N = w.shape[0]
+        assert M % self.tp == 0 and (M // self.tp) * N <= self.max_rows * self.max_cols
+        rows = M // self.tp
+        b = self.cur
+        self.cur ^= 1
+        self.acc[self.cur][: min(M * N, self.max_rows * self.max_cols)].zero_()   # whatever form the next call has
+        self.barrier(2)
+        rc = _lib.lib().b200_gemm_bf16_tp(
+            _lib.ptr(x), None, _lib.ptr(w), None, self.acc_ptrs[b], None, ctypes.c_int(M), ctypes.c_int(N),
+            ctypes.c_int(K), ctypes.c_int(x.stride(0)), ctypes.c_int(w.stride(0)), ctypes.c_int(N),
+            ctypes.c_int(self.tp), ctypes.c_int(rows), ctypes.c_int(2), ctypes.c_int(0),
+            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, "gemm_tp_reduce_scatter")
+        self.barrier(3)
+        return self.acc[b][: rows * N].view(rows, N)
 
     def column_parallel_gathered(self, x_shard: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None):
         """x_shard [M/tp, K] (this rank's rows), w [N_local, K] -> bf16 [M, N_local] over the gathered rows."""

@@ -366,7 +366,13 @@ class RolloutEngine:
                         deltas[k_] = mrope_positions(t, grids, cfg.image_token_id, merge, cfg.video_token_id)[1]
             for d, (_, _, row) in zip(deltas, items):
                 self.rope_delta[row] = d
-        h, _ = m(ids, pos, cu, max(new_lens), attn_fn=attn_fn, inputs_embeds=embeds)
+        # ranks prefill independently of each other: expert-parallel dispatch (a collective of the training passes) is
+        # off here, every rank runs all experts of its own copy of the weights
+        ep_saved, m.ep = m.ep, None
+        try:
+            h, _ = m(ids, pos, cu, max(new_lens), attn_fn=attn_fn, inputs_embeds=embeds)
+        finally:
+            m.ep = ep_saved
         m.train(was_training)
         last = (cu[1:] - 1).long()
         self.stats["prefill_tokens"] += int(cu_new[-1])

@@ -50,12 +50,13 @@ def build_trainable(strategy, path: str, node: SimpleNamespace, *, device, max_s
 
         lm = shard_for_training(lm, strategy.mesh.group("tp"), shard_world=zw)
         source = ("tp_train", lm)
+    ep_range = strategy.attach_expert_parallel(lm, strategy.ep_max_tokens())
     opt = dict(lr=node.adam.lr, betas=tuple(node.adam.betas), eps=node.adam.eps, weight_decay=node.adam.weight_decay,
                max_norm=getattr(node, "max_norm", 1.0), group=strategy.zero_group(), scheduler=_scheduler(node, max_steps))
     if z3:
         from ..parallel.zero3 import Zero3Engine
 
-        engine = Zero3Engine(lm, **opt)
+        engine = Zero3Engine(lm, expert_range=ep_range, **opt)
         source = ("zero3", engine)
     else:
         engine = ZeroEngine(lm, zero_stage=int(strategy.stage), use_symm=False if tp_train else use_symm,
@@ -82,7 +83,10 @@ def build_frozen(strategy, path: str, *, device, seed: int, with_lm_head: bool =
     elif use_zero3(strategy):
         from ..parallel.zero3 import Zero3Engine
 
-        Zero3Engine(lm, group=strategy.zero_group(), train=False)      # attaches itself as lm.z3
+        ep_range = strategy.attach_expert_parallel(lm, strategy.ep_max_tokens())
+        Zero3Engine(lm, group=strategy.zero_group(), train=False, expert_range=ep_range)   # attaches itself as lm.z3
+    else:
+        strategy.attach_expert_parallel(lm, strategy.ep_max_tokens())
     return lm
 
 

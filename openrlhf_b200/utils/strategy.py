@@ -141,6 +141,8 @@ class Strategy:
         self.ring_attn_size = int(getattr(ds, "ring_attn_size", 1) or 1)
         self.ds_tensor_parallel_size = int(getattr(ds, "tensor_parallel_size", 1) or 1)
         self.adam_offload = getattr(ds, "adam_offload", False)
+        self.expert_parallel_size = int(getattr(ds, "expert_parallel_size", 1) or 1)
+        self._ep_group = None
         self.use_dynamic_batch = bool(getattr(getattr(args, "train", SimpleNamespace()), "dynamic_batch_enable", False)) \
             if args is not None else False
         self.is_rlhf = False
@@ -167,6 +169,19 @@ class Strategy:
         self.mesh = RankMesh(self.world_size, self.ring_attn_size, self.ds_tensor_parallel_size, self.rank)
         for dim in ("dp", "sp", "tp") + (("zero",) if self.ring_attn_size > 1 else ()):
             self.mesh.group(dim)
+        ep = self.expert_parallel_size
+        if ep > 1:
+            if self.ring_attn_size > 1 or self.ds_tensor_parallel_size > 1:
+                raise ValueError("--ds.expert_parallel_size is combined with data parallelism only (no ring attention "
+                                 "or tensor-parallel training in the same run)")
+            if self.world_size % ep:
+                raise ValueError(f"--ds.expert_parallel_size {ep} does not divide the {self.world_size} ranks")
+            if self.world_size > 1 and dist.is_initialized():
+                for k in range(self.world_size // ep):          # collective: every rank creates every group
+                    ranks = list(range(k * ep, (k + 1) * ep))
+                    g = dist.new_group(ranks)
+                    if self.rank in ranks:
+                        self._ep_group = g
         dp = self.mesh.dp
         self.accumulated_gradient = max(1, self.train_batch_size * self.ring_attn_size * self.ds_tensor_parallel_size
                                         // max(self.micro_train_batch_size, 1) // max(self.world_size, 1))
@@ -186,6 +201,36 @@ class Strategy:
 
     def dp_group(self):
         return self.mesh.group("dp")
+
+    def ep_group(self):
+        """Process group over which the experts of MoE layers are split (None: no expert parallelism)."""
+        return self._ep_group if self.expert_parallel_size > 1 else None
+
+    def attach_expert_parallel(self, lm, max_tokens: int):
+        """Give a mixture-of-experts model its expert-parallel context (GPU ranks; CPU ranks keep all experts local).
+        Returns the expert range this rank computes, or None."""
+        g = self.ep_group()
+        cfg = lm.cfg
+        if g is None or not getattr(cfg, "num_experts", 0) or lm.flat.device.type != "cuda":
+            return None
+        from ..parallel.ep import EPContext
+
+        if cfg.num_experts % self.expert_parallel_size:
+            raise ValueError(f"{cfg.num_experts} experts are not divisible by --ds.expert_parallel_size "
+                             f"{self.expert_parallel_size}")
+        lm.ep = EPContext(g, max_tokens, cfg.num_experts_per_tok, cfg.hidden_size, cfg.num_experts, lm.flat.device)
+        return lm.ep.rank * lm.ep.E_loc, (lm.ep.rank + 1) * lm.ep.E_loc
+
+    def ep_max_tokens(self) -> int:
+        """Upper bound on the packed tokens of one forward pass on a rank (sizes the dispatch buffers)."""
+        a = self.args
+        tr = getattr(a, "train", SimpleNamespace())
+        ro = getattr(a, "rollout", SimpleNamespace())
+        max_len = int(getattr(getattr(a, "data", SimpleNamespace()), "max_len", 2048) or 2048)
+        if getattr(tr, "dynamic_batch_enable", False):
+            return int(max(getattr(tr, "max_tokens_per_gpu", 16192), getattr(ro, "max_tokens_per_gpu", 0) or 0))
+        mb = max(int(getattr(tr, "micro_batch_size", 1) or 1), int(getattr(ro, "micro_batch_size", 1) or 1))
+        return mb * max_len
 
     def zero_group(self):
         """Ranks over which gradients are averaged and ZeRO state is sharded (dp x ring-attention members)."""
@@ -227,6 +272,7 @@ class Strategy:
                 if tp > 1:
                     module = tp_shard(module)
                 lm = _inner_lm(module)
+                ep_range = self.attach_expert_parallel(lm, self.ep_max_tokens())
                 sched = LRScheduler(cfg.get("lr", 1e-6), cfg.get("max_steps", 1000), cfg.get("lr_warmup_ratio", 0.03),
                                     cfg.get("min_lr_ratio", 0.1), cfg.get("lr_scheduler", "cosine_with_min_lr"))
                 if cfg.get("optim", "adam") == "muon":
@@ -246,7 +292,8 @@ class Strategy:
                                          "adapters; use stage 2 for those runs")
                     eng = Zero3Engine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                       eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),
-                                      max_norm=self.max_norm, group=self.zero_group(), scheduler=sched)
+                                      max_norm=self.max_norm, group=self.zero_group(), scheduler=sched,
+                                      expert_range=ep_range)
                 else:
                     eng = ZeroEngine(lm, lr=cfg.get("lr", 1e-6), betas=tuple(cfg.get("betas", (0.9, 0.95))),
                                      eps=cfg.get("eps", 1e-8), weight_decay=cfg.get("weight_decay", 0.0),

@@ -30,8 +30,16 @@ def main():
         _lib.check_status(dev)
         err = (out - ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item(), f"row-parallel iter {it}: err {err}"
-    ns = N // tp
     rows = M // tp
+    for it in range(3):                                     # reduce-scatter form: this rank's rows of the same sum
+        out = ctx.row_parallel_scatter(x[:, rank * ks:(rank + 1) * ks].contiguous(),
+                                       w[:, rank * ks:(rank + 1) * ks].contiguous())
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        want = ref[rank * rows:(rank + 1) * rows]
+        err = (out - want).abs().max().item()
+        assert out.shape == want.shape and err <= 2e-2 * ref.abs().max().item(), f"reduce-scatter iter {it}: err {err}"
+    ns = N // tp
     bias = torch.randn(ns, generator=g, device=dev).to(torch.bfloat16)
     for it in range(2):
         out = ctx.column_parallel_gathered(x[rank * rows:(rank + 1) * rows].contiguous(),

@@ -87,6 +87,32 @@ def test_fused_logprob_fwd_bwd():
     _close(h.grad, hr.grad, rtol=4e-2, atol=4e-2); _close(w.grad, wr.grad, rtol=4e-2, atol=4e-2)
 
 
+@pytest.mark.parametrize("T,H,V,temp", [(130, 256, 5000, 1.0), (1, 128, 264, 0.5), (257, 320, 1000, 1.3)])
+def test_fused_logprob_ragged_vocabulary_and_edge_labels(T, H, V, temp):
+    """Vocabulary sizes that are not multiples of the 256-column tile (the last tile is partly outside), token counts
+    that are not multiples of 128 and labels on the first / last column, against the fp32 PyTorch computation."""
+    from openrlhf_b200.ops import functional as F
+    torch.manual_seed(1)
+    h = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.08 * torch.randn(V, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = torch.randint(0, V, (T,), device="cuda")
+    y[0] = V - 1
+    y[-1] = 0
+    logp, ent = F.fused_logprob(h, w, y, temperature=temp, want_entropy=True, chunk=128)
+    g = torch.randn(T, device="cuda")
+    logp.backward(g)
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logits = hr @ wr.t()
+    lr = torch.log_softmax(logits / temp, -1).gather(-1, y[:, None]).squeeze(-1)
+    p = torch.softmax(logits, -1); er = torch.logsumexp(logits, -1) - (p * logits).sum(-1)
+    lr.backward(g)
+    _close(logp, lr, atol=3e-2); _close(ent, er, atol=3e-2)
+    _close(h.grad, hr.grad, rtol=4e-2, atol=4e-2); _close(w.grad, wr.grad, rtol=4e-2, atol=4e-2)
+    logp2, none = F.fused_logprob(h.detach(), w.detach(), y, temperature=temp, want_entropy=False)
+    assert none is None
+    _close(logp2, lr.detach(), atol=3e-2)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,splits", [(3, 12, 2, 1), (5, 32, 8, 1), (4, 28, 4, 3), (2, 16, 2, 2)])
 def test_paged_decode(B, Hq, Hkv, splits):
     from openrlhf_b200.ops import _lib, reference as R
