@@ -69,7 +69,7 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob",
+    ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob", "logprob_bwd",
                                                          "rmsnorm", "adamw"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
@@ -132,6 +132,26 @@ def main():
         byt = 2.0 * (M * K + N * K + M * N)
         print(f"{a.kernel} M{M} N{N} K{K} {a.layout} bn{a.bn} splits{a.splits}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s "
               f"({fl / t / 1e12 / tf:.2f} {tag} bf16 peak), {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+        if a.kernel == "gemm":
+            import openrlhf_b200.ops.gemm as G
+
+            G.PAIR_KERNEL = "1"                      # the same GEMM on CTA pairs (tcgen05.mma.cta_group::2)
+            if G._use_pair_kernel(M, N, K, 1, 0, a.bn):
+                ref = gemm(A, B, a_mn=a_mn, b_mn=b_mn, bn=a.bn).float()
+                G.PAIR_KERNEL = "0"
+                one = gemm(A, B, a_mn=a_mn, b_mn=b_mn, bn=a.bn).float()
+                G.PAIR_KERNEL = "1"
+                err = (ref - one).abs().max().item()
+                t2 = _time(fn, a.iters)
+                print(f"cta_group::2 kernel: {t2 * 1e6:.1f} us, {fl / t2 / 1e12:.0f} TFLOP/s ({fl / t2 / 1e12 / tf:.2f} {tag} "
+                      f"bf16 peak), max |diff| vs single-CTA kernel {err:.3g}")
+            G.PAIR_KERNEL = "0"
+            # the library GEMM on the same operands, same process, same timing loop
+            At, Bt = (A.t() if a_mn else A), (B if b_mn else B.t())
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            tl = _time(lambda: torch.matmul(At, Bt, out=out), a.iters)
+            print(f"torch.matmul same operands: {tl * 1e6:.1f} us, {fl / tl / 1e12:.0f} TFLOP/s; this kernel / library "
+                  f"= {tl / t:.2f}x")
     elif a.kernel == "decode_attn":
         B_, Hq, Hkv, ctx = a.batch, a.hq, a.hkv, a.ctx
         per = ctx // 128 + 1
@@ -176,6 +196,22 @@ def main():
             t = _time(lambda: F.fused_logprob(h, w, y), a.iters)
         fl = 2.0 * T * V * H
         print(f"logprob T{T} V{V} H{H}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s ({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
+    elif a.kernel == "logprob_bwd":
+        T, V, H = a.m, a.n, a.k
+        h = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = (0.02 * torch.randn(V, H, device=dev)).to(torch.bfloat16).requires_grad_()
+        w.main_grad = torch.zeros(V, H, device=dev, dtype=torch.float32)
+        y = torch.randint(0, V, (T,), device=dev)
+        g = torch.randn(T, device=dev)
+
+        def step():
+            lp, _ = F.fused_logprob(h, w, y)
+            lp.backward(g)
+            h.grad = None
+
+        t = _time(step, a.iters)
+        fl = 8.0 * T * V * H              # forward, recomputation, dH and dW GEMMs
+        print(f"logprob fwd+bwd T{T} V{V} H{H}: {t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s ({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
     elif a.kernel == "rmsnorm":
         T, H = a.m, a.k
         x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)

@@ -6,6 +6,7 @@ place of ``nn.Linear`` (the reference's projections are HF ``nn.Linear`` modules
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -63,6 +64,16 @@ def gemm(
         assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and not out_f32
         assert residual.stride(0) == out.stride(0)
     st = _lib.status_word(a.device)
+    if _use_pair_kernel(M, N, K, k_splits, split_stride, bn):
+        rc = _lib.lib().b200_gemm2_bf16(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual),
+            ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+            ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(out_f32)),
+            ctypes.c_int(int(accumulate)), ctypes.c_int(int(k_splits)), ctypes.c_float(alpha), ctypes.c_int(256),
+            _lib.ptr(st), _lib.stream_ptr())
+        _lib.check_rc(rc, "b200_gemm2_bf16")
+        return out
     rc = _lib.lib().b200_gemm_bf16(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
@@ -74,6 +85,17 @@ def gemm(
     )
     _lib.check_rc(rc, "b200_gemm_bf16")
     return out
+
+
+PAIR_KERNEL = os.environ.get("OPENRLHF_B200_GEMM2", "1")      # "0": keep every GEMM on the single-CTA kernel
+
+
+def _use_pair_kernel(M: int, N: int, K: int, k_splits: int, split_stride: int, bn: int) -> bool:
+    """The CTA-pair kernel (csrc/gemm2_tcgen05.cu) takes the large training / prefill GEMMs: at least one 256-row
+    tile pair per cluster slot, no split-K slabs, caller did not ask for a specific tile width."""
+    if PAIR_KERNEL != "1" or split_stride or bn not in (0, 256):
+        return False
+    return M >= 1024 and N >= 256 and K >= 256 and ((M + 255) // 256) * ((N + 255) // 256) * max(k_splits, 1) >= 74
 
 
 def gemm_swiglu(x: torch.Tensor, w: torch.Tensor, want_gate_up: bool = False, bn: int = 0):

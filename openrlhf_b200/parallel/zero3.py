@@ -106,7 +106,7 @@ class Zero3Engine:
             self.pad.zero_()
             self._hs = symm_mem.rendezvous(self.pad, self.group)
             self.pad_ptrs = _ptr_array(self._hs.buffer_ptrs)
-            self.bar_epoch = 0
+            self.bar_epochs = [0, 0]
         else:
             self.param_shard = torch.empty(self.per, dtype=full.dtype, device=self.device)
             self.grad_work = torch.zeros(self.work_size, dtype=torch.float32, device=self.device) if train else None
@@ -147,18 +147,23 @@ class Zero3Engine:
         self._tmp = torch.empty(min(self.per, _round(slot, 256)) if train else 0, dtype=torch.float32,
                                 device=self.device)
         self._pending_zero = -1
+        self._rs_stream = None                    # side stream of the per-layer gradient reductions
+        self._slot_reduced = [None, None]         # event: the gradient slot has been reduced and cleared
         self._sync()
         self.gather_resident()
 
     # ------------------------------------------------------------------------------------------------ plumbing
-    def _sync(self):
-        """All ranks' parameter slices (or gradient slots) are in a consistent state."""
+    def _sync(self, channel: int = 0):
+        """All ranks' parameter slices (or gradient slots) are in a consistent state. Barriers issued on the side
+        stream of the gradient reductions use their own flag channel and epoch counter: they may execute out of order
+        with the compute stream's barriers, and one channel's epochs must only ever grow."""
         if self.world == 1:
             return
         if self.on_gpu:
-            self.bar_epoch += 1
+            self.bar_epochs[channel] += 1
             rc = _lib.lib().b200_symm_barrier(self.pad_ptrs, ctypes.c_int(self.rank), ctypes.c_int(self.world),
-                                              ctypes.c_int(0), ctypes.c_uint(self.bar_epoch), ctypes.c_double(60.0),
+                                              ctypes.c_int(channel), ctypes.c_uint(self.bar_epochs[channel]),
+                                              ctypes.c_double(60.0),
                                               _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
             _lib.check_rc(rc, "symm_barrier")
         else:
@@ -278,6 +283,12 @@ class Zero3Engine:
 
     def pre_backward_hook(self, i: int):
         def hook(grad):
+            ev = self._slot_reduced[i % 2]
+            if ev is not None:
+                # layer i's weight gradients go into the gradient slot that layer i + 2 used: its reduction (which ran
+                # on the side stream under layer i + 1's backward pass) must have emptied the slot
+                torch.cuda.current_stream(self.device).wait_event(ev)
+                self._slot_reduced[i % 2] = None
             self.gather_layer(i)
             if i > 0:
                 self._start_gather(i - 1)      # prefetch for the next layer of the backward pass
@@ -291,19 +302,41 @@ class Zero3Engine:
         return hook
 
     def _layer_backward_done(self, i: int):
+        """Layer i's weight gradients are complete on this rank: reduce them into the owners' gradient slices and empty
+        the slot. With more than one rank this runs on a side stream, under the backward pass of layer i - 1:
+        barrier (every rank finished layer i) -> pull-reduce -> barrier (every rank finished pulling) -> clear."""
         if not self.on_gpu:
             return                                     # CPU ranks reduce after loss.backward() (see backward)
         a, b = self.layer_rng[i]
-        self._sync()                                   # every rank has finished layer i's backward
-        self._reduce_range(a, b, self.slot_base[i % 2])
-        # the slot reduced one layer earlier is free now: all ranks passed the barrier above after pulling from it
-        if self._pending_zero >= 0:
-            s = self.slot_base[self._pending_zero]
-            self.grad_work[s:s + (self.slot_base[1] - self.slot_base[0])].zero_()
-        self._pending_zero = i % 2
+        slot = self.slot_base[i % 2]
+        width = self.slot_base[1] - self.slot_base[0]
+        if self.world == 1:
+            self._reduce_range(a, b, slot)
+            self.grad_work[slot:slot + width].zero_()
+            return
+        if self._rs_stream is None:
+            self._rs_stream = torch.cuda.Stream(device=self.device)
+        cur = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        with torch.cuda.stream(self._rs_stream):
+            self._rs_stream.wait_event(ready)
+            self._sync(1)
+            self._reduce_range(a, b, slot)
+            self._sync(1)
+            self.grad_work[slot:slot + width].zero_()
+            done = torch.cuda.Event()
+            done.record(self._rs_stream)
+        self._slot_reduced[i % 2] = done
 
     def _finish_backward(self):
-        """Resident parameters' gradients, and the last layer slot."""
+        """Resident parameters' gradients; joins the per-layer reductions still running on the side stream."""
+        if self.on_gpu:
+            cur = torch.cuda.current_stream(self.device)
+            for k in (0, 1):
+                if self._slot_reduced[k] is not None:
+                    cur.wait_event(self._slot_reduced[k])
+                    self._slot_reduced[k] = None
         self._sync()
         for s in self.model.specs:
             if s.name in self.res_map:

@@ -30,6 +30,11 @@ from ..ops.sampling import sample
 from .block_manager import BlockManager
 
 
+import os as _os
+
+_DEBUG = _os.environ.get("OPENRLHF_B200_DEBUG", "0") == "1"
+
+
 @dataclass
 class SamplingParams:
     temperature: float = 1.0
@@ -897,7 +902,39 @@ class RolloutEngine:
                     del self._req[r.request_id]
         if self.on_gpu:
             _lib.check_status(self.device)
+        if _DEBUG:
+            self.check_invariants()
         return finished
+
+    def check_invariants(self):
+        """Debug check of the scheduler's bookkeeping against the device state (``OPENRLHF_B200_DEBUG=1`` runs it after
+        every step): every page of a live row is inside the pool and owned only by rows that share it on purpose, the
+        device block table of a decoding row equals the host's, its write slot lies in its own pages, and inactive
+        rows write to the dummy page. Raises AssertionError with the offending row."""
+        owners: dict[int, list] = {}
+        for i, r in enumerate(self.rows):
+            if r is None:
+                continue
+            assert len(set(r.pages)) == len(r.pages), f"row {i} holds a page twice: {r.pages}"
+            for idx, pg in enumerate(r.pages):
+                assert 0 < pg < self.num_pages, f"row {i} holds page {pg} outside the pool"
+                owners.setdefault(pg, []).append((i, idx))
+        for pg, own in owners.items():
+            if len(own) > 1:
+                assert len({idx for _, idx in own}) == 1 and len({self.rows[i].request_id for i, _ in own}) == 1 \
+                    or pg in self._cache_hash, f"page {pg} is held by unrelated rows {own}"
+        bt = self.block_table.cpu()
+        slots, pos, act = self.slots.cpu(), self.pos.cpu(), self.active.cpu()
+        hold = {r for _, rows, _ in self._prefilling for r in rows}
+        for i, r in enumerate(self.rows):
+            decoding = r is not None and i not in hold and r.prefilled < 0
+            if decoding and int(act[i]):
+                assert bt[i, : len(r.pages)].tolist() == r.pages, f"row {i}: device block table differs from the host's"
+                assert int(slots[i]) // PAGE == r.pages[int(pos[i]) // PAGE], f"row {i}: write slot outside its pages"
+            elif not decoding and not self._table_dirty and not self._stale_rows:
+                assert int(slots[i]) // PAGE == self.dummy_page or r is not None, \
+                    f"inactive row {i} writes to page {int(slots[i]) // PAGE}"
+        return True
 
     @torch.no_grad()
     def generate(self, prompt_token_ids: list[list[int]], sampling_params: SamplingParams | list[SamplingParams],

@@ -121,3 +121,69 @@ def test_gemm_swiglu_epilogue(M, I, K, bn):
     _lib.check_status()
     assert (xa.grad.float() - xb.grad.float()).abs().max().item() <= 0.02 * xb.grad.float().abs().max().item()
     assert (wa.grad.float() - wb.grad.float()).abs().max().item() <= 0.02 * wb.grad.float().abs().max().item()
+
+
+def _gemm2(a, b, *, a_mn=False, b_mn=False, bias=None, residual=None, out=None, accumulate=False, k_splits=1, bn=256):
+    """The CTA-pair kernel through its C symbol (ops.gemm only routes large shapes to it)."""
+    import ctypes
+
+    from openrlhf_b200.ops import _lib
+
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=torch.bfloat16)
+    f32 = out.dtype == torch.float32
+    rc = _lib.lib().b200_gemm2_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual), ctypes.c_int(M), ctypes.c_int(N),
+        ctypes.c_int(K), ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_int(int(f32)), ctypes.c_int(int(accumulate)),
+        ctypes.c_int(k_splits), ctypes.c_float(1.0), ctypes.c_int(bn), _lib.ptr(_lib.status_word(a.device)),
+        _lib.stream_ptr())
+    assert rc == 0, rc
+    return out
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K,bn", [(256, 256, 64, 256), (512, 768, 256, 256), (1000, 1536, 1544, 256),
+                                      (2048, 1024, 512, 128), (4096, 2304, 1536, 256), (136, 264, 72, 128)])
+def test_gemm_cta_pair_layouts(a_mn, b_mn, M, N, K, bn):
+    """tcgen05.mma.cta_group::2 kernel (two CTAs per 256-row tile) against fp32 PyTorch: all operand layouts, ragged
+    M / N / K tails (the odd CTA of the last pair may hold no valid row at all), one and many tiles per pair."""
+    from openrlhf_b200.ops import _lib
+
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    out = _gemm2(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, f"max err {err} (scale {scale})"
+
+
+def test_gemm_cta_pair_epilogues():
+    from openrlhf_b200.ops import _lib
+
+    torch.manual_seed(3)
+    M, N, K = 768, 640, 320
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = _gemm2(a, b, bias=bias, residual=res)
+    ref = a.float() @ b.float().t() + bias.float() + res.float()
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    # weight-gradient form: fp32 accumulation into an existing buffer, split along the token dimension
+    T, Nw, Kw = 4096, 512, 384
+    dy = torch.randn(T, Nw, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(T, Kw, device="cuda", dtype=torch.bfloat16)
+    grad = torch.ones(Nw, Kw, device="cuda", dtype=torch.float32)
+    _gemm2(dy, x, a_mn=True, b_mn=True, out=grad, accumulate=True, k_splits=4)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    want = 1.0 + dy.float().t() @ x.float()
+    assert (grad - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-2

@@ -8,6 +8,14 @@ from openrlhf_b200.models.transformer import TransformerLM
 from openrlhf_b200.rollout.engine import RolloutEngine, SamplingParams
 
 
+@pytest.fixture(autouse=True)
+def _invariant_checks(monkeypatch):
+    """Every engine step of these tests re-checks the page / slot bookkeeping against the device state."""
+    import openrlhf_b200.rollout.engine as E
+
+    monkeypatch.setattr(E, "_DEBUG", True)
+
+
 @pytest.fixture(scope="module")
 def model():
     return TransformerLM(ModelConfig.from_pretrained("tiny-qwen2"), device="cpu", dtype=torch.float32, seed=0)
