@@ -112,6 +112,20 @@ def main():
         x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         w = torch.randn(2 * I, K, device=dev, dtype=torch.bfloat16)
         fl = 2.0 * M * 2 * I * K
+        import openrlhf_b200.ops.gemm as G
+
+        ref_y = None
+        for pair in ("0", "1"):
+            G.PAIR_KERNEL = pair
+            yy, gg = gemm_swiglu(x, w, want_gate_up=True, bn=a.bn)
+            if ref_y is not None:
+                print(f"cta_group::2 vs single-CTA: max |dy| {(yy.float() - ref_y[0].float()).abs().max().item():.3g}, "
+                      f"max |d gate_up| {(gg.float() - ref_y[1].float()).abs().max().item():.3g}")
+            ref_y = (yy, gg)
+            t = _time(lambda: gemm_swiglu(x, w, want_gate_up=True, bn=a.bn), a.iters)
+            print(f"gemm_swiglu M{M} I{I} K{K} fused (y + gate_up), {'CTA pairs' if pair == '1' else 'single CTA'}: "
+                  f"{t * 1e6:.1f} us, {fl / t / 1e12:.0f} TFLOP/s ({fl / t / 1e12 / tf:.2f} {tag} bf16 peak)")
+        G.PAIR_KERNEL = "0"
         for name, fn in (("fused (y only)", lambda: gemm_swiglu(x, w, bn=a.bn)),
                          ("fused (y + gate_up)", lambda: gemm_swiglu(x, w, want_gate_up=True, bn=a.bn)),
                          ("gemm + swiglu kernel", lambda: F.swiglu(gemm(x, w, bn=a.bn)))):

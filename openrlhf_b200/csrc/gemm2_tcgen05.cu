@@ -43,6 +43,20 @@ struct Gemm2Params {
   int out_f32, accumulate, k_splits;
   float alpha;
   int* status;
+  // SwiGLU epilogue (K-major B = [gate rows | up rows], N = 2 * sw_half): the even CTA loads BN/2 gate rows, the odd
+  // CTA the BN/2 up rows of the same output columns, so accumulator columns [0, BN/2) are gate and [BN/2, BN) are up
+  // products; the epilogue writes silu(gate) * up to C[M, sw_half]; C2 (optional, [M, ldc2]) receives the bf16
+  // gate / up values for the backward pass.
+  int swiglu, sw_half;
+  __nv_bfloat16* C2;
+  int ldc2;
+  // LM-head backward recomputation: C receives d logits = g / T * (onehot(label) - exp(z / T - lse)) as bf16
+  // (z = the product, one row per token); see GemmParams::lp_mode in gemm_tcgen05.cu.
+  int lp_mode;
+  const long long* lp_labels;
+  float lp_inv_t;
+  const float* lp_lse;
+  const float* lp_dlogp;
 };
 
 template <int BN>
@@ -126,7 +140,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int pair = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
   const int m_pairs = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
-  const int n_blocks = (p.N + BN - 1) / BN;
+  const int n_blocks = p.swiglu ? (p.sw_half + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
   const int kb_total = (p.K + G2_BK - 1) / G2_BK;
   const int splits = p.k_splits > 1 ? p.k_splits : 1;
   const int kb_per_split = (kb_total + splits - 1) / splits;
@@ -180,7 +194,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         int mp, n_blk, kb0, kb1;
         tile_coords(tile, mp, n_blk, kb0, kb1);
         const int row0 = mp * 2 * G2_BM + (int)cta * G2_BM;
-        const int col0 = n_blk * BN + (int)cta * (BN / 2);
+        const int col0 = p.swiglu ? (int)cta * p.sw_half + n_blk * (BN / 2) : n_blk * BN + (int)cta * (BN / 2);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -244,6 +258,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const int quarter = warp & 3;
     const bool wide_c = !p.out_f32 && (p.ldc % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 31) == 0);
     const bool v4_ok = p.out_f32 && (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool wide_c2 = p.C2 != nullptr && (p.ldc2 % 16 == 0) && (p.sw_half % 16 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(p.C2) & 31) == 0);
     int local = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++local) {
@@ -258,6 +274,64 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool has_work = kb1 > kb0;
       const float alpha = p.alpha;
+      if (p.swiglu) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, g);
+          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          const int col0 = n_blk * (BN / 2) + c * 32;
+          if (row_ok && has_work && col0 < p.sw_half) {
+            __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 16) {
+              // sw_half is a multiple of BN / 2 >= 64: a 32-column chunk is never ragged
+              uint4 o[2], og[2], ou[2];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const int jj = j + 8 * hh;
+                float y[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const float gv = __uint_as_float(g[jj + q]);
+                  y[q] = gv / (1.f + __expf(-gv)) * __uint_as_float(u[jj + q]);
+                }
+                o[hh].x = pack_bf16x2(y[0], y[1]);
+                o[hh].y = pack_bf16x2(y[2], y[3]);
+                o[hh].z = pack_bf16x2(y[4], y[5]);
+                o[hh].w = pack_bf16x2(y[6], y[7]);
+                og[hh].x = pack_bf16x2(__uint_as_float(g[jj]), __uint_as_float(g[jj + 1]));
+                og[hh].y = pack_bf16x2(__uint_as_float(g[jj + 2]), __uint_as_float(g[jj + 3]));
+                og[hh].z = pack_bf16x2(__uint_as_float(g[jj + 4]), __uint_as_float(g[jj + 5]));
+                og[hh].w = pack_bf16x2(__uint_as_float(g[jj + 6]), __uint_as_float(g[jj + 7]));
+                ou[hh].x = pack_bf16x2(__uint_as_float(u[jj]), __uint_as_float(u[jj + 1]));
+                ou[hh].y = pack_bf16x2(__uint_as_float(u[jj + 2]), __uint_as_float(u[jj + 3]));
+                ou[hh].z = pack_bf16x2(__uint_as_float(u[jj + 4]), __uint_as_float(u[jj + 5]));
+                ou[hh].w = pack_bf16x2(__uint_as_float(u[jj + 6]), __uint_as_float(u[jj + 7]));
+              }
+              if (wide_c) {
+                st_global_256(yrow + j, o[0], o[1]);
+              } else {
+                *reinterpret_cast<uint4*>(yrow + j) = o[0];
+                *reinterpret_cast<uint4*>(yrow + j + 8) = o[1];
+              }
+              if (p.C2 != nullptr) {
+                __nv_bfloat16* grow = p.C2 + (size_t)row * p.ldc2 + col0 + j;
+                if (wide_c2) {
+                  st_global_256(grow, og[0], og[1]);
+                  st_global_256(grow + p.sw_half, ou[0], ou[1]);
+                } else {
+                  *reinterpret_cast<uint4*>(grow) = og[0];
+                  *reinterpret_cast<uint4*>(grow + 8) = og[1];
+                  *reinterpret_cast<uint4*>(grow + p.sw_half) = ou[0];
+                  *reinterpret_cast<uint4*>(grow + p.sw_half + 8) = ou[1];
+                }
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -292,6 +366,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                   float v[8];
 #pragma unroll
                   for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[jj + q]) * alpha;
+                  if (p.lp_mode == 2) {
+                    const float g = p.lp_dlogp[row] * p.lp_inv_t, lse = p.lp_lse[row];
+                    const long long label = p.lp_labels[row];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                      const float o_ = -g * __expf(v[q] * p.lp_inv_t - lse);
+                      v[q] = ((long long)(col0 + jj + q) == label) ? o_ + g : o_;
+                    }
+                  }
                   if (p.bias != nullptr) {
                     uint4 bb = *reinterpret_cast<const uint4*>(p.bias + col0 + jj);
                     const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
@@ -361,7 +444,8 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Para
   static std::atomic<unsigned long long> configured{0};      // one bit per device (per template instance)
   auto kern = gemm2_bf16_kernel<BN, A_MN, B_MN>;
   if (!set_max_smem_once(configured, kern, L::TOTAL)) return -2;
-  const int m_pairs = (p.M + 2 * G2_BM - 1) / (2 * G2_BM), n_blocks = (p.N + BN - 1) / BN;
+  const int m_pairs = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int n_blocks = p.swiglu ? (p.sw_half + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
   const int tiles = m_pairs * n_blocks * (p.k_splits > 1 ? p.k_splits : 1);
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
@@ -410,4 +494,63 @@ extern "C" int b200_gemm2_bf16(const void* A, const void* B, void* C, const void
   if (bn == 256) { B200_DISPATCH2(256) }
   B200_DISPATCH2(128)
 #undef B200_DISPATCH2
+}
+
+
+// Y[M, I] = silu(A W_gate^T) * (A W_up^T) with W = [gate rows | up rows] ([2I, K], K-major) on CTA pairs; GU (optional,
+// [M, ldgu]) receives the bf16 gate / up products for the backward pass. I must be a multiple of bn / 2.
+extern "C" int b200_gemm2_bf16_swiglu(const void* A, const void* W, void* Y, void* GU, int M, int I, int K, int lda,
+                                      int ldb, int ldy, int ldgu, int bn, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if (bn != 128 && bn != 256) bn = 256;
+  if ((lda % 8) || (ldb % 8) || (ldy % 8) || (I % (bn / 2)) || (GU != nullptr && (ldgu % 8))) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Y) |
+       reinterpret_cast<uintptr_t>(GU)) & 15) return -12;
+  if (g2_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g2_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16_2d(&ta, A, M, K, lda, G2_BM, G2_BK);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tb, W, 2 * I, K, ldb, bn / 2, G2_BK);
+  if (r) return r;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.C = Y;
+  p.M = M; p.N = 2 * I; p.K = K; p.ldc = ldy; p.k_splits = 1; p.alpha = 1.f; p.status = status;
+  p.swiglu = 1; p.sw_half = I;
+  p.C2 = reinterpret_cast<__nv_bfloat16*>(GU); p.ldc2 = ldgu;
+  if (bn == 256) return launch2<256, false, false>(ta, tb, p, g2_sm_count, stream);
+  return launch2<128, false, false>(ta, tb, p, g2_sm_count, stream);
+}
+
+
+// LM-head backward recomputation on CTA pairs: dlogits (bf16 [T, ldc]) = g / T * (onehot(label) - softmax(H W^T / T)).
+extern "C" int b200_lmhead2_dlogits(const void* H, const void* W, void* dlogits, const long long* labels,
+                                    const float* lse, const float* dlogp, float inv_t, int T, int V, int K, int ldh,
+                                    int ldw, int ldc, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (T <= 0 || V <= 0 || K <= 0) return 0;
+  if ((ldh % 8) || (ldw % 8) || (ldc % 8) || (V % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(H) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(dlogits)) & 15)
+    return -12;
+  if (g2_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g2_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16_2d(&ta, H, T, K, ldh, G2_BM, G2_BK);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tb, W, V, K, ldw, 128, G2_BK);
+  if (r) return r;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.C = dlogits;
+  p.M = T; p.N = V; p.K = K; p.ldc = ldc; p.k_splits = 1; p.alpha = 1.f; p.status = status;
+  p.lp_mode = 2; p.lp_labels = labels; p.lp_inv_t = inv_t; p.lp_lse = lse; p.lp_dlogp = dlogp;
+  return launch2<256, false, false>(ta, tb, p, g2_sm_count, stream);
 }

@@ -350,10 +350,13 @@ class _FusedLogprob(torch.autograd.Function):
             e = min(T, s + ctx.chunk)
             if ctx.fused:
                 dz = torch.empty(e - s, V, dtype=torch.bfloat16, device=h.device)
-                rc = L.b200_lmhead_dlogits(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(dz), _lib.ptr(labels[s:e]),
-                                           _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]), _c_f(inv_t), _c_int(e - s),
-                                           _c_int(V), _c_int(K), _c_int(h.stride(0)), _c_int(w.stride(0)), _c_int(V),
-                                           _lib.ptr(st), _lib.stream_ptr())
+                from .gemm import PAIR_KERNEL
+                # CTA-pair kernel when the chunk has enough 256-row tiles to fill the GPU
+                fn = L.b200_lmhead2_dlogits if (PAIR_KERNEL == "1" and e - s >= 1024) else L.b200_lmhead_dlogits
+                rc = fn(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(dz), _lib.ptr(labels[s:e]),
+                        _lib.ptr(lse[s:e]), _lib.ptr(dlogp[s:e]), _c_f(inv_t), _c_int(e - s),
+                        _c_int(V), _c_int(K), _c_int(h.stride(0)), _c_int(w.stride(0)), _c_int(V),
+                        _lib.ptr(st), _lib.stream_ptr())
                 _lib.check_rc(rc, "lmhead_dlogits")
             else:
                 dz = gemm(h[s:e], w)

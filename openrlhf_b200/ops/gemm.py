@@ -111,6 +111,13 @@ def gemm_swiglu(x: torch.Tensor, w: torch.Tensor, want_gate_up: bool = False, bn
     if M == 0:
         return y, gu
     st = _lib.status_word(x.device)
+    if PAIR_KERNEL == "1" and bn in (0, 256) and M >= 1024 and ((M + 255) // 256) * (I // 128) >= 74:
+        rc = _lib.lib().b200_gemm2_bf16_swiglu(
+            _lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(gu), ctypes.c_int(M), ctypes.c_int(I), ctypes.c_int(K),
+            ctypes.c_int(x.stride(0)), ctypes.c_int(w.stride(0)), ctypes.c_int(I), ctypes.c_int(2 * I),
+            ctypes.c_int(256), _lib.ptr(st), _lib.stream_ptr())
+        _lib.check_rc(rc, "b200_gemm2_bf16_swiglu")
+        return y, gu
     rc = _lib.lib().b200_gemm_bf16_swiglu(
         _lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(gu), ctypes.c_int(M), ctypes.c_int(I), ctypes.c_int(K),
         ctypes.c_int(x.stride(0)), ctypes.c_int(w.stride(0)), ctypes.c_int(I), ctypes.c_int(2 * I), ctypes.c_int(bn),

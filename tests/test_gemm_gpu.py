@@ -91,7 +91,7 @@ def test_gemm_e4m3_matches_dequantised_reference(M, N, K):
 
 
 @pytest.mark.parametrize("M,I,K,bn", [(128, 8960, 1536, 128), (1000, 512, 256, 0), (4096, 1024, 1536, 256),
-                                      (37, 128, 72, 128), (10240, 8960, 1536, 0)])
+                                      (37, 128, 72, 128), (10240, 8960, 1536, 0), (2500, 2048, 264, 256), (2700, 1920, 512, 0)])
 def test_gemm_swiglu_epilogue(M, I, K, bn):
     """SwiGLU fused into the GEMM epilogue (two B boxes per stage) against fp32 PyTorch; the optional gate / up output
     and the autograd wrapper against the unfused composition."""

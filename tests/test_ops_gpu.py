@@ -87,8 +87,9 @@ def test_fused_logprob_fwd_bwd():
     _close(h.grad, hr.grad, rtol=4e-2, atol=4e-2); _close(w.grad, wr.grad, rtol=4e-2, atol=4e-2)
 
 
-@pytest.mark.parametrize("T,H,V,temp", [(130, 256, 5000, 1.0), (1, 128, 264, 0.5), (257, 320, 1000, 1.3)])
-def test_fused_logprob_ragged_vocabulary_and_edge_labels(T, H, V, temp):
+@pytest.mark.parametrize("T,H,V,temp,chunk", [(130, 256, 5000, 1.0, 128), (1, 128, 264, 0.5, 128),
+                                              (257, 320, 1000, 1.3, 128), (1300, 256, 5000, 0.9, 2048)])
+def test_fused_logprob_ragged_vocabulary_and_edge_labels(T, H, V, temp, chunk):
     """Vocabulary sizes that are not multiples of the 256-column tile (the last tile is partly outside), token counts
     that are not multiples of 128 and labels on the first / last column, against the fp32 PyTorch computation."""
     from openrlhf_b200.ops import functional as F
@@ -98,7 +99,7 @@ def test_fused_logprob_ragged_vocabulary_and_edge_labels(T, H, V, temp):
     y = torch.randint(0, V, (T,), device="cuda")
     y[0] = V - 1
     y[-1] = 0
-    logp, ent = F.fused_logprob(h, w, y, temperature=temp, want_entropy=True, chunk=128)
+    logp, ent = F.fused_logprob(h, w, y, temperature=temp, want_entropy=True, chunk=chunk)   # >= 1024: CTA pairs
     g = torch.randn(T, device="cuda")
     logp.backward(g)
     hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
