@@ -8,11 +8,15 @@ calls itself). Random-init weights, synthetic prompts (no network on the box).
 
 ``--config`` selects the workload (weak scaling: the per-GPU share is fixed):
 
-* ``qwen2.5-1.5b-reinforce`` (default): REINFORCE++-baseline on the Qwen2.5-1.5B architecture; every GPU runs 16 prompts
-  x 512 tokens, n = 8 responses x 2048 tokens (EOS ignored), rule reward, ZeRO-2, micro-batch 4 packed sequences: 128
-  prompts per step on 8 GPUs.
-* ``qwen2.5-7b-grpo``: GRPO (group-normalised advantages, k3 KL loss against a reference model) on the Qwen2.5-7B
-  architecture with ZeRO-3 for the policy and the reference model; 8 prompts x 512 tokens per GPU, n = 8 x 1024 tokens.
+* ``qwen2.5-7b-grpo`` (default): GRPO (group-normalised advantages, k3 KL loss against a reference model) on the
+  Qwen2.5-7B architecture with ZeRO-3 for the policy and the reference model; 8 prompts x 512 tokens per GPU, n = 8
+  responses x 1024 tokens (EOS ignored), rule reward; 512 samples per step on 8 GPUs. Every step gathers the ZeRO-3
+  parameter slices into the rollout engine's copy (the weight sync) and, on more than one GPU, runs the per-layer
+  gathers and gradient reductions over NVLink. Micro-batch 2 packed sequences on one GPU (which holds the whole
+  optimizer state), 8 once the state is sharded.
+* ``qwen2.5-1.5b-reinforce``: REINFORCE++-baseline on the Qwen2.5-1.5B architecture; every GPU runs 16 prompts x 512
+  tokens, n = 8 responses x 2048 tokens, rule reward, ZeRO-2, micro-batch 4 packed sequences: 128 prompts per step on 8
+  GPUs.
 * ``llama3-8b-ppo``: full PPO on the Llama-3-8B architecture: actor, critic, reference and reward model, GAE
   (gamma 1, lambda 0.95), ZeRO-3 for all four, rollout engines with tensor parallelism 2, weight sync from the ZeRO-3
   slices into the tensor-parallel shards every step; 32 prompts x 1024 tokens per GPU, one response x 1024 tokens
@@ -20,7 +24,8 @@ calls itself). Random-init weights, synthetic prompts (no network on the box).
 
 Prints one JSON line on rank 0. `value` is device-timed (CUDA events around the K steps, max over ranks) with the
 prompts already staged on the device; `e2e` times K further steps through the public API (`rl_step`) from pinned host
-prompts to the host-side loss, with a wall clock around a synchronize. After the default config, when time allows
+prompts to the host-side loss, with a wall clock around a synchronize (fewer than K steps, at least two, when K
+more would overrun ``BENCH_TIME_BUDGET_S``; ``e2e.steps`` says how many). After the default config, when time allows
 (``BENCH_TIME_BUDGET_S``), the other configs that fit the GPU count run for one short measurement each in child
 processes and are attached under ``extra_configs``.
 """
@@ -44,11 +49,12 @@ CONFIGS = {
                                    metric="RL-step samples/s (REINFORCE++-baseline hybrid engine, generation + "
                                           "experience + train + weight sync)"),
     "qwen2.5-7b-grpo": dict(model="qwen2.5-7b", prompts_per_gpu=8, prompt_len=512, n_samples=8, max_new=1024, micro=2,
+                            micro_sharded=8,     # micro-batch once the ZeRO-3 state is sharded (N >= 2): fewer gathers
                             estimator="group_norm", kl=0.001, kl_loss=True, zero_stage=3, rollout_tp=1, critic=False,
                             reward_model=False, min_gpus=1,
                             metric="RL-step samples/s (GRPO hybrid engine, ZeRO-3 policy + reference, generation + "
                                    "experience + train + weight sync)"),
-    "llama3-8b-ppo": dict(model="llama3-8b", prompts_per_gpu=32, prompt_len=1024, n_samples=1, max_new=1024, micro=2,
+    "llama3-8b-ppo": dict(model="llama3-8b", prompts_per_gpu=32, prompt_len=1024, n_samples=1, max_new=1024, micro=4,
                           estimator="gae", kl=0.01, zero_stage=3, rollout_tp=2, critic=True, reward_model=True,
                           min_gpus=8,
                           metric="RL-step samples/s (PPO with critic, reward and reference models, ZeRO-3, rollout "
@@ -62,7 +68,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="qwen2.5-1.5b-reinforce", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="qwen2.5-7b-grpo", choices=sorted(CONFIGS))
     ap.add_argument("--model", default=None, help="override the architecture preset of the config")
     ap.add_argument("--layers", type=int, default=None, help="cut the layer count (functional tests on few GPUs)")
     ap.add_argument("--prompts-per-gpu", type=int, default=None)
@@ -151,10 +157,11 @@ def run_extras(args, world: int, rank: int) -> dict:
     context; a failure or an overrun there cannot take the headline number with it). Skipped when the time budget of
     the whole bench (BENCH_TIME_BUDGET_S, default 800 s) does not leave room."""
     budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "800"))
-    est = {"qwen2.5-7b-grpo": 170.0, "llama3-8b-ppo": 230.0}
+    est = {"qwen2.5-7b-grpo": 150.0, "llama3-8b-ppo": 170.0, "qwen2.5-1.5b-reinforce": 100.0}
     out = {}
     port0 = int(os.environ.get("MASTER_PORT", "29500"))
-    for k, name in enumerate(n for n in ("llama3-8b-ppo", "qwen2.5-7b-grpo") if n != args.config):
+    for k, name in enumerate(n for n in ("llama3-8b-ppo", "qwen2.5-1.5b-reinforce", "qwen2.5-7b-grpo")
+                             if n != args.config):
         if world < CONFIGS[name]["min_gpus"]:
             out[name] = {"skipped": f"needs {CONFIGS[name]['min_gpus']} GPUs"}
             continue
@@ -209,6 +216,10 @@ def main():
                               "unavailable": f"this config needs {c['min_gpus']} GPUs (four 8B models under ZeRO-3)"}))
         return 0
     P, L, n, new = c["prompts_per_gpu"], c["prompt_len"], c["n_samples"], c["max_new"]
+    if world > 1 and args.micro is None and "micro_sharded" in c:
+        # one GPU holds the whole optimizer state and has room for small micro-batches only; the work per GPU and per
+        # optimizer step is the same, only the number of forward / backward passes it is cut into differs
+        c["micro"] = c["micro_sharded"]
     model = c["model"]
     if args.layers is not None:
         import dataclasses
@@ -274,10 +285,18 @@ def main():
     launches = _lib.LAUNCHES - launches0
     dev_s = e0.elapsed_time(e1) / 1e3
     # ---- end-to-end region: pinned host prompts in, host-side loss out, wall clock
+    # as many steps as the device-timed region, unless the time budget of the whole run would be exceeded (slow
+    # configs under a long --steps): then fewer, at least two, the same number on every rank
+    budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "800"))
+    fit = int((budget - (time.time() - T_START) - 15.0) / max(dev_s / args.steps, 1e-3))
+    e2e_steps = torch.tensor([max(min(2, args.steps), min(args.steps, fit))], device=f"cuda:{local}")
+    if world > 1:
+        dist.broadcast(e2e_steps, 0)
+    e2e_steps = int(e2e_steps)
     barrier()
     t0 = time.perf_counter()
     d2h = 0
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         st = worker.rl_step(next(it))
         loss = float(st["policy_loss"])  # host-side result of the step
         d2h += 8 * P * n * new + 4 * P * n * new + 4
@@ -315,13 +334,13 @@ def main():
                        "optimizer_step": opt, "worker": "runtime.workers.RLWorker (SPMD subclass HybridRLWorker)",
                        "l2": "working set (weights + KV cache) is larger than L2"},
             "clocks": clocks,
-            "e2e": {"value": samples / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": P * L * 8,
-                    "d2h_bytes_per_step": d2h // args.steps},
+            "e2e": {"value": P * n * world * e2e_steps / e2e_s, "unit": "samples/s", "steps": e2e_steps,
+                    "h2d_bytes_per_step": P * L * 8, "d2h_bytes_per_step": d2h // e2e_steps},
             "gpu_launches": launches,
             "impl": "b200",
         }
     # ---- release the GPU before the optional child runs
-    if args.extras == "auto" and args.config == "qwen2.5-1.5b-reinforce" and args.layers is None:
+    if args.extras == "auto" and args.config == "qwen2.5-7b-grpo" and args.layers is None and args.model is None:
         try:
             worker.rollout.sleep()
         except Exception:  # noqa: BLE001

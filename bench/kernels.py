@@ -25,6 +25,7 @@ def _peaks():
 
 FLUSH = True
 GRAPH = 0
+CHAIN = False
 
 
 def _time(fn, iters: int, flush: bool | None = None) -> float:
@@ -38,8 +39,11 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
             for _ in range(3):
                 fn()
         torch.cuda.current_stream().wait_stream(side)
+        import contextlib
+
+        from openrlhf_b200.ops import _lib
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g), (_lib.decode_chain() if CHAIN else contextlib.nullcontext()):
             for _ in range(GRAPH):
                 fn()
         g.replay()
@@ -70,7 +74,10 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob", "logprob_bwd",
-                                                         "rmsnorm", "adamw"])
+                                                         "rmsnorm", "adamw", "decode_step"])
+    ap.add_argument("--model", default="qwen2.5-1.5b", help="decode_step: model preset")
+    ap.add_argument("--layers", type=int, default=0, help="decode_step: cut the preset to this many layers (0: all)")
+    ap.add_argument("--no-pdl", action="store_true", help="decode_step: plain launches instead of the dependent-launch chain")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
     ap.add_argument("--k", type=int, default=1536)
@@ -84,10 +91,13 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--graph", type=int, default=0, help="time N back-to-back launches inside one CUDA graph")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed launches")
+    ap.add_argument("--chain", action="store_true",
+                    help="with --graph: record the launches as a programmatic-dependent-launch chain (decode loop)")
     a = ap.parse_args()
-    global FLUSH, GRAPH
+    global FLUSH, GRAPH, CHAIN
     FLUSH = not a.no_flush
     GRAPH = a.graph
+    CHAIN = a.chain
     from openrlhf_b200.ops import _lib
     from openrlhf_b200.ops import functional as F
     from openrlhf_b200.ops.attention import attn_bwd_tcgen05, attn_fwd_tcgen05, paged_decode
@@ -177,6 +187,51 @@ def main():
         byt = B_ * ctx * 2 * Hkv * 128 * 2
         print(f"decode_attn B{B_} Hq{Hq} Hkv{Hkv} ctx{ctx} splits{a.splits}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s "
               f"({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "decode_step":
+        # the rollout engine's whole decode step (CUDA graph of one token for `batch` sequences at context `ctx`),
+        # through the public engine API; host work of the scheduler is included, amortised over its 16-step bursts
+        import dataclasses
+
+        from openrlhf_b200.models.config import PRESETS
+        from openrlhf_b200.models.transformer import TransformerLM
+        from openrlhf_b200.rollout.engine import RolloutEngine, SamplingParams
+        cfg = dataclasses.replace(PRESETS[a.model])
+        if a.layers:
+            cfg.num_hidden_layers = a.layers
+        m = TransformerLM(cfg, device=dev, seed=0)
+        B, ctx, bursts = a.batch, a.ctx, max(2, a.iters)
+        chunks = (B * ctx + 16383) // 16384          # rows that finish their prefill early decode during the others'
+        new = 16 * (bursts + 8 + chunks)
+        eng = RolloutEngine(m, max_num_seqs=B, max_model_len=ctx + new + 128,
+                            num_pages=B * ((ctx + new) // 128 + 2) + 8, seed=1, decode_pdl=not a.no_pdl)
+        g = torch.Generator().manual_seed(0)
+        sp = SamplingParams(temperature=1.0, max_tokens=new, n=1, ignore_eos=True)
+        for i in range(B):
+            eng.add_request(i, torch.randint(3, cfg.vocab_size, (ctx,), generator=g).tolist(), sp)
+        new_steps = 0
+        for _ in range(chunks + 8):  # chunked prefill of every row, graph capture, then three warm-up bursts
+            eng.step()
+            decoding = sum(1 for r in eng.rows if r is not None and r.prefilled < 0)
+            new_steps += 1 if decoding == B else 0
+            if new_steps == 3:
+                break
+        assert new_steps == 3, "the rows did not all reach the decode phase"
+        torch.cuda.synchronize()
+        d0 = eng.decode_steps
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(bursts):
+            eng.step()
+        e_.record()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        n = eng.decode_steps - d0
+        t = s_.elapsed_time(e_) * 1e-3 / n
+        wbytes = (m.flat.numel() - (0 if cfg.tie_word_embeddings else cfg.vocab_size * cfg.hidden_size)) * 2
+        kvbytes = 2 * cfg.num_hidden_layers * B * (ctx + 16 * 3 + n // 2) * cfg.kv_size * 2
+        print(f"decode_step {a.model} layers{cfg.num_hidden_layers} B{B} ctx{ctx}: {t * 1e3:.3f} ms per step over {n} "
+              f"steps, {(wbytes + kvbytes) / t / 1e9:.0f} GB/s of weights + KV ({(wbytes + kvbytes) / t / 1e9 / hbm:.2f} "
+              f"{tag} HBM), launches per graph {eng.graph_launches}, dependent-launch chain {not a.no_pdl}")
     elif a.kernel == "attn_fwd":
         T, Hq, Hkv, L = a.m, a.hq, a.hkv, a.ctx
         qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device=dev, dtype=torch.bfloat16)

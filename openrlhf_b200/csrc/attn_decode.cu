@@ -26,6 +26,7 @@ struct DecodeParams {
   int B, Hq, Hkv, max_pages, splits;
   float scale_log2;        // softmax scale * log2(e)
   int* status;
+  int early_trigger;       // the grid fits in one wave (two CTAs per SM): dependents may be released at once
 };
 
 struct DecSmem {
@@ -63,14 +64,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
-  pdl_wait();   // seq_lens / block_table / q / the KV cache come from earlier kernels of the stream
-  const int len = p.seq_lens[b];
-  const int n_tiles_all = (len + PAGE - 1) / PAGE;
-  const int tiles_per_split = (n_tiles_all + p.splits - 1) / p.splits;
-  const int tile0 = split * tiles_per_split;
-  const int tile1 = min(n_tiles_all, tile0 + tiles_per_split);
-  const int n_tiles = max(tile1 - tile0, 0);
-
+  // prologue first: it touches nothing an earlier kernel produces, so under programmatic dependent launch it runs
+  // while the predecessor is still working
   if (threadIdx.x == 0) {
     mbar_init(k_full, 1);
     mbar_init(k_empty, 1);
@@ -99,6 +94,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;        // 2 x 16 columns
   const uint32_t tmem_o = tmem_base + 32;   // 16 columns
+  if (p.early_trigger) pdl_launch_dependents();
+  pdl_wait();   // seq_lens / block_table / q / the KV cache come from earlier kernels of the stream
+  const int len = p.seq_lens[b];
+  const int n_tiles_all = (len + PAGE - 1) / PAGE;
+  const int tiles_per_split = (n_tiles_all + p.splits - 1) / p.splits;
+  const int tile0 = split * tiles_per_split;
+  const int tile1 = min(n_tiles_all, tile0 + tiles_per_split);
+  const int n_tiles = max(tile1 - tile0, 0);
+
 
   if (n_tiles > 0) {
     if (warp == 0) {
@@ -293,9 +297,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   }
 
   __syncwarp();
-  // this grid can be larger than one wave: successors are released only now, so that their CTAs do not take SMs
-  // away from the CTAs of this grid that have not started yet
-  pdl_launch_dependents();
+  // a grid larger than one wave releases its successors only now, so that their CTAs do not take SMs away from the
+  // CTAs of this grid that have not started yet
+  if (!p.early_trigger) pdl_launch_dependents();
   if (p.status != nullptr && *(volatile int*)p.status != 0) {
     uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
@@ -399,6 +403,7 @@ extern "C" int b200_attn_decode(const void* q, const void* k_cache, const void* 
   p.part_o = part_o; p.part_ml = part_ml; p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
   dim3 grid(Hkv, B, splits);
+  p.early_trigger = (long long)Hkv * B * splits <= 2LL * 148 ? 1 : 0;      // two resident CTAs on each of 148 SMs
   if (launch_pdl(attn_decode_kernel, grid, dim3(192), (size_t)DecSmem::TOTAL, stream, tq, tk, tv, p) != cudaSuccess) return -3;
   if (splits > 1) {
     attn_decode_merge_kernel<<<B * Hq, HD, 0, stream>>>(part_o, part_ml, reinterpret_cast<__nv_bfloat16*>(out), B * Hq,

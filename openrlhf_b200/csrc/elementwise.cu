@@ -54,8 +54,8 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int T, int H, int ldx, int ldy,
                    float eps) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   extern __shared__ uint4 row_cache[];  // H/8 vectors
   __shared__ float red[32];
   const int nvec = H >> 3;
@@ -104,8 +104,8 @@ rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                         __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int T, int H, int ldx, int ldy,
                         float eps) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   const int nvec = H >> 3;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -313,8 +313,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restri
 // ------------------------------------------------------------------ SwiGLU: y = silu(g) * u, gu = [g | u]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, long long T,
                                   int F) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   const int nvec = F >> 3;
   const long long total = T * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -358,8 +358,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ------------------------------------------------------------------ embedding
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, int T, int H, int V) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   const int nvec = H >> 3;
   const long long total = (long long)T * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -569,8 +569,8 @@ splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long
                              const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
                              __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ x_out, int M, int N,
                              float eps) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   extern __shared__ uint4 row_cache[];
   __shared__ float red[32];
   const int nvec = N >> 3;
@@ -722,8 +722,8 @@ __global__ void rope_kvwrite_splitk_kernel(const float* __restrict__ ws, int spl
                                            const int* __restrict__ slots, const float2* __restrict__ cos_sin,
                                            __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                                            __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv, int max_pos) {
+  pdl_launch_dependents();   // successors may start their prologue / weight fetch now; they wait for this grid
   pdl_wait();
-  pdl_launch_dependents();
   constexpr int HALF = 64;
   const int heads = Hq + 2 * Hkv;
   const int ld = heads * 128;

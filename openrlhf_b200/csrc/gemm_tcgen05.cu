@@ -70,6 +70,10 @@ struct GemmParams {
   const float* lp_lse;          // mode 2: [M] log-sum-exp of z / T
   const float* lp_dlogp;        // mode 2: [M] upstream gradient of the log-prob
   int lp_entropy;               // mode 1: also accumulate the entropy terms (slots 2, 3)
+  // B is a weight matrix that no kernel in flight writes (decode chain under programmatic dependent launch): the
+  // producer fetches the first B tiles of its ring before it waits for the previous kernel, so the weights stream
+  // while the predecessor is still running; A and everything written come after the wait.
+  int b_static;
 };
 
 // Tensor maps of the A shards of all ranks (each CTA loads its remote tile itself; plain tiled TMA, peer memory).
@@ -131,8 +135,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();                 // operands and C may be produced / still read by the previous kernel in the stream
-  pdl_launch_dependents();    // the next kernel may run its prologue while this one works
+  pdl_launch_dependents();    // the next kernel may run its prologue (and fetch its weights) while this one works
+  // operands and C may be produced / still read by the previous kernel in the stream; with static weights the
+  // producer thread waits only after it has issued its first B tiles (below)
+  const bool early_b = p.b_static && !A_MN && !B_MN && p.ag_world == 0 && p.group_mode == 0;
+  if (!(early_b && threadIdx.x == 0)) pdl_wait();
 
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& kb0, int& kb1, int& grp) {
     grp = 0;
@@ -171,13 +178,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int prefetched = 0;      // stages of the first tile whose B boxes are already in flight
+      if (early_b) {
+        if ((int)blockIdx.x < num_tiles) {
+          int m_blk, n_blk, kb0, kb1, grp;
+          tile_coords(blockIdx.x, m_blk, n_blk, kb0, kb1, grp);
+          for (int kb = kb0; kb < kb1 && prefetched < STAGES; ++kb, ++prefetched) {
+            uint8_t* sb = smem + prefetched * L::STAGE_BYTES + L::A_BYTES;     // fresh ring: every stage is empty
+            mbar_expect_tx(&full_bar[prefetched], L::STAGE_BYTES);
+            if (p.swiglu) {
+              tma_load_2d(sb, &tma_b, &full_bar[prefetched], kb * bke, n_blk * (BN / 2));
+              tma_load_2d(sb + (BN / 2) * 128, &tma_b, &full_bar[prefetched], kb * bke, p.sw_half + n_blk * (BN / 2));
+            } else {
+              tma_load_2d(sb, &tma_b, &full_bar[prefetched], kb * bke, n_blk * BN);
+            }
+          }
+        }
+        pdl_wait();
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk, kb0, kb1, grp;
         tile_coords(tile, m_blk, n_blk, kb0, kb1, grp);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
+          if (prefetched > 0) {
+            // first pass over the ring: the stage was armed and its B boxes issued before the dependency wait
+            --prefetched;
+            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * bke, m_blk * BM);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           if (!A_MN) {
             if (p.ag_world > 0) {
@@ -575,6 +607,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const PeerMaps& 
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, const __nv_bfloat16* __restrict__ bias,
                      const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int M, int N, int ldc) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nvec = N >> 2;
   const long long total = (long long)M * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -616,11 +650,14 @@ extern "C" int b200_splitk_reduce(const float* ws, int splits, const void* bias,
   long long work = (long long)M * (N / 4);
   long long blocks = (work + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  splitk_reduce_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      ws, splits, (long long)M * N, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, M,
-      N, ldc);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return launch_pdl(splitk_reduce_kernel, dim3((int)blocks), dim3(256), (size_t)0, reinterpret_cast<cudaStream_t>(stream_),
+                    ws, splits, (long long)M * N, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+                    (__nv_bfloat16*)out, M, N, ldc) == cudaSuccess ? 0 : -3;
 }
+
+// Declares (on != 0) or ends the decode chain for the calling process: kernels launched meanwhile carry the
+// programmatic-dependent-launch attribute and GEMMs treat their B operand as static weights. Returns the old mode.
+extern "C" int b200_set_pdl(int on) { return b200::g_pdl_mode.exchange(on ? 1 : 0); }
 
 // C-callable entry point. a_mn / b_mn select the operand layouts documented at the top of this file.
 // lda / ldb are the row strides (elements) of the tensors as they sit in memory. Returns 0 on a successful launch.
@@ -656,6 +693,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.M = M; p.N = N; p.K = K; p.ldc = ldc;
   p.out_f32 = out_f32; p.accumulate = accumulate; p.k_splits = k_splits; p.split_stride = split_stride; p.alpha = alpha; p.status = status;
   p.n_peer_c = 0; p.ag_world = 0; p.ag_rows = 0;
+  p.b_static = pdl_static_weights() ? 1 : 0;
   for (int i = 0; i < 8; ++i) p.peer_c[i] = nullptr;
   static PeerMaps no_peers;
 #define B200_DISPATCH(BN_)                                                                            \
@@ -790,6 +828,7 @@ extern "C" int b200_gemm_bf16_swiglu(const void* A, const void* W, void* Y, void
   p.k_splits = 1; p.alpha = 1.f; p.status = status;
   p.swiglu = 1; p.sw_half = I;
   p.C2 = reinterpret_cast<__nv_bfloat16*>(GU); p.ldc2 = ldgu;
+  p.b_static = pdl_static_weights() ? 1 : 0;
   static PeerMaps no_peers;
   if (bn == 256) return launch<256, false, false>(ta, tb, no_peers, p, g_sm_count, stream);
   return launch<128, false, false>(ta, tb, no_peers, p, g_sm_count, stream);

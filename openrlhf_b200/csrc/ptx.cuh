@@ -312,17 +312,27 @@ inline bool set_max_smem_once(std::atomic<unsigned long long>& done, K kernel, i
   return true;
 }
 
-// Host side: launch with the programmatic-stream-serialization attribute when the environment variable
-// OPENRLHF_B200_PDL is "1"; a plain launch otherwise (the default: with grids larger than one wave the early-started
-// successor CTAs take SMs away from the predecessor's remaining CTAs, which measured slower on the decode loop).
-inline bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
+// Host side: programmatic dependent launch is a mode of the calling code, not of a kernel. The rollout engine turns
+// it on (b200_set_pdl) while it records or runs its decode step, where a chain of small kernels is bound by launch
+// and prologue latency and every GEMM's B operand is a weight matrix that no kernel of the chain writes; everything
+// else launches plainly (with grids of several waves the early-started successor CTAs only take SMs away from the
+// predecessor's remaining CTAs). OPENRLHF_B200_PDL=0 keeps it off everywhere, =1 forces the launch attribute on.
+inline std::atomic<int> g_pdl_mode{0};
+inline int pdl_env() {
+  static int v = -2;
+  if (v == -2) {
     const char* e = getenv("OPENRLHF_B200_PDL");
-    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    v = e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
   }
-  return v == 1;
+  return v;
 }
+inline bool pdl_enabled() {
+  const int e = pdl_env();
+  return e == 1 || (e != 0 && g_pdl_mode.load(std::memory_order_relaxed) != 0);
+}
+// True while the caller declared the decode chain: GEMM B operands are static weights and may be fetched before the
+// dependency wait.
+inline bool pdl_static_weights() { return pdl_env() != 0 && g_pdl_mode.load(std::memory_order_relaxed) != 0; }
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {

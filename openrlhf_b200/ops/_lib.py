@@ -6,6 +6,7 @@ library is an error, never a silent fallback.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 import threading
@@ -75,6 +76,18 @@ def check_status(device: torch.device | None = None) -> None:
     if code != 0:
         buf.zero_()
         raise KernelError(f"kernel status {code}: {ERROR_NAMES.get(code, 'unknown')}")
+
+
+@contextlib.contextmanager
+def decode_chain():
+    """Kernels launched inside this block form a decode chain: they carry the programmatic-dependent-launch attribute
+    (a kernel's prologue overlaps its predecessor's tail) and GEMMs fetch their first weight tiles before they wait
+    for the predecessor. Only valid where no kernel of the chain writes a GEMM's B operand."""
+    old = lib().b200_set_pdl(ctypes.c_int(1))
+    try:
+        yield
+    finally:
+        lib().b200_set_pdl(ctypes.c_int(old))
 
 
 LAUNCHES = 0  # number of kernel launches issued through this library (graph replays add their captured count)

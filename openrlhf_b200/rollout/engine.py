@@ -14,6 +14,7 @@ to hand out KV pages and retire finished rows.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
 from dataclasses import dataclass, field
@@ -108,7 +109,7 @@ class RolloutEngine:
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
                  eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None,
                  quantization: str | None = None, enable_prefix_caching: bool = False,
-                 max_prefill_tokens: int = 16384):
+                 max_prefill_tokens: int = 16384, decode_pdl: bool = True):
         assert model.cfg.head_dim == 128 or not model.flat.is_cuda, \
             "the decode attention kernel is specialised for head_dim 128"
         assert quantization in (None, "fp8"), "rollout quantisation: None or 'fp8' (per-tensor e4m3)"
@@ -117,6 +118,7 @@ class RolloutEngine:
         # every weight update), activations are quantised per call; halves the weight bytes a decode step streams.
         # Prefill, attention, norms and the lm_head stay bf16.
         self.quantization = quantization
+        self.decode_pdl = decode_pdl      # fused decode layers launch as a programmatic-dependent-launch chain
         self.fp8: dict = {}
         self.tp = tp          # rollout.tp_engine.TPDecode: `model` then holds this rank's tensor-parallel shard
         self.cfg: ModelConfig = model.cfg
@@ -394,7 +396,9 @@ class RolloutEngine:
         if self.mrope:
             torch.add(self.pos[:B], self.rope_delta[:B], out=self.rope_pos[:B])
         if fused:
-            logits = self._decode_layers_fused(B)
+            # launch- and prologue-bound chain of small kernels over static weights: programmatic dependent launch
+            with (_lib.decode_chain() if self.decode_pdl else contextlib.nullcontext()):
+                logits = self._decode_layers_fused(B)
         else:
             logits = self._decode_layers_generic(B)
         sample(logits, temperature=self.temperature[:B], top_k=self.top_k_rows[:B], top_p=self.top_p_rows[:B], seed=self.seed,
