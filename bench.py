@@ -155,9 +155,9 @@ def resolve(args) -> dict:
 def run_extras(args, world: int, rank: int) -> dict:
     """The configs other than the one just measured, one short run each in a child process per rank (a fresh CUDA
     context; a failure or an overrun there cannot take the headline number with it). Skipped when the time budget of
-    the whole bench (BENCH_TIME_BUDGET_S, default 800 s) does not leave room."""
-    budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "800"))
-    est = {"qwen2.5-7b-grpo": 150.0, "llama3-8b-ppo": 170.0, "qwen2.5-1.5b-reinforce": 100.0}
+    the whole bench (BENCH_TIME_BUDGET_S, default 830 s) does not leave room."""
+    budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "830"))
+    est = {"qwen2.5-7b-grpo": 150.0, "llama3-8b-ppo": 110.0, "qwen2.5-1.5b-reinforce": 100.0}
     out = {}
     port0 = int(os.environ.get("MASTER_PORT", "29500"))
     for k, name in enumerate(n for n in ("llama3-8b-ppo", "qwen2.5-1.5b-reinforce", "qwen2.5-7b-grpo")
@@ -166,14 +166,14 @@ def run_extras(args, world: int, rank: int) -> dict:
             out[name] = {"skipped": f"needs {CONFIGS[name]['min_gpus']} GPUs"}
             continue
         left = budget - (time.time() - T_START)
-        if left < est[name] + 30:
+        if left < est[name] + 25:
             out[name] = {"skipped": f"time budget: {left:.0f} s left, about {est[name]:.0f} s needed"}
             continue
         env = dict(os.environ, MASTER_PORT=str(port0 + 17 + k), NCCL_NVLS_ENABLE="0")
         cmd = [sys.executable, os.path.abspath(__file__), "--config", name, "--gpus", str(world), "--steps", "1",
                "--warmup", "1", "--extras", "none"]
         try:
-            r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=left - 25)
+            r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=left - 15)
             line = next((ln for ln in reversed(r.stdout.splitlines()) if ln.startswith("{")), None)
             if rank == 0:
                 if r.returncode == 0 and line:
@@ -287,7 +287,7 @@ def main():
     # ---- end-to-end region: pinned host prompts in, host-side loss out, wall clock
     # as many steps as the device-timed region, unless the time budget of the whole run would be exceeded (slow
     # configs under a long --steps): then fewer, at least two, the same number on every rank
-    budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "800"))
+    budget = float(os.environ.get("BENCH_TIME_BUDGET_S", "830"))
     fit = int((budget - (time.time() - T_START) - 15.0) / max(dev_s / args.steps, 1e-3))
     e2e_steps = torch.tensor([max(min(2, args.steps), min(args.steps, fit))], device=f"cuda:{local}")
     if world > 1:

@@ -74,10 +74,10 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob", "logprob_bwd",
-                                                         "rmsnorm", "adamw", "decode_step"])
+                                                         "rmsnorm", "adamw", "decode_step", "decode_gemms"])
     ap.add_argument("--model", default="qwen2.5-1.5b", help="decode_step: model preset")
     ap.add_argument("--layers", type=int, default=0, help="decode_step: cut the preset to this many layers (0: all)")
-    ap.add_argument("--no-pdl", action="store_true", help="decode_step: plain launches instead of the dependent-launch chain")
+    ap.add_argument("--pdl", action="store_true", help="decode_step: launch the fused layers as a dependent-launch chain")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8960)
     ap.add_argument("--k", type=int, default=1536)
@@ -150,7 +150,14 @@ def main():
         if a.kernel == "gemm":
             fn = lambda: gemm(A, B, a_mn=a_mn, b_mn=b_mn, bn=a.bn)
         else:
-            fn = lambda: gemm_splitk(A, B, a.splits, bn=a.bn)
+            # distinct weight matrices in turn, more than L2 holds: every launch streams its weights from HBM, as the
+            # layers of a decode step do
+            Bs = [B] + [torch.randn_like(B) for _ in range(max(0, (300 << 20) // (2 * N * K)))]
+            turn = [0]
+
+            def fn():
+                turn[0] += 1
+                return gemm_splitk(A, Bs[turn[0] % len(Bs)], a.splits, bn=a.bn)
         t = _time(fn, a.iters)
         fl = 2.0 * M * N * K
         byt = 2.0 * (M * K + N * K + M * N)
@@ -187,6 +194,42 @@ def main():
         byt = B_ * ctx * 2 * Hkv * 128 * 2
         print(f"decode_attn B{B_} Hq{Hq} Hkv{Hkv} ctx{ctx} splits{a.splits}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s "
               f"({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "decode_gemms":
+        # the four projections of one decoder layer at decode batch size, launched exactly as the rollout engine
+        # launches them (split-K into the fp32 workspace / SwiGLU epilogue), over distinct weights in turn so that
+        # every launch streams from HBM; use --graph N (and --chain) for the in-graph situation
+        import dataclasses
+
+        from openrlhf_b200.models.config import PRESETS
+        from openrlhf_b200.ops.gemm import gemm_swiglu
+        from openrlhf_b200.rollout.engine import gemm_to_workspace
+        cfg = dataclasses.replace(PRESETS[a.model])
+        H, I, B = cfg.hidden_size, cfg.intermediate_size, a.batch
+        shapes = {"qkv": (cfg.qkv_size, H), "o": (H, cfg.q_size), "gate_up": (2 * I, H), "down": (H, I)}
+        for name, (N, K) in shapes.items():
+            x = torch.randn(B, K, device=dev, dtype=torch.bfloat16)
+            ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+                  for _ in range(1 + (300 << 20) // (2 * N * K))]
+            turn = [0]
+
+            def fn():
+                turn[0] += 1
+                w = ws[turn[0] % len(ws)]
+                if name == "gate_up":
+                    return gemm_swiglu(x, w, bn=128)
+                return gemm_to_workspace(x, w)
+            t = _time(fn, a.iters)
+            byt = 2.0 * N * K
+            outs = torch.empty(B, N, device=dev, dtype=torch.bfloat16)
+
+            def lib_fn():
+                turn[0] += 1
+                return torch.matmul(x, ws[turn[0] % len(ws)].t(), out=outs)
+            t_lib = _time(lib_fn, a.iters)
+            print(f"decode_gemms {a.model} B{B} {name} N{N} K{K}: {t * 1e6:.1f} us, weights {byt / t / 1e9:.0f} GB/s "
+                  f"({byt / t / 1e9 / hbm:.2f} {tag} HBM), chain {CHAIN}, graph {GRAPH}; torch.matmul (no SwiGLU, bf16 "
+                  f"output): {t_lib * 1e6:.1f} us")
+            del ws
     elif a.kernel == "decode_step":
         # the rollout engine's whole decode step (CUDA graph of one token for `batch` sequences at context `ctx`),
         # through the public engine API; host work of the scheduler is included, amortised over its 16-step bursts
@@ -203,7 +246,7 @@ def main():
         chunks = (B * ctx + 16383) // 16384          # rows that finish their prefill early decode during the others'
         new = 16 * (bursts + 8 + chunks)
         eng = RolloutEngine(m, max_num_seqs=B, max_model_len=ctx + new + 128,
-                            num_pages=B * ((ctx + new) // 128 + 2) + 8, seed=1, decode_pdl=not a.no_pdl)
+                            num_pages=B * ((ctx + new) // 128 + 2) + 8, seed=1, decode_pdl=a.pdl)
         g = torch.Generator().manual_seed(0)
         sp = SamplingParams(temperature=1.0, max_tokens=new, n=1, ignore_eos=True)
         for i in range(B):
@@ -231,7 +274,7 @@ def main():
         kvbytes = 2 * cfg.num_hidden_layers * B * (ctx + 16 * 3 + n // 2) * cfg.kv_size * 2
         print(f"decode_step {a.model} layers{cfg.num_hidden_layers} B{B} ctx{ctx}: {t * 1e3:.3f} ms per step over {n} "
               f"steps, {(wbytes + kvbytes) / t / 1e9:.0f} GB/s of weights + KV ({(wbytes + kvbytes) / t / 1e9 / hbm:.2f} "
-              f"{tag} HBM), launches per graph {eng.graph_launches}, dependent-launch chain {not a.no_pdl}")
+              f"{tag} HBM), launches per graph {eng.graph_launches}, dependent-launch chain {a.pdl}")
     elif a.kernel == "attn_fwd":
         T, Hq, Hkv, L = a.m, a.hq, a.hkv, a.ctx
         qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device=dev, dtype=torch.bfloat16)

@@ -215,7 +215,26 @@ reshard_copy_kernel(const ReshardEntry* __restrict__ plan, PeerTable srcs, __nv_
   __nv_bfloat16* out = dst + e.dst_off;
   const int vec_per_row = e.row_elems >> 3;
   const long long total = (long long)e.rows * vec_per_row;
-  for (long long i = blockIdx.y * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.y * blockDim.x) {
+  const long long stride = (long long)gridDim.y * blockDim.x;
+  long long i = blockIdx.y * (long long)blockDim.x + threadIdx.x;
+  // four independent 16-byte loads in flight per thread: a launch with few blocks (a copy that shares the GPU with
+  // compute kernels) still covers the NVLink latency
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long j = i + u * stride;
+      const int r = (int)(j / vec_per_row), c = (int)(j % vec_per_row);
+      v[u] = reinterpret_cast<const uint4*>(src + (size_t)r * e.src_ld)[c];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long j = i + u * stride;
+      const int r = (int)(j / vec_per_row), c = (int)(j % vec_per_row);
+      reinterpret_cast<uint4*>(out + (size_t)r * e.dst_ld)[c] = v[u];
+    }
+  }
+  for (; i < total; i += stride) {
     const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row);
     reinterpret_cast<uint4*>(out + (size_t)r * e.dst_ld)[c] = reinterpret_cast<const uint4*>(src + (size_t)r * e.src_ld)[c];
   }
@@ -382,17 +401,26 @@ extern "C" int b200_zero_adam_gather(float* master, float* m, float* v, const fl
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int b200_reshard_copy(const void* plan_dev, int n_entries, const void* const* src_ptrs, int world, void* dst,
-                                 void* stream) {
+// max_ctas > 0 caps the launch at about that many blocks: a copy that runs next to compute kernels (ZeRO-3 layer
+// gathers under the previous layer's GEMMs) must leave thread slots on every SM free, or the compute stream's kernels
+// cannot become resident until the copy's blocks retire. 0: fill the GPU.
+extern "C" int b200_reshard_copy_budget(const void* plan_dev, int n_entries, const void* const* src_ptrs, int world,
+                                        void* dst, int max_ctas, void* stream) {
   if (n_entries <= 0) return 0;
   if (world > MAX_PEERS) return -10;
   // enough blocks per entry to fill the GPU even when a plan has only a handful of large entries
-  int gy = (148 * 8 + n_entries - 1) / n_entries;
-  gy = gy < 8 ? 8 : (gy > 1024 ? 1024 : gy);
+  const int want = max_ctas > 0 ? max_ctas : 148 * 8;
+  int gy = (want + n_entries - 1) / n_entries;
+  const int gy_min = max_ctas > 0 ? 1 : 8;
+  gy = gy < gy_min ? gy_min : (gy > 1024 ? 1024 : gy);
   dim3 grid(n_entries, gy);
   reshard_copy_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const ReshardEntry*>(plan_dev), make_table(src_ptrs, world), reinterpret_cast<__nv_bfloat16*>(dst));
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+extern "C" int b200_reshard_copy(const void* plan_dev, int n_entries, const void* const* src_ptrs, int world, void* dst,
+                                 void* stream) {
+  return b200_reshard_copy_budget(plan_dev, n_entries, src_ptrs, world, dst, 0, stream);
 }
 
 extern "C" int b200_cp_dkv_reduce(const void* const* part_ptrs, int world, int rank, int rows_per_rank, int cols,

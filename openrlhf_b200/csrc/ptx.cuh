@@ -11,6 +11,8 @@
 #include <stdlib.h>
 
 #include <atomic>
+#include <mutex>
+#include <unordered_map>
 
 namespace b200 {
 
@@ -333,9 +335,26 @@ inline bool pdl_enabled() {
 // True while the caller declared the decode chain: GEMM B operands are static weights and may be fetched before the
 // dependency wait.
 inline bool pdl_static_weights() { return pdl_env() != 0 && g_pdl_mode.load(std::memory_order_relaxed) != 0; }
+// Kernels of a decode chain ask for the largest shared-memory carveout, like the GEMM and attention kernels between
+// them need: an SM whose resident kernel was placed under a different L1 / shared-memory split has to drain before a
+// kernel with another split can start on it, which would undo the overlap that dependent launches are for. The
+// preference belongs to (kernel, device); it is set once per pair.
+inline void prefer_max_carveout(const void* kernel) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, unsigned long long> done;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+  std::lock_guard<std::mutex> lock(mu);
+  unsigned long long& bits = done[kernel];
+  if (bits & (1ull << dev)) return;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  bits |= 1ull << dev;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {
+  if (pdl_enabled()) prefer_max_carveout(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -70,6 +70,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     """y = x @ w.T (+ bias) (+ residual); x [T, K], w [N, K]."""
     if not x.is_cuda:
         return reference.linear(x, w, bias, residual)
+    if w.shape[0] % 8 or w.shape[1] % 8:
+        # the TMA tiles want 16-byte rows: a projection with fewer than 8 (or a ragged number of) outputs, such as the
+        # router of a model with 4 experts, is too small for the tensor-core kernel to matter
+        return reference.linear(x, w, bias, residual)
     return _Linear.apply(x, w, bias, residual)
 
 

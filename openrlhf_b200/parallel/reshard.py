@@ -201,10 +201,13 @@ class ReshardPlan:
         self.n = len(entries)
         self.dev = torch.from_numpy(rec.view(np.uint8).copy()).to(device)
 
-    def run(self, src_ptrs: list[int], dst: torch.Tensor) -> None:
+    def run(self, src_ptrs: list[int], dst: torch.Tensor, max_ctas: int = 0) -> None:
+        """max_ctas > 0: launch about that many blocks only (a copy that overlaps compute kernels on another stream
+        must leave room on every SM for them)."""
         from ..ops import _lib
 
         arr = (ctypes.c_void_p * len(src_ptrs))(*[ctypes.c_void_p(int(p)) for p in src_ptrs])
-        rc = _lib.lib().b200_reshard_copy(_lib.ptr(self.dev), ctypes.c_int(self.n), arr, ctypes.c_int(len(src_ptrs)),
-                                          _lib.ptr(dst), _lib.stream_ptr())
+        rc = _lib.lib().b200_reshard_copy_budget(_lib.ptr(self.dev), ctypes.c_int(self.n), arr,
+                                                 ctypes.c_int(len(src_ptrs)), _lib.ptr(dst), ctypes.c_int(max_ctas),
+                                                 _lib.stream_ptr())
         _lib.check_rc(rc, "reshard_copy")

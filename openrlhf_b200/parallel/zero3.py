@@ -22,6 +22,7 @@ CPU / gloo ranks run the same control flow with torch.distributed collectives in
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 
 import torch
@@ -31,6 +32,15 @@ from ..models.transformer import ALIGN, ParamSpec, TransformerLM
 from ..ops import _lib
 from .reshard import CopyEntry, ReshardPlan
 from .zero import LRScheduler
+
+
+# Block budget of the copy / reduction kernels that run on side streams under the compute stream's GEMMs (0: fill the
+# GPU). Measured on 2 GPUs with the Qwen2.5-7B architecture, budgets of one or two blocks per SM were not faster than
+# full launches (training phase 4.85 / 4.62 s against 4.55 s), so the default is 0.
+OVERLAP_CTAS = int(os.environ.get("OPENRLHF_B200_OVERLAP_CTAS", "0"))
+# "0": run the layer gathers and gradient reductions on the compute stream (no overlap; for measurements)
+OVERLAP = os.environ.get("OPENRLHF_B200_ZERO3_OVERLAP", "1") != "0"
+GRAD_SLOTS = int(os.environ.get("OPENRLHF_B200_ZERO3_GRAD_SLOTS", "4"))
 
 
 def _round(n: int, m: int) -> int:
@@ -83,6 +93,14 @@ class Zero3Engine:
         self.res_size = off
         self.slot_base = [self.res_size, self.res_size + slot]
         self.work_size = self.res_size + 2 * slot
+        # gradient slots: layer i accumulates into slot i % G. More slots than parameter slots, so that a layer's
+        # reduction (two cross-rank barriers around a pull over NVLink) has G - 1 layers of backward compute to finish
+        # in before its slot is needed again; with two slots every rank would run in lockstep with the slowest one
+        # at a granularity of one layer.
+        self.gslots = max(2, min(GRAD_SLOTS, L)) if train else 2
+        self.gslot_base = [self.res_size + k * slot for k in range(self.gslots)]
+        self.slot_width = slot
+        self.gwork_size = self.res_size + self.gslots * slot
 
         # ---- this rank's slices (taken from the full buffer the model was built on)
         full = model.flat
@@ -99,7 +117,7 @@ class Zero3Engine:
             self.param_ptrs = list(self._hp.buffer_ptrs)
             self.grad_work = self.grad_ptrs = None
             if train:
-                self.grad_work = symm_mem.empty(self.work_size, dtype=torch.float32, device=self.device)
+                self.grad_work = symm_mem.empty(self.gwork_size, dtype=torch.float32, device=self.device)
                 self._hg = symm_mem.rendezvous(self.grad_work, self.group)
                 self.grad_ptrs = list(self._hg.buffer_ptrs)
             self.pad = symm_mem.empty(1024, dtype=torch.int32, device=self.device)
@@ -109,7 +127,7 @@ class Zero3Engine:
             self.bar_epochs = [0, 0]
         else:
             self.param_shard = torch.empty(self.per, dtype=full.dtype, device=self.device)
-            self.grad_work = torch.zeros(self.work_size, dtype=torch.float32, device=self.device) if train else None
+            self.grad_work = torch.zeros(self.gwork_size, dtype=torch.float32, device=self.device) if train else None
         self.param_shard.copy_(full[self.lo:self.hi])
         self.master = self.exp_avg = self.exp_avg_sq = self.grad_shard = None
         if train:
@@ -136,7 +154,8 @@ class Zero3Engine:
             self.work_off[s.name] = w_off
             p.data = self.work[w_off:w_off + s.numel].view(s.shape)
             if train:
-                p.main_grad = self.grad_work[w_off:w_off + s.numel].view(s.shape)
+                g_off = w_off if i < 0 else self.gslot_base[i % self.gslots] + (s.offset - self.layer_rng[i][0])
+                p.main_grad = self.grad_work[g_off:g_off + s.numel].view(s.shape)
         model.flat = self.work          # the logical flat buffer no longer exists on this rank
         model.z3 = self
         del full
@@ -148,7 +167,7 @@ class Zero3Engine:
                                 device=self.device)
         self._pending_zero = -1
         self._rs_stream = None                    # side stream of the per-layer gradient reductions
-        self._slot_reduced = [None, None]         # event: the gradient slot has been reduced and cleared
+        self._slot_reduced = [None] * self.gslots  # event: the gradient slot has been reduced and cleared
         self._sync()
         self.gather_resident()
 
@@ -179,8 +198,9 @@ class Zero3Engine:
             a += n
         return out
 
-    def _gather_range(self, key, pieces):
-        """pieces: list of (logical lo, logical hi, working offset). One copy kernel over peer memory per call."""
+    def _gather_range(self, key, pieces, max_ctas: int = 0):
+        """pieces: list of (logical lo, logical hi, working offset). One copy kernel over peer memory per call.
+        max_ctas: block budget of a copy that runs under compute kernels of another stream (0: fill the GPU)."""
         if self.world == 1:
             for a, b, w in pieces:
                 self.work.data[w:w + (b - a)].copy_(self.param_shard[a:b])
@@ -193,7 +213,7 @@ class Zero3Engine:
                     for r, so, la, n in self._ranges(a, b):
                         entries.append(CopyEntry(so, w + (la - a), 1, n, n, n, r))
                 plan = self._plans[key] = ReshardPlan(entries, self.device)
-            plan.run(self.param_ptrs, self.work)
+            plan.run(self.param_ptrs, self.work, max_ctas)
             return
         full = torch.empty(self.padded, dtype=self.param_shard.dtype)
         dist.all_gather_into_tensor(full, self.param_shard, group=self.group)
@@ -228,14 +248,16 @@ class Zero3Engine:
                 else:
                     n = _round(sp.numel, ALIGN)
                     pieces.append((sp.offset, sp.offset + n, w))
-        if self.on_gpu and self.world > 1:
+        if self.on_gpu and self.world > 1 and OVERLAP:
             if self._side is None:
-                self._side = torch.cuda.Stream(device=self.device)
+                # high priority: the copy's few blocks are placed as soon as a slot frees up instead of queueing
+                # behind the waves of the compute stream's kernels
+                self._side = torch.cuda.Stream(device=self.device, priority=-1)
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self._side):
                 self._side.wait_event(ready)
-                self._gather_range(("layer", i), pieces)
+                self._gather_range(("layer", i), pieces, OVERLAP_CTAS)
                 done = torch.cuda.Event()
                 done.record(self._side)
             self._inflight[i] = done
@@ -250,7 +272,7 @@ class Zero3Engine:
         if done is not None:
             torch.cuda.current_stream(self.device).wait_event(done)
 
-    def _reduce_range(self, a: int, b: int, w_off: int):
+    def _reduce_range(self, a: int, b: int, w_off: int, max_ctas: int = 0):
         """grad_shard[my part of logical [a, b)] += mean over ranks of the working gradients at w_off + (x - a)."""
         lo, hi = max(a, self.lo), min(b, self.hi)
         if self.world == 1:
@@ -271,7 +293,7 @@ class Zero3Engine:
             tmp = self._tmp[:n]
             rc = _lib.lib().b200_zero_reduce(ptrs, None, ctypes.c_int(self.world), ctypes.c_longlong(w_off + (c0 - a)),
                                              ctypes.c_longlong(n), ctypes.c_float(1.0 / self.world), _lib.ptr(tmp),
-                                             _lib.ptr(self.scalars), ctypes.c_int(0), _lib.stream_ptr())
+                                             _lib.ptr(self.scalars), ctypes.c_int(max_ctas), _lib.stream_ptr())
             _lib.check_rc(rc, "zero_reduce")
             self.grad_shard[c0 - self.lo:c0 - self.lo + n].add_(tmp)
 
@@ -283,12 +305,12 @@ class Zero3Engine:
 
     def pre_backward_hook(self, i: int):
         def hook(grad):
-            ev = self._slot_reduced[i % 2]
+            ev = self._slot_reduced[i % self.gslots]
             if ev is not None:
-                # layer i's weight gradients go into the gradient slot that layer i + 2 used: its reduction (which ran
-                # on the side stream under layer i + 1's backward pass) must have emptied the slot
+                # layer i's weight gradients go into the gradient slot that layer i + G used: its reduction (which ran
+                # on the side stream under the backward passes of the layers in between) must have emptied the slot
                 torch.cuda.current_stream(self.device).wait_event(ev)
-                self._slot_reduced[i % 2] = None
+                self._slot_reduced[i % self.gslots] = None
             self.gather_layer(i)
             if i > 0:
                 self._start_gather(i - 1)      # prefetch for the next layer of the backward pass
@@ -308,32 +330,38 @@ class Zero3Engine:
         if not self.on_gpu:
             return                                     # CPU ranks reduce after loss.backward() (see backward)
         a, b = self.layer_rng[i]
-        slot = self.slot_base[i % 2]
-        width = self.slot_base[1] - self.slot_base[0]
+        slot = self.gslot_base[i % self.gslots]
+        width = self.slot_width
         if self.world == 1:
             self._reduce_range(a, b, slot)
             self.grad_work[slot:slot + width].zero_()
             return
+        if not OVERLAP:
+            self._sync(1)
+            self._reduce_range(a, b, slot)
+            self._sync(1)
+            self.grad_work[slot:slot + width].zero_()
+            return
         if self._rs_stream is None:
-            self._rs_stream = torch.cuda.Stream(device=self.device)
+            self._rs_stream = torch.cuda.Stream(device=self.device, priority=-1)
         cur = torch.cuda.current_stream(self.device)
         ready = torch.cuda.Event()
         ready.record(cur)
         with torch.cuda.stream(self._rs_stream):
             self._rs_stream.wait_event(ready)
             self._sync(1)
-            self._reduce_range(a, b, slot)
+            self._reduce_range(a, b, slot, OVERLAP_CTAS)
             self._sync(1)
             self.grad_work[slot:slot + width].zero_()
             done = torch.cuda.Event()
             done.record(self._rs_stream)
-        self._slot_reduced[i % 2] = done
+        self._slot_reduced[i % self.gslots] = done
 
     def _finish_backward(self):
         """Resident parameters' gradients; joins the per-layer reductions still running on the side stream."""
         if self.on_gpu:
             cur = torch.cuda.current_stream(self.device)
-            for k in (0, 1):
+            for k in range(self.gslots):
                 if self._slot_reduced[k] is not None:
                     cur.wait_event(self._slot_reduced[k])
                     self._slot_reduced[k] = None
@@ -362,9 +390,9 @@ class Zero3Engine:
                         if s.name.startswith(f"layers.{i}.") and named[s.name].grad is not None:
                             named[s.name].main_grad.add_(named[s.name].grad.float())
                     a, b = self.layer_rng[i]
-                    self._reduce_range(a, b, self.slot_base[i % 2])
-                    base = self.slot_base[i % 2]
-                    self.grad_work[base:base + (self.slot_base[1] - self.slot_base[0])].zero_()
+                    base = self.gslot_base[i % self.gslots]
+                    self._reduce_range(a, b, base)
+                    self.grad_work[base:base + self.slot_width].zero_()
                 for s in self.model.specs:
                     if s.name in self.res_map and named[s.name].grad is not None:
                         named[s.name].main_grad.add_(named[s.name].grad.float())

@@ -109,7 +109,7 @@ class RolloutEngine:
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.5, seed: int = 0,
                  eos_token_id: int | None = None, use_cuda_graph: bool = True, check_interval: int = 16, tp=None,
                  quantization: str | None = None, enable_prefix_caching: bool = False,
-                 max_prefill_tokens: int = 16384, decode_pdl: bool = True):
+                 max_prefill_tokens: int = 16384, decode_pdl: bool = False):
         assert model.cfg.head_dim == 128 or not model.flat.is_cuda, \
             "the decode attention kernel is specialised for head_dim 128"
         assert quantization in (None, "fp8"), "rollout quantisation: None or 'fp8' (per-tensor e4m3)"
@@ -118,7 +118,9 @@ class RolloutEngine:
         # every weight update), activations are quantised per call; halves the weight bytes a decode step streams.
         # Prefill, attention, norms and the lm_head stay bf16.
         self.quantization = quantization
-        self.decode_pdl = decode_pdl      # fused decode layers launch as a programmatic-dependent-launch chain
+        # fused decode layers launched as a programmatic-dependent-launch chain; off by default: on the decode loops
+        # measured (Qwen2.5-1.5B at batch 128, Qwen2.5-7B at batch 64) it changes the step time by less than 1 %
+        self.decode_pdl = decode_pdl
         self.fp8: dict = {}
         self.tp = tp          # rollout.tp_engine.TPDecode: `model` then holds this rank's tensor-parallel shard
         self.cfg: ModelConfig = model.cfg

@@ -328,6 +328,13 @@ def test_reshard_plan_kernel(tp, src_world):
         ReshardPlan(entries, "cuda").run([s.data_ptr() for s in srcs], got)
         torch.cuda.synchronize()
         assert torch.equal(got.cpu(), want)
+        # the same plan under a block budget (a copy that shares the GPU with compute kernels): fewer blocks, each
+        # with several loads in flight, identical result
+        for budget in (1, 37, 296):
+            got.zero_()
+            ReshardPlan(entries, "cuda").run([s.data_ptr() for s in srcs], got, max_ctas=budget)
+            torch.cuda.synchronize()
+            assert torch.equal(got.cpu(), want), budget
 
 
 @pytest.mark.parametrize("T,H,I,E,k", [(300, 128, 128, 8, 2), (1000, 256, 192, 16, 4)])
