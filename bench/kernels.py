@@ -232,7 +232,7 @@ def main():
             del ws
     elif a.kernel == "decode_step":
         # the rollout engine's whole decode step (CUDA graph of one token for `batch` sequences at context `ctx`),
-        # through the public engine API; host work of the scheduler is included, amortised over its 16-step bursts
+        # through the public engine API; host work of the scheduler is included, amortised over its 32-step bursts
         import dataclasses
 
         from openrlhf_b200.models.config import PRESETS
@@ -244,9 +244,11 @@ def main():
         m = TransformerLM(cfg, device=dev, seed=0)
         B, ctx, bursts = a.batch, a.ctx, max(2, a.iters)
         chunks = (B * ctx + 16383) // 16384          # rows that finish their prefill early decode during the others'
-        new = 16 * (bursts + 8 + chunks)
+        interval = 4                                 # bursts of 4 steps while rows still prefill, 8 x 4 afterwards
+        new = interval * (8 * (bursts + 5) + chunks + 4)
         eng = RolloutEngine(m, max_num_seqs=B, max_model_len=ctx + new + 128,
-                            num_pages=B * ((ctx + new) // 128 + 2) + 8, seed=1, decode_pdl=a.pdl)
+                            num_pages=B * ((ctx + new) // 128 + 2) + 8, seed=1, decode_pdl=a.pdl,
+                            check_interval=interval)
         g = torch.Generator().manual_seed(0)
         sp = SamplingParams(temperature=1.0, max_tokens=new, n=1, ignore_eos=True)
         for i in range(B):
@@ -271,7 +273,7 @@ def main():
         n = eng.decode_steps - d0
         t = s_.elapsed_time(e_) * 1e-3 / n
         wbytes = (m.flat.numel() - (0 if cfg.tie_word_embeddings else cfg.vocab_size * cfg.hidden_size)) * 2
-        kvbytes = 2 * cfg.num_hidden_layers * B * (ctx + 16 * 3 + n // 2) * cfg.kv_size * 2
+        kvbytes = 2 * cfg.num_hidden_layers * B * (ctx + interval * 8 * 3 + n // 2) * cfg.kv_size * 2
         print(f"decode_step {a.model} layers{cfg.num_hidden_layers} B{B} ctx{ctx}: {t * 1e3:.3f} ms per step over {n} "
               f"steps, {(wbytes + kvbytes) / t / 1e9:.0f} GB/s of weights + KV ({(wbytes + kvbytes) / t / 1e9 / hbm:.2f} "
               f"{tag} HBM), launches per graph {eng.graph_launches}, dependent-launch chain {a.pdl}")

@@ -852,7 +852,14 @@ class RolloutEngine:
             return finished
         # ---- decode burst
         left = [self.rows[i].max_tokens - self.rows[i].gen for i in live if self.rows[i].max_tokens > self.rows[i].gen]
-        steps = max(1, min([self.check_interval] + left)) if left else 0
+        # rows that ignore EOS can only finish at their token limit, which `left` already bounds: nothing can happen
+        # inside a longer burst that the host would have to react to, so it is allowed to be several times as long
+        # (fewer host round trips between bursts)
+        # (only while nothing waits for admission or for its next prefill chunk)
+        busy = bool(self.waiting) or any(r is not None and r.prefilled >= 0 for r in self.rows)
+        fixed_length = not busy and all(self._req[self.rows[i].request_id][1].ignore_eos for i in live)
+        cap = self.check_interval * (8 if fixed_length else 1)
+        steps = max(1, min([cap] + left)) if left else 0
         if steps:
             def short(k):
                 return sum(self._pages_short(i, self.rows[i].prompt_len + (self.rows[i].gen - self.rows[i].base) + k)
