@@ -48,6 +48,9 @@ class ModelConfig:
     vision_end_token_id: int = -1
     mrope_section: tuple = ()
     extra: dict = field(default_factory=dict)  # unknown config.json keys, preserved on save
+    # rows of lm_head.weight held by this model object: 0 = all of the vocabulary; a tensor-parallel training shard
+    # with a vocabulary-parallel head holds vocab_size / tp of them (never written to config.json)
+    lm_head_vocab: int = 0
 
     def __post_init__(self):
         if not self.head_dim:

@@ -64,7 +64,7 @@ def build_param_specs(cfg: ModelConfig, with_lm_head: bool = True, with_value_he
             add(p + "down.weight", (H, cfg.intermediate_size))
     add("norm.weight", (H,), False, "ones")
     if with_lm_head and not cfg.tie_word_embeddings:
-        add("lm_head.weight", (cfg.vocab_size, H))
+        add("lm_head.weight", (cfg.lm_head_vocab or cfg.vocab_size, H))
     if with_value_head:
         add("value_head.weight", (1, H))
     if cfg.vision is not None:
@@ -288,9 +288,25 @@ class TransformerLM(nn.Module):
 
     # ------------------------------------------------------------------ heads
     def logprobs(self, hidden, labels, temperature=1.0, want_entropy=False, chunk=4096):
+        tpt = self.tp_train
+        if tpt is not None and tpt.vocab_parallel:
+            # this rank holds vocab_size / tp rows of the head: every rank streams its own columns of the logits and
+            # the ranks exchange 16 bytes of softmax statistics per token
+            return F.vocab_parallel_logprob(hidden, self.lm_head_weight(), labels, tpt.vocab_start, tpt.group,
+                                            temperature, want_entropy, chunk)
         return F.fused_logprob(hidden, self.lm_head_weight(), labels, temperature, want_entropy, chunk)
 
     def logits(self, hidden):
+        tpt = self.tp_train
+        if tpt is not None and tpt.vocab_parallel:
+            import torch.distributed as dist
+
+            assert not (torch.is_grad_enabled() and hidden.requires_grad), \
+                "full logits of a vocabulary-parallel head are for evaluation; train through logprobs()"
+            local = F.linear(hidden, self.lm_head_weight())
+            parts = [torch.empty_like(local) for _ in range(tpt.size)]
+            dist.all_gather(parts, local.contiguous(), group=tpt.group)
+            return torch.cat(parts, dim=1)
         return F.linear(hidden, self.lm_head_weight())
 
     def values(self, hidden):

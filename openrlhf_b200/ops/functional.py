@@ -398,6 +398,33 @@ def _vp_combine(stats: torch.Tensor):
     return logp, ent, lse_g
 
 
+def _lmhead_stats(h, w, labels, inv_t: float, want_entropy: bool):
+    """(log p(label), entropy at temperature 1 or None, log-sum-exp of z / T) per row from the fused LM-head kernels:
+    the GEMM epilogue leaves softmax partials, a merge kernel folds them; no logits are written. Labels outside
+    [0, rows of w) contribute no label term (vocabulary shards)."""
+    T, K = h.shape
+    V = w.shape[0]
+    dev = h.device
+    L = _L()
+    logp = torch.empty(T, dtype=torch.float32, device=dev)
+    ent = torch.empty(T, dtype=torch.float32, device=dev) if want_entropy else None
+    lse = torch.empty(T, dtype=torch.float32, device=dev)
+    nb = int(L.b200_lmhead_num_blocks(_c_int(V)))
+    rows_max = max(128, min(T, (1 << 28) // (nb * 8)))
+    partial = torch.empty(nb * min(T, rows_max) * 8, dtype=torch.float32, device=dev)
+    st = _lib.status_word(dev)
+    for s in range(0, T, rows_max):
+        e = min(T, s + rows_max)
+        rc = L.b200_lmhead_partials(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(labels[s:e]), _c_f(inv_t),
+                                    _c_int(int(want_entropy)), _lib.ptr(partial), _c_int(e - s), _c_int(V), _c_int(K),
+                                    _c_int(h.stride(0)), _c_int(w.stride(0)), _lib.ptr(st), _lib.stream_ptr())
+        _lib.check_rc(rc, "lmhead_partials")
+        rc = L.b200_lmhead_merge(_lib.ptr(partial), _c_int(nb), _c_int(e - s), _c_f(inv_t), _lib.ptr(logp[s:e]),
+                                 _lib.ptr(ent[s:e]) if ent is not None else None, _lib.ptr(lse[s:e]), _lib.stream_ptr())
+        _lib.check_rc(rc, "lmhead_merge")
+    return logp, ent, lse
+
+
 class _VocabParallelLogprob(torch.autograd.Function):
     """Fused log-prob over an lm_head whose rows (vocabulary) are split across a group: every rank streams its own
     V/n columns of the logits, 16 bytes of statistics per token and rank are exchanged, and the backward pass needs one
@@ -411,7 +438,16 @@ class _VocabParallelLogprob(torch.autograd.Function):
         lab = labels.long() - vocab_start
         inr = (lab >= 0) & (lab < Vl)
         stats = torch.zeros(T, 4, dtype=torch.float32, device=h.device)
-        if h.is_cuda:
+        ctx.fused = bool(h.is_cuda and _lmhead_fusable(h, w))
+        if ctx.fused:
+            lab = lab.contiguous()
+            logp, ent, lse = _lmhead_stats(h, w, lab, 1.0 / temperature, want_entropy)
+            stats[:, 0] = lse
+            stats[:, 1] = torch.where(inr, logp + lse, torch.zeros_like(logp))
+            if want_entropy:
+                lse1 = lse if temperature == 1.0 else _lmhead_stats(h, w, lab, 1.0, False)[2]
+                stats[:, 2], stats[:, 3] = lse1, lse1 - ent
+        elif h.is_cuda:
             logp = torch.empty(T, dtype=torch.float32, device=h.device)
             lse = torch.empty_like(logp)
             ent = torch.empty_like(logp)
@@ -464,13 +500,24 @@ class _VocabParallelLogprob(torch.autograd.Function):
         if h.is_cuda:
             dh = torch.empty_like(h)
             dw_buf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            st = _lib.status_word(h.device)
             for s in range(0, T, ctx.chunk):
                 e = min(T, s + ctx.chunk)
-                logits = gemm(h[s:e], w)
-                rc = _L().b200_logprob_bwd_rows(_lib.ptr(logits), _c_int(e - s), _c_int(Vl), _c_int(logits.stride(0)),
-                                                _lib.ptr(lab[s:e]), _lib.ptr(lse_g[s:e]), _lib.ptr(dlogp[s:e]),
-                                                _c_f(inv_t), _lib.stream_ptr())
-                _lib.check_rc(rc, "logprob_bwd_rows")
+                if ctx.fused:
+                    # the recomputed logits leave the GEMM epilogue as d logits (global log-sum-exp; the one-hot term
+                    # only on the rank whose shard holds the label)
+                    logits = torch.empty(e - s, Vl, dtype=torch.bfloat16, device=h.device)
+                    rc = _L().b200_lmhead_dlogits(_lib.ptr(h[s:e]), _lib.ptr(w), _lib.ptr(logits), _lib.ptr(lab[s:e]),
+                                                  _lib.ptr(lse_g[s:e]), _lib.ptr(dlogp[s:e]), _c_f(inv_t), _c_int(e - s),
+                                                  _c_int(Vl), _c_int(h.shape[1]), _c_int(h.stride(0)),
+                                                  _c_int(w.stride(0)), _c_int(Vl), _lib.ptr(st), _lib.stream_ptr())
+                    _lib.check_rc(rc, "lmhead_dlogits")
+                else:
+                    logits = gemm(h[s:e], w)
+                    rc = _L().b200_logprob_bwd_rows(_lib.ptr(logits), _c_int(e - s), _c_int(Vl),
+                                                    _c_int(logits.stride(0)), _lib.ptr(lab[s:e]), _lib.ptr(lse_g[s:e]),
+                                                    _lib.ptr(dlogp[s:e]), _c_f(inv_t), _lib.stream_ptr())
+                    _lib.check_rc(rc, "logprob_bwd_rows")
                 gemm(logits, w, b_mn=True, out=dh[s:e])
                 gemm(logits, h[s:e], a_mn=True, b_mn=True, out=dw_buf, accumulate=True)
             dw = None if mg is not None else dw_buf.to(w.dtype)

@@ -33,7 +33,7 @@ class CopyEntry:
     src_rank: int
 
 
-def _tp_row_ranges(name: str, shape, cfg: ModelConfig, tp_rank: int, tp: int):
+def _tp_row_ranges(name: str, shape, cfg: ModelConfig, tp_rank: int, tp: int, vocab_parallel: bool = False):
     """(row ranges, column range) of the parameter that TP rank `tp_rank` holds. Column-parallel matrices are cut by
     rows of the fused layouts (q | k | v heads, gate | up), row-parallel ones by columns; the rest is replicated."""
     D = cfg.head_dim
@@ -42,6 +42,10 @@ def _tp_row_ranges(name: str, shape, cfg: ModelConfig, tp_rank: int, tp: int):
     cols_all = (0, shape[-1]) if len(shape) > 1 else (0, 1)
     if tp == 1:
         return rows_all, cols_all
+    if vocab_parallel and name == "lm_head.weight":
+        assert shape[0] % tp == 0
+        s = shape[0] // tp
+        return [(tp_rank * s, (tp_rank + 1) * s)], cols_all
     Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
     if leaf in ("qkv.weight", "qkv.bias"):
         assert Hq % tp == 0 and Hkv % tp == 0, "heads must divide the tensor-parallel size"
@@ -62,14 +66,14 @@ def _tp_row_ranges(name: str, shape, cfg: ModelConfig, tp_rank: int, tp: int):
 
 
 def tp_param_specs(cfg: ModelConfig, tp_rank: int, tp: int, with_lm_head: bool = True,
-                   with_value_head: bool = False) -> list[ParamSpec]:
+                   with_value_head: bool = False, vocab_parallel: bool = False) -> list[ParamSpec]:
     """Layout of one TP rank's flat buffer (same order and alignment rule as the trainer's)."""
     out, off = [], 0
     for s in build_param_specs(cfg, with_lm_head, with_value_head):
         if len(s.shape) == 3:          # experts [E, rows, cols]: kept whole (expert parallelism shards by expert)
             shape = s.shape
         else:
-            rows, cols = _tp_row_ranges(s.name, s.shape, cfg, tp_rank, tp)
+            rows, cols = _tp_row_ranges(s.name, s.shape, cfg, tp_rank, tp, vocab_parallel)
             nrows = sum(b - a for a, b in rows)
             shape = (nrows, cols[1] - cols[0]) if len(s.shape) == 2 else (nrows,)
         n = 1
@@ -81,13 +85,14 @@ def tp_param_specs(cfg: ModelConfig, tp_rank: int, tp: int, with_lm_head: bool =
 
 
 def build_plan(cfg: ModelConfig, tp_rank: int = 0, tp: int = 1, src_world: int = 1, src_shard_elems: int | None = None,
-               with_lm_head: bool = True, with_value_head: bool = False) -> tuple[list[CopyEntry], int]:
+               with_lm_head: bool = True, with_value_head: bool = False,
+               vocab_parallel: bool = False) -> tuple[list[CopyEntry], int]:
     """Copy plan for one destination TP rank. Sources: `src_world` == 1 (every rank holds the whole flat buffer: read
     locally, source rank 0 in the table the caller passes) or a flat buffer cut into `src_world` slices of
     `src_shard_elems` elements (ZeRO-3: entries are split where a row block crosses a slice boundary).
     Returns (entries, destination buffer size in elements)."""
     src_specs = build_param_specs(cfg, with_lm_head, with_value_head)
-    dst_specs = tp_param_specs(cfg, tp_rank, tp, with_lm_head, with_value_head)
+    dst_specs = tp_param_specs(cfg, tp_rank, tp, with_lm_head, with_value_head, vocab_parallel)
     entries: list[CopyEntry] = []
 
     def emit(src_off, dst_off, rows, row_elems, src_ld, dst_ld):
@@ -136,7 +141,7 @@ def build_plan(cfg: ModelConfig, tp_rank: int = 0, tp: int = 1, src_world: int =
         if len(s.shape) == 3 or len(s.shape) == 1 and tp == 1:
             emit(s.offset, d.offset, 1, s.numel, s.numel, s.numel)
             continue
-        rows, cols = _tp_row_ranges(s.name, s.shape, cfg, tp_rank, tp)
+        rows, cols = _tp_row_ranges(s.name, s.shape, cfg, tp_rank, tp, vocab_parallel)
         r_out = 0
         if len(s.shape) == 1:
             for a, b in rows:

@@ -1,8 +1,9 @@
 """Tensor parallelism for training: every rank of a TP group holds 1/tp of each projection and the same activations.
 
 * qkv and gate_up are column-parallel (a rank owns Hq/tp query heads, Hkv/tp kv heads and I/tp FFN columns), o_proj and
-  down_proj are row-parallel; embeddings, norms, lm_head and value head are replicated. The per-rank model is an
-  ordinary ``TransformerLM`` built from the local head / FFN counts, so every kernel (fused RoPE + attention, SwiGLU
+  down_proj are row-parallel; an lm_head that is a matrix of its own is split by vocabulary rows (the log-prob kernel
+  exchanges 16 bytes of softmax statistics per token); embeddings, norms and the value head are replicated. The
+  per-rank model is an ordinary ``TransformerLM`` built from the local head / FFN counts, so every kernel (fused RoPE + attention, SwiGLU
   GEMM epilogue, fused log-prob head) runs unchanged on the shard.
 * Two autograd-aware collectives stitch the shards together: the input of a column-parallel projection is an identity
   whose backward sums the input gradients over the group, the output of a row-parallel projection is a sum over the
@@ -86,13 +87,23 @@ class _RowParallelFused(torch.autograd.Function):
         return dx, dw, None
 
 
-def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+def vocab_parallel_head(cfg: ModelConfig, tp: int, with_lm_head: bool) -> bool:
+    """The lm_head is split by vocabulary rows when it is a matrix of its own (no tied embeddings) and its rows divide
+    evenly into shards that the GEMM accepts (multiples of 8); OPENRLHF_B200_TP_VOCAB_PARALLEL=0 keeps it replicated."""
+    import os
+
+    return (with_lm_head and not cfg.tie_word_embeddings and cfg.vocab_size % (8 * tp) == 0
+            and os.environ.get("OPENRLHF_B200_TP_VOCAB_PARALLEL", "1") != "0")
+
+
+def local_config(cfg: ModelConfig, tp: int, vocab_parallel: bool = False) -> ModelConfig:
     assert cfg.num_experts == 0, "tensor-parallel training covers dense models (MoE layers use expert parallelism)"
     assert cfg.num_attention_heads % tp == 0 and cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % tp == 0, \
         "attention heads, kv heads and the FFN width must be divisible by the tensor-parallel size"
     return dataclasses.replace(cfg, num_attention_heads=cfg.num_attention_heads // tp,
                                num_key_value_heads=cfg.num_key_value_heads // tp,
-                               intermediate_size=cfg.intermediate_size // tp, head_dim=cfg.head_dim)
+                               intermediate_size=cfg.intermediate_size // tp, head_dim=cfg.head_dim,
+                               lm_head_vocab=cfg.vocab_size // tp if vocab_parallel else 0)
 
 
 class TPTrain:
@@ -104,8 +115,12 @@ class TPTrain:
         self.rank = dist.get_rank(group)
         self.full_cfg = full_cfg
         self.with_lm_head, self.with_value_head = with_lm_head, with_value_head
+        # vocabulary-parallel head: this rank's rows [vocab_start, vocab_start + vocab_size / tp) of lm_head.weight
+        self.vocab_parallel = vocab_parallel_head(full_cfg, self.size, with_lm_head)
+        self.vocab_start = self.rank * (full_cfg.vocab_size // self.size) if self.vocab_parallel else 0
         self.entries, self.shard_numel = build_plan(full_cfg, self.rank, self.size, with_lm_head=with_lm_head,
-                                                    with_value_head=with_value_head)
+                                                    with_value_head=with_value_head,
+                                                    vocab_parallel=self.vocab_parallel)
         # GEMM + all-reduce in one kernel for the row-parallel projections of the forward pass (GPU, bf16);
         # OPENRLHF_B200_TP_FUSED=0 falls back to a GEMM followed by an NCCL all-reduce
         import os
@@ -188,7 +203,7 @@ class TPTrain:
         dist.all_gather(shards, model.flat.contiguous(), group=self.group)
         for r in range(self.size):
             entries, _ = build_plan(self.full_cfg, r, self.size, with_lm_head=self.with_lm_head,
-                                    with_value_head=self.with_value_head)
+                                    with_value_head=self.with_value_head, vocab_parallel=self.vocab_parallel)
             for e in entries:            # inverse of full -> shard: destination and source swap roles
                 dst = full.as_strided((e.rows, e.row_elems), (e.src_ld, 1), e.src_off)
                 src = shards[r].as_strided((e.rows, e.row_elems), (e.dst_ld, 1), e.dst_off)
@@ -204,7 +219,8 @@ def shard_for_training(full: TransformerLM, group, shard_world: int = 1) -> Tran
     assert getattr(full, "lora", None) is None, "tensor-parallel training does not cover LoRA adapters"
     assert not full.cfg.is_vlm, "tensor-parallel training does not cover vision-language models"
     ctx = TPTrain(full.cfg, group, full.with_lm_head, full.with_value_head)
-    shard = TransformerLM(local_config(full.cfg, tp), device=full.flat.device, dtype=full.flat.dtype,
+    shard = TransformerLM(local_config(full.cfg, tp, ctx.vocab_parallel), device=full.flat.device,
+                          dtype=full.flat.dtype,
                           with_lm_head=full.with_lm_head, with_value_head=full.with_value_head, seed=None,
                           shard_world=shard_world)
     assert shard.total_numel <= ctx.shard_numel + 128

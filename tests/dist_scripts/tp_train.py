@@ -1,5 +1,5 @@
-"""Tensor-parallel training (column / row parallel shards, differentiable collectives, replicated-gradient averaging,
-TP-aware clipping norm) against the same model trained unsharded: same losses, same gradient norm, same weights after
+"""Tensor-parallel training (column / row parallel shards, vocabulary-parallel head, differentiable collectives,
+replicated-gradient averaging, TP-aware clipping norm) against the same model trained unsharded: same losses, same gradient norm, same weights after
 two optimizer steps with gradient clipping. Runs on CPU ranks (gloo, fp32) and on GPUs (nccl, bf16); world = dp x tp
 with tp = 2."""
 import dataclasses
@@ -81,6 +81,16 @@ def main():
     from openrlhf_b200.models.hf_io import hf_state_dict
 
     sd = hf_state_dict(shard)
+    # the head is vocabulary-parallel: half of the rows per rank, the full matrix in the export, and full logits
+    # (evaluation only) equal to the unsharded model's
+    assert shard.tp_train.vocab_parallel and shard.p("lm_head.weight").shape == (cfg.vocab_size // tp, cfg.hidden_size)
+    assert sd["lm_head.weight"].shape == (cfg.vocab_size, cfg.hidden_size)
+    with torch.no_grad():
+        pb = pack_lists(data[0], device=dev)
+        hs, _ = shard(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+        hr, _ = ref(pb.input_ids, pb.position_ids, pb.cu_seqlens, pb.max_seqlen)
+        ls, lr = shard.logits(hs).float(), ref.logits(hr).float()
+    assert ls.shape == lr.shape and (ls - lr).abs().max().item() < (0.25 if gpu else 1e-3) * lr.abs().max().item()
     assert sd["model.layers.0.self_attn.q_proj.weight"].shape == (cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size)
     assert sd["model.layers.1.mlp.down_proj.weight"].shape == (cfg.hidden_size, cfg.intermediate_size)
     dist.barrier()
