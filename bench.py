@@ -337,6 +337,7 @@ def main():
             "e2e": {"value": P * n * world * e2e_steps / e2e_s, "unit": "samples/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": P * L * 8, "d2h_bytes_per_step": d2h // e2e_steps},
             "gpu_launches": launches,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated(local) / 2 ** 30, 1),     # rank 0's allocator peak
             "impl": "b200",
         }
     # ---- release the GPU before the optional child runs

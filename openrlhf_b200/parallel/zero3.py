@@ -91,13 +91,17 @@ class Zero3Engine:
             self.res_map[s.name] = off
             off += _round(s.numel, ALIGN)
         self.res_size = off
-        self.slot_base = [self.res_size, self.res_size + slot]
-        self.work_size = self.res_size + 2 * slot
+        # parameter slots: two rotating ones, or one per layer when the gathered copy may stay (see _want_persist): a
+        # layer is then gathered once per optimizer step (once ever for a frozen model) instead of twice per
+        # micro-batch; parameters at rest stay sharded either way
+        self.gslots = max(2, min(GRAD_SLOTS, L)) if train else 2
+        self.pslots = L if self._want_persist(L, slot, train) else 2
+        self.slot_base = [self.res_size + k * slot for k in range(self.pslots)]
+        self.work_size = self.res_size + self.pslots * slot
         # gradient slots: layer i accumulates into slot i % G. More slots than parameter slots, so that a layer's
         # reduction (two cross-rank barriers around a pull over NVLink) has G - 1 layers of backward compute to finish
         # in before its slot is needed again; with two slots every rank would run in lockstep with the slowest one
         # at a granularity of one layer.
-        self.gslots = max(2, min(GRAD_SLOTS, L)) if train else 2
         self.gslot_base = [self.res_size + k * slot for k in range(self.gslots)]
         self.slot_width = slot
         self.gwork_size = self.res_size + self.gslots * slot
@@ -150,7 +154,8 @@ class Zero3Engine:
         self.work_off = {}
         for s, p in model.named_specs():
             i = layer_of(s.name)
-            w_off = self.res_map[s.name] if i < 0 else self.slot_base[i % 2] + (s.offset - self.layer_rng[i][0])
+            w_off = (self.res_map[s.name] if i < 0 else
+                     self.slot_base[i % self.pslots] + (s.offset - self.layer_rng[i][0]))
             self.work_off[s.name] = w_off
             p.data = self.work[w_off:w_off + s.numel].view(s.shape)
             if train:
@@ -159,7 +164,7 @@ class Zero3Engine:
         model.flat = self.work          # the logical flat buffer no longer exists on this rank
         model.z3 = self
         del full
-        self.slot_layer = [-1, -1]      # which layer's parameters each slot holds (or is being filled with)
+        self.slot_layer = [-1] * self.pslots   # which layer's parameters each slot holds (or is being filled with)
         self._inflight: dict = {}       # layer -> event of its gather on the side stream
         self._side = None
         self._plans: dict = {}
@@ -172,6 +177,22 @@ class Zero3Engine:
         self.gather_resident()
 
     # ------------------------------------------------------------------------------------------------ plumbing
+    def _want_persist(self, L: int, slot: int, train: bool) -> bool:
+        """Keep every layer's gathered parameters (one slot per layer) instead of rotating two slots? Yes when asked
+        (OPENRLHF_B200_ZERO3_PERSIST=1), never with one rank or when told not to (=0); otherwise on a GPU when what is
+        already allocated plus this engine's own state plus the full bf16 copy stays below 40 % of the device memory
+        (the rest is for activations, the rollout engine and the other models)."""
+        env = os.environ.get("OPENRLHF_B200_ZERO3_PERSIST", "auto")
+        if env == "0" or self.world == 1:
+            return False
+        if env == "1":
+            return True
+        if not self.on_gpu:
+            return False
+        free, total = torch.cuda.mem_get_info(self.device)
+        own = self.per * (18 if train else 2) + (self.res_size + max(2, min(GRAD_SLOTS, L)) * slot) * (4 if train else 0)
+        return (total - free) + own + (self.res_size + L * slot) * 2 < 0.4 * total
+
     def _sync(self, channel: int = 0):
         """All ranks' parameter slices (or gradient slots) are in a consistent state. Barriers issued on the side
         stream of the gradient reductions use their own flag channel and epoch counter: they may execute out of order
@@ -231,17 +252,17 @@ class Zero3Engine:
         """Begin pulling layer i into its slot. On a GPU the copy kernel runs on a side stream, after everything that
         is already enqueued on the compute stream (which includes the last user of that slot), so it overlaps with
         the layer that is about to run."""
-        if self.slot_layer[i % 2] == i:
+        if self.slot_layer[i % self.pslots] == i:
             return
         a, b = self.layer_rng[i]
-        pieces = [(a, b, self.slot_base[i % 2])]
+        pieces = [(a, b, self.slot_base[i % self.pslots])]
         if self.expert_range is not None:
             pieces = []
             e0, e1 = self.expert_range
             for sp in self.model.specs:
                 if not sp.name.startswith(f"layers.{i}."):
                     continue
-                w = self.slot_base[i % 2] + (sp.offset - a)
+                w = self.slot_base[i % self.pslots] + (sp.offset - a)
                 if len(sp.shape) == 3:                       # [experts, rows, cols]: the local experts' block only
                     per_e = sp.shape[1] * sp.shape[2]
                     pieces.append((sp.offset + e0 * per_e, sp.offset + e1 * per_e, w + e0 * per_e))
@@ -263,7 +284,7 @@ class Zero3Engine:
             self._inflight[i] = done
         else:
             self._gather_range(("layer", i), pieces)
-        self.slot_layer[i % 2] = i
+        self.slot_layer[i % self.pslots] = i
 
     def gather_layer(self, i: int):
         """Layer i's parameters are in their slot for everything enqueued on the compute stream after this call."""
@@ -458,7 +479,7 @@ class Zero3Engine:
         for ev in self._inflight.values():
             torch.cuda.current_stream(self.device).wait_event(ev)
         self._inflight.clear()
-        self.slot_layer = [-1, -1]
+        self.slot_layer = [-1] * self.pslots
         self.gather_resident()
         if self.scheduler is not None:
             self.scheduler.step()
@@ -523,5 +544,5 @@ class Zero3Engine:
         self.opt_step = int(opt_step)
         self.param_shard.copy_(self.master.to(self.param_shard.dtype))
         self._sync()
-        self.slot_layer = [-1, -1]
+        self.slot_layer = [-1] * self.pslots
         self.gather_resident()
