@@ -85,3 +85,28 @@ def test_nucleus_settings_are_per_request(model, prompts):
            SamplingParams(temperature=1.0, top_p=1e-6, max_tokens=6, ignore_eos=True)]   # nucleus of one token
     out = eng.generate([prompts[0]] * 3, sps)
     assert out[0].outputs[0].token_ids == out[1].outputs[0].token_ids == out[2].outputs[0].token_ids
+
+
+def test_fixed_length_rows_decode_in_long_bursts_with_identical_outputs(model, prompts):
+    """Rows that ignore EOS can only finish at their token limit, so the engine runs them in bursts of up to eight
+    check intervals once nothing waits for admission or prefill; rows that may stop on EOS keep the short bursts.
+    Same tokens and log-probs either way, far fewer host round trips."""
+    sp_fixed = SamplingParams(temperature=0.0, max_tokens=90, n=1, ignore_eos=True)
+    sp_eos = SamplingParams(temperature=0.0, max_tokens=90, n=1, ignore_eos=False)
+    calls = {}
+    outs = {}
+    for name, sp in (("fixed", sp_fixed), ("eos", sp_eos)):
+        eng = RolloutEngine(model, max_num_seqs=8, max_model_len=512, num_pages=40, check_interval=4,
+                            eos_token_id=-1)            # no token is ever the EOS: both runs generate 90 tokens
+        for i, p in enumerate(prompts[:4]):
+            eng.add_request(i, p, sp)
+        n, done = 0, []
+        while eng.has_unfinished():
+            done += eng.step()
+            n += 1
+        calls[name] = n
+        outs[name] = sorted(done, key=lambda o: o.request_id)
+        assert eng.decode_steps >= 90 - 1
+    _same(outs["fixed"], outs["eos"])
+    # 90 tokens: 23 bursts of 4 steps when a row may stop on EOS, 3-4 bursts of 32 when none can
+    assert calls["eos"] >= 20 and calls["fixed"] <= 6, calls
