@@ -13,7 +13,7 @@ from __future__ import annotations
 import argparse
 import os
 
-from ..runtime.core import ActorGroup, get
+from ..runtime.core import ActorGroup, WorkerDied, get
 from ..utils.strategy import get_strategy
 from . import flags as F
 
@@ -46,6 +46,8 @@ RL_FLAGS = [
     ("--train.max_tokens_per_gpu", int, 16192), ("--train.num_episodes", int, 1), ("--train.max_epochs", int, 1),
     ("--train.micro_batch_size", int, 1), ("--train.batch_size", int, 128), ("--train.seed", int, 42),
     ("--train.full_determinism_enable", B, False), ("--train.agent_func_path", str, None),
+    # not a reference flag: how often a job whose worker died is restarted from its last checkpoint inside this process
+    ("--train.max_restarts", int, 0),
     # rollout
     ("--rollout.max_tokens_per_gpu", int, None), ("--rollout.batch_size", int, 1024),
     ("--rollout.vllm_generate_batch_size", int, None), ("--rollout.micro_batch_size", int, 1),
@@ -197,13 +199,7 @@ def plan_placement(a, has_critic: bool, has_ref: bool, has_reward: bool) -> list
 
 
 def train(args):
-    import copy
-
     import torch
-
-    from ..runtime.core import free_port
-    from ..trainer.ppo_trainer import PPOTrainer, RoleGroups
-    from ..trainer.ppo_trainer_async import PPOTrainerAsync
 
     a = args
     os.environ.setdefault("TOKENIZERS_PARALLELISM", "true")
@@ -223,6 +219,35 @@ def train(args):
               "engines their own GPUs (drop --train.colocate_all) for generation to overlap with training.")
     dup_train = a.ds.ring_attn_size * a.ds.tensor_parallel_size
     tp = max(1, a.vllm.tensor_parallel_size)
+    # Recovery: a dead worker (process exit, missed heartbeats) surfaces as WorkerDied from a future. The reference
+    # leaves the restart to the user (relaunch with --ckpt.load_enable, openrlhf/trainer/ppo_trainer.py:429-442);
+    # with --train.max_restarts N the controller does that itself: it stops every worker of the job, builds the
+    # worker groups again and resumes from the last checkpoint (what was done since that checkpoint is repeated).
+    restarts_left = int(getattr(a.train, "max_restarts", 0) or 0)
+    while True:
+        try:
+            return _run_job(a, strategy, plan, on_gpu, backend, dup_train, tp, has_critic, has_ref, has_reward)
+        except WorkerDied as e:
+            if restarts_left <= 0:
+                raise
+            if not (a.ckpt.path and a.ckpt.save_steps and a.ckpt.save_steps > 0):
+                print("[Warning] a worker died and --train.max_restarts is set, but the job writes no checkpoints "
+                      "(--ckpt.path / --ckpt.save_steps): nothing to resume from", flush=True)
+                raise
+            restarts_left -= 1
+            print(f"[Warning] worker died ({e}); restarting the job from its last checkpoint "
+                  f"({restarts_left} restarts left)", flush=True)
+            a.ckpt.load_enable = True
+
+
+def _run_job(a, strategy, plan, on_gpu, backend, dup_train, tp, has_critic, has_ref, has_reward):
+    """Build the worker groups of one placement plan, train, save; always stops the workers it started."""
+    import copy
+
+    from ..runtime.core import free_port
+    from ..trainer.ppo_trainer import PPOTrainer, RoleGroups
+    from ..trainer.ppo_trainer_async import PPOTrainerAsync
+
     made: dict[str, ActorGroup] = {}
     try:
         for g in plan:

@@ -115,3 +115,42 @@ def test_checkpoint_resume_continues_from_the_saved_step(tmp_path):
     assert r.returncode == 0, log[-3000:]
     steps = [int(m) for m in re.findall(r"^global step (\d+):", r.stdout, flags=re.M)]
     assert steps and steps[0] == 2, steps                               # resumed after step 1, not from scratch
+
+
+def test_worker_death_restarts_the_job_from_its_last_checkpoint(tmp_path):
+    """--train.max_restarts: a worker process that dies in the middle of the run (here: killed on the host by its own
+    reward function, once, during the third rollout) surfaces as WorkerDied in the controller, which stops all
+    workers, starts them again and resumes from the last checkpoint; the run then finishes all its steps."""
+    marker = tmp_path / "died_once"
+    counter = tmp_path / "calls"
+    reward = tmp_path / "reward_func.py"
+    reward.write_text(
+        "import os, torch\n"
+        f"MARKER, COUNTER = {str(marker)!r}, {str(counter)!r}\n"
+        "def reward_func(queries, prompts, labels, **kw):\n"
+        "    fd = os.open(COUNTER, os.O_WRONLY | os.O_CREAT | os.O_APPEND)   # one byte per call, from any thread\n"
+        "    os.write(fd, b'x'); os.close(fd)\n"
+        "    n = os.path.getsize(COUNTER)\n"
+        "    if n > 70 and not os.path.exists(MARKER):      # 32 samples per rollout: inside the third one\n"
+        "        open(MARKER, 'w').write('x')\n"
+        "        os._exit(17)                               # the worker process ends here, on the host\n"
+        "    return {'rewards': torch.tensor([float(len(q) % 2) for q in queries]), 'scores': torch.zeros(len(queries)),\n"
+        "            'extra_logs': {}}\n")
+    ck = str(tmp_path / "ckpt")
+    common = [c for c in COMMON]
+    common[common.index("--reward.remote_url") + 1] = str(reward)
+    common[common.index("--data.max_samples") + 1] = "32"            # four rollouts of 8 prompts
+    cmd = [sys.executable, "-m", "openrlhf.cli.train_ppo_ray", *common, "--actor.num_gpus_per_node", "1",
+           "--train.colocate_all", "--actor.model_name_or_path", "tiny-qwen2", "--ds.zero_stage", "2",
+           "--algo.kl.init_coef", "0", "--ckpt.path", ck, "--ckpt.save_steps", "1", "--train.max_restarts", "1",
+           "--ckpt.output_dir", str(tmp_path / "out")]
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), OMP_NUM_THREADS="2",
+               CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    log = r.stdout + r.stderr
+    assert r.returncode == 0, log[-4000:]
+    assert marker.exists() and "restarting the job from its last checkpoint" in log, log[-4000:]
+    steps = [int(m) for m in re.findall(r"^global step (\d+):", r.stdout, flags=re.M)]
+    # steps before the death, then the resumed run continues after the last checkpointed step up to the last one
+    assert steps[-1] == 4 and steps.count(1) == 1 and len(steps) >= 4, steps
+    assert os.path.exists(os.path.join(str(tmp_path / "out"), "config.json"))
