@@ -74,7 +74,8 @@ def _time(fn, iters: int, flush: bool | None = None) -> float:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True, choices=["gemm", "gemm_fp8", "gemm_splitk", "gemm_swiglu", "decode_attn", "attn_fwd", "attn_bwd", "logprob", "logprob_bwd",
-                                                         "rmsnorm", "adamw", "decode_step", "decode_gemms"])
+                                                         "rmsnorm", "adamw", "decode_step", "decode_gemms", "sample", "ppo_loss", "gae"])
+    ap.add_argument("--top-p", type=float, default=1.0, help="sample: nucleus threshold (1.0: plain Gumbel-max pass)")
     ap.add_argument("--model", default="qwen2.5-1.5b", help="decode_step: model preset")
     ap.add_argument("--layers", type=int, default=0, help="decode_step: cut the preset to this many layers (0: all)")
     ap.add_argument("--pdl", action="store_true", help="decode_step: launch the fused layers as a dependent-launch chain")
@@ -194,6 +195,51 @@ def main():
         byt = B_ * ctx * 2 * Hkv * 128 * 2
         print(f"decode_attn B{B_} Hq{Hq} Hkv{Hkv} ctx{ctx} splits{a.splits}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s "
               f"({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "sample":
+        # sampler of the rollout engine over [batch, vocabulary] bf16 logits (--n: vocabulary size)
+        from openrlhf_b200.ops.sampling import sample
+        B, V = a.batch, a.n
+        logits = torch.randn(max(B, (300 << 20) // (2 * V) + B), V, device=dev, dtype=torch.bfloat16)   # > L2
+        toks = torch.zeros(B, dtype=torch.int64, device=dev)
+        lps = torch.zeros(B, dtype=torch.float32, device=dev)
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + B) % (logits.shape[0] - B + 1)
+            return sample(logits[turn[0]:turn[0] + B], temperature=1.0, top_k=-1, top_p=a.top_p, seed=1, step=turn[0],
+                          out_tokens=toks, out_logprobs=lps)
+        t = _time(fn, a.iters)
+        byt = 2.0 * B * V
+        print(f"sample B{B} V{V} top_p{a.top_p}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s of logits "
+              f"({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "ppo_loss":
+        # fused clipped-surrogate loss + k3 KL + metrics over [sequences, action tokens] fp32 (--m x --n), forward and
+        # backward (the backward is a scale of the dlogp the forward kernel already wrote)
+        from openrlhf_b200.ops.rl import ppo_loss
+        Bq, A = a.m, a.n
+        logp = (-torch.rand(Bq, A, device=dev)).requires_grad_()
+        old = logp.detach() + 0.05 * torch.randn(Bq, A, device=dev)
+        ref = logp.detach() + 0.05 * torch.randn(Bq, A, device=dev)
+        adv = torch.randn(Bq, A, device=dev)
+        mask = (torch.rand(Bq, A, device=dev) > 0.1).float()
+
+        def fn():
+            logp.grad = None
+            out = ppo_loss(logp, old, adv, mask, ref_logp=ref, kl_coef=0.001, kl_estimator="k3")
+            out["loss"].backward()
+        t = _time(fn, a.iters)
+        byt = 4.0 * Bq * A * 7          # five inputs read, dlogp written and read once more by the backward scale
+        print(f"ppo_loss fwd+bwd B{Bq} A{A}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
+    elif a.kernel == "gae":
+        # reward shaping + GAE scan over [sequences, action tokens] fp32 (--m x --n)
+        from openrlhf_b200.ops.rl import gae_advantages
+        Bq, A = a.m, a.n
+        values, kl = torch.randn(Bq, A, device=dev), 0.01 * torch.randn(Bq, A, device=dev)
+        mask = torch.ones(Bq, A, device=dev)
+        rew = torch.randn(Bq, device=dev)
+        t = _time(lambda: gae_advantages(values, kl, rew, mask, beta=0.01, gamma=1.0, lambd=0.95), a.iters)
+        byt = 4.0 * Bq * A * 5
+        print(f"gae B{Bq} A{A}: {t * 1e6:.1f} us, {byt / t / 1e9:.0f} GB/s ({byt / t / 1e9 / hbm:.2f} {tag} HBM)")
     elif a.kernel == "decode_gemms":
         # the four projections of one decoder layer at decode batch size, launched exactly as the rollout engine
         # launches them (split-K into the fp32 workspace / SwiGLU epilogue), over distinct weights in turn so that
