@@ -3,8 +3,6 @@ prompts go through the chat template (with a generation prompt) or ``input_templ
 VLM content lists."""
 from __future__ import annotations
 
-import copy
-
 from torch.utils.data import Dataset
 
 
@@ -21,46 +19,42 @@ def _with_image_parts(text: str):
     return content
 
 
-def preprocess_data(data, input_template=None, input_key="input", label_key=None, apply_chat_template=None):
-    if apply_chat_template:
-        chat = data[input_key]
-        if isinstance(chat, str):
-            chat = [{"role": "user", "content": _with_image_parts(chat)}]
-        else:
-            chat = copy.deepcopy(chat)
-            for msg in chat:
-                if isinstance(msg.get("content"), str):
-                    msg["content"] = _with_image_parts(msg["content"])
-        prompt = apply_chat_template(chat, tokenize=False, add_generation_prompt=True)
+def render_prompt(row: dict, input_key: str, chat, template: str | None) -> str:
+    """The text a rollout engine is prompted with: the chat template with a generation prompt (string inputs become a
+    single user message; ``<image>`` tags become content parts), or the plain input through ``template.format``."""
+    value = row[input_key]
+    if chat is None:
+        return template.format(value) if template else value
+    if isinstance(value, str):
+        messages = [{"role": "user", "content": _with_image_parts(value)}]
     else:
-        prompt = data[input_key]
-        if input_template:
-            prompt = input_template.format(prompt)
-    return prompt, ("" if label_key is None else data[label_key])
+        messages = [dict(m, content=_with_image_parts(m["content"])) if isinstance(m.get("content"), str) else dict(m)
+                    for m in value]
+    return chat(messages, tokenize=False, add_generation_prompt=True)
 
 
 class PromptDataset(Dataset):
+    """Items are (datasource, prompt text, label, images), rendered once at construction."""
+
     def __init__(self, dataset, tokenizer, strategy, input_template=None) -> None:
         super().__init__()
         self.strategy, self.tokenizer, self.input_template = strategy, tokenizer, input_template
         d = strategy.args.data
         input_key, label_key = getattr(d, "input_key", None), getattr(d, "label_key", None)
-        tmpl = tokenizer.apply_chat_template if getattr(d, "apply_chat_template", False) else None
+        chat = tokenizer.apply_chat_template if getattr(d, "apply_chat_template", False) else None
         self.image_key = getattr(d, "image_key", "images")
-        self.prompts, self.labels, self.images, self.datasources = [], [], [], []
-        for row in dataset:
-            p, l = preprocess_data(row, input_template, input_key, label_key, tmpl)
-            self.prompts.append(p)
-            self.labels.append(l)
-            self.images.append(row.get(self.image_key, None))
-            self.datasources.append(row.get("datasource", "default"))
+        self.items = [(row.get("datasource", "default"), render_prompt(row, input_key, chat, input_template),
+                       "" if label_key is None else row[label_key], row.get(self.image_key, None))
+                      for row in dataset]
 
     def __len__(self):
-        return len(self.prompts)
+        return len(self.items)
 
     def __getitem__(self, idx):
-        return self.datasources[idx], self.prompts[idx], self.labels[idx], self.images[idx]
+        return self.items[idx]
 
     def collate_fn(self, item_list):
-        cols = list(zip(*item_list)) if item_list else [(), (), (), ()]
-        return tuple(list(c) for c in cols)
+        if not item_list:
+            return [], [], [], []
+        sources, prompts, labels, images = (list(col) for col in zip(*item_list))
+        return sources, prompts, labels, images

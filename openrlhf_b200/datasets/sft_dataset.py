@@ -1,5 +1,16 @@
-"""SFT dataset (openrlhf/datasets/sft_dataset.py:35-228): prompt/response split (chat-template prefix trick), multi-turn
-response ranges, loss mask on ``[prompt_len-1 : -1]``, forced EOS as last token, right-pad collate, pretrain mode."""
+"""Supervised fine-tuning dataset.
+
+Every row is encoded once, when the dataset is built: the row is rendered to its full training text together with the
+character spans the model is trained to produce (the response of a prompt / response pair, every assistant turn of a
+conversation, or everything in pre-training mode), the text is tokenised, the spans become token spans, and the item
+that ``__getitem__`` returns is assembled from those stored ids and spans without touching the tokenizer again.
+
+Behaviour follows the reference's SFT dataset (openrlhf/datasets/sft_dataset.py:35-228): the chat-template prefix
+trick separates prompt from response (the response is what the template adds after the generation prompt), rows with
+an empty side or a prompt that nearly fills ``max_length`` are dropped, the text ends with the EOS token, a truncated
+sample still ends with a real EOS id, and the loss mask is shifted by one position (position t is trained to predict
+token t + 1), so a span of target tokens [a, b) sets mask[a - 1 : b - 1].
+"""
 from __future__ import annotations
 
 from typing import Callable
@@ -10,23 +21,48 @@ from torch.utils.data import Dataset
 from ..rl.experience import pad_stack
 
 
-def preprocess_data(data, input_template=None, input_key="input", output_key=None, apply_chat_template=None):
-    if apply_chat_template:
+def render_row(row: dict, *, input_key: str, output_key: str | None, template: str | None, chat: Callable | None,
+               multiturn: bool, pretrain: bool) -> tuple[str, str, list[tuple[int, int]]]:
+    """(prompt text, full text, character spans of the target parts inside the full text) of one row.
+
+    Pre-training rows are their raw input and one span over all of it. Prompt / response rows have one span: the
+    response. Conversations (``multiturn``) have one span per assistant message, found with the template-prefix trick:
+    the text of the conversation up to and including the message, minus the text up to the message with the
+    generation prompt appended."""
+    if pretrain:
+        text = row[input_key]
+        return "", text, [(0, len(text))]
+    if multiturn:
+        msgs = list(row[input_key])
+        if output_key and row.get(output_key):
+            msgs.append(row[output_key])           # a trajectory whose last assistant turn sits in its own column
+        full = chat(msgs, tokenize=False)
+        spans = []
+        for i, m in enumerate(msgs):
+            if m["role"] == "assistant":
+                head = chat(msgs[:i], tokenize=False, add_generation_prompt=True)
+                upto = chat(msgs[:i + 1], tokenize=False)
+                spans.append((len(head), len(upto)))
+        prompt = chat(msgs[:-1], tokenize=False, add_generation_prompt=True)
+        return prompt, full, spans
+    if chat is not None:
+        turns = row[input_key]
         if output_key:
-            p, r = data[input_key], data[output_key]
-            if isinstance(p, str) and isinstance(r, str):
-                p, r = [{"role": "user", "content": p}], [{"role": "assistant", "content": r}]
-            prompt = apply_chat_template(p, tokenize=False, add_generation_prompt=True)
-            response = apply_chat_template(p + r, tokenize=False)[len(prompt):]
+            reply = row[output_key]
+            if isinstance(turns, str) and isinstance(reply, str):
+                turns, reply = [{"role": "user", "content": turns}], [{"role": "assistant", "content": reply}]
+            prompt = chat(turns, tokenize=False, add_generation_prompt=True)
+            full = chat(turns + reply, tokenize=False)
         else:
-            prompt = apply_chat_template(data[input_key][:-1], tokenize=False, add_generation_prompt=True)
-            response = apply_chat_template(data[input_key], tokenize=False)[len(prompt):]
+            prompt = chat(turns[:-1], tokenize=False, add_generation_prompt=True)
+            full = chat(turns, tokenize=False)
+        full = prompt + full[len(prompt):]
     else:
-        prompt = data[input_key]
-        if input_template:
-            prompt = input_template.format(prompt)
-        response = data[output_key] if output_key else ""
-    return prompt, response
+        prompt = row[input_key]
+        if template:
+            prompt = template.format(prompt)
+        full = prompt + (row[output_key] if output_key else "")
+    return prompt, full, [(len(prompt), len(full))]
 
 
 class SFTDataset(Dataset):
@@ -34,79 +70,71 @@ class SFTDataset(Dataset):
                  pretrain_mode: bool = False, num_processors: int = 8, multiturn: bool = False) -> None:
         super().__init__()
         self.tokenizer, self.strategy, self.max_length = tokenizer, strategy, max_length
-        self.pretrain_mode, self.multiturn, self.input_template = pretrain_mode, multiturn, input_template
+        self.pretrain_mode, self.multiturn = pretrain_mode, multiturn
         d = strategy.args.data
-        self.input_key, self.output_key = getattr(d, "input_key", None), getattr(d, "output_key", None)
-        self.apply_chat_template = None
-        if getattr(d, "apply_chat_template", False):
-            self.apply_chat_template = tokenizer.apply_chat_template
+        chat = None
+        if getattr(d, "apply_chat_template", False) and not pretrain_mode:
+            chat = tokenizer.apply_chat_template
             if getattr(d, "tokenizer_chat_template", None):
                 tokenizer.chat_template = d.tokenizer_chat_template
-        rows = dataset.map(self.process_data, remove_columns=dataset.column_names, num_proc=num_processors)
-        rows = rows.filter(lambda x: x["prompt"] is not None)
-        self.prompts, self.responses = rows["prompt"], rows["response"]
-        self.prompt_ids_lens = rows["prompt_ids_len"]
-        self.response_ranges = rows["response_ranges"] if multiturn else None
+        if multiturn:
+            assert chat is not None, "multi-turn rows are rendered with the tokenizer's chat template"
+        self._render = dict(input_key=getattr(d, "input_key", None), output_key=getattr(d, "output_key", None),
+                            template=None if pretrain_mode else input_template, chat=chat, multiturn=multiturn,
+                            pretrain=pretrain_mode)
+        rows = dataset.map(self._encode, remove_columns=dataset.column_names, num_proc=num_processors)
+        rows = rows.filter(lambda r: r["keep"])
+        self.input_ids, self.target_spans = rows["input_ids"], rows["target_spans"]
 
-    def _ntok(self, text: str) -> int:
-        t = self.tokenizer(text, max_length=self.max_length, padding=False, truncation=True, return_tensors="pt",
-                           add_special_tokens=False)
-        return int(t["attention_mask"].int().sum().item())
+    # ------------------------------------------------------------------ construction-time encoding
+    def _ids(self, text: str) -> list[int]:
+        out = self.tokenizer(text, max_length=self.max_length, padding=False, truncation=True, add_special_tokens=False)
+        ids = out["input_ids"]
+        return list(ids[0]) if ids and isinstance(ids[0], (list, tuple)) else list(ids)
 
-    def process_data(self, data):
-        ranges = None
-        if self.multiturn and self.output_key:
-            data[self.input_key].append(data[self.output_key])
-            data[self.output_key] = None
-        if self.multiturn:
-            if self.output_key and data[self.output_key]:
-                raise AssertionError("put the whole trajectory into data[input_key]; do not set output_key")
-            ranges = []
-            msgs = data[self.input_key]
-            for i, m in enumerate(msgs):
-                if m["role"] != "assistant":
-                    continue
-                before = self.apply_chat_template(msgs[:i], tokenize=False, add_generation_prompt=True)
-                reply = self.apply_chat_template(msgs[:i + 1], tokenize=False)[len(before):]
-                start = self._ntok(before)
-                ranges.append((start, start + self._ntok(reply) - 1))      # closed interval
-        prompt, response = preprocess_data(data, None if self.pretrain_mode else self.input_template, self.input_key,
-                                           self.output_key, None if self.pretrain_mode else self.apply_chat_template)
-        n_prompt = 0
+    def _encode(self, row):
+        prompt, text, spans = render_row(row, **self._render)
+        empty = {"input_ids": [], "target_spans": [], "keep": False}
         if not self.pretrain_mode:
-            n_prompt = self._ntok(prompt)
-            if not prompt or not response or n_prompt >= self.max_length - 2:
-                prompt = None
-        return {"prompt": prompt, "response": response, "prompt_ids_len": n_prompt, "response_ranges": ranges}
-
-    def __len__(self):
-        return len(self.prompts)
-
-    def __getitem__(self, idx):
-        text = self.prompts[idx]
-        if not self.pretrain_mode:
-            text = (text + self.responses[idx]).rstrip("\n")
+            if not prompt or all(b <= a for a, b in spans):
+                return empty                                   # nothing to condition on, or nothing to learn
+            # the text ends with the EOS token (outside the template's own spans in a conversation, inside the
+            # response span of a prompt / response pair)
+            stripped = text.rstrip("\n")
+            spans = [(min(a, len(stripped)), min(b, len(stripped))) for a, b in spans]
+            text = stripped
             if not text.endswith(self.tokenizer.eos_token):
                 text += " " + self.tokenizer.eos_token
-        tok = self.tokenizer(text, max_length=self.max_length, padding=False, truncation=True, return_tensors="pt",
-                             add_special_tokens=False)
-        ids, att = tok["input_ids"], tok["attention_mask"]
-        mask = self.get_loss_mask(ids, idx)
-        if not self.pretrain_mode:                       # survive truncation with a real EOS at the end
-            ids[0][-1] = self.tokenizer.eos_token_id
-            att[0][-1] = True
-        return ids, att, mask
+            if not self.multiturn:
+                spans = [(spans[0][0], len(text))]
+            if len(self._ids(prompt)) >= self.max_length - 2:
+                return empty                                   # the prompt alone (nearly) fills the window
+        ids = self._ids(text)
+        # character spans -> token spans: tokens of the text before the span, then tokens of the span itself (the
+        # boundaries produced by chat templates fall between tokens)
+        tok_spans = []
+        for a, b in spans:
+            start = len(self._ids(text[:a])) if a > 0 else 0
+            stop = len(ids) if b >= len(text) and not self.multiturn else start + len(self._ids(text[a:b]))
+            tok_spans.append((min(start, len(ids)), min(stop, len(ids))))
+        if not self.pretrain_mode and ids:
+            ids[-1] = self.tokenizer.eos_token_id               # a truncated sample still ends with a real EOS
+        return {"input_ids": ids, "target_spans": tok_spans, "keep": len(ids) > 0}
 
-    def get_loss_mask(self, input_ids, idx):
+    # ------------------------------------------------------------------ items
+    def __len__(self):
+        return len(self.input_ids)
+
+    def __getitem__(self, idx):
+        ids = torch.tensor(self.input_ids[idx], dtype=torch.long).unsqueeze(0)
+        att = torch.ones_like(ids)
         if self.pretrain_mode:
-            return torch.ones_like(input_ids, dtype=torch.float32)
-        m = torch.zeros_like(input_ids, dtype=torch.float32)
-        if not self.multiturn:
-            m[0, self.prompt_ids_lens[idx] - 1:-1] = 1
-        else:
-            for a, b in self.response_ranges[idx]:
-                m[0, a - 1:b] = 1
-        return m
+            return ids, att, torch.ones_like(ids, dtype=torch.float32)
+        mask = torch.zeros_like(ids, dtype=torch.float32)
+        for a, b in self.target_spans[idx]:
+            if b > max(a, 1):
+                mask[0, max(a, 1) - 1:b - 1] = 1                # position t predicts token t + 1
+        return ids, att, mask
 
     def collate_fn(self, item_list):
         ids, att, mask = zip(*item_list)

@@ -113,3 +113,59 @@ def test_sharded_checkpoint_round_trip_and_fault_injection(tmp_path):
     with pytest.raises(Exception):
         ckpt.load_sharded(_engine(seed=2)[1], d)
     assert ckpt.load_sharded(_engine(seed=2)[1], str(tmp_path / "nothing"))[0] is None
+
+
+class _ListDataset:
+    """Minimal stand-in for a datasets.Dataset (map / filter / column access) over a list of dict rows."""
+
+    def __init__(self, rows):
+        self.rows = rows
+        self.column_names = sorted({k for r in rows for k in r})
+
+    def map(self, fn, remove_columns=None, num_proc=None):
+        return _ListDataset([fn(dict(r)) for r in self.rows])
+
+    def filter(self, fn):
+        return _ListDataset([r for r in self.rows if fn(r)])
+
+    def __getitem__(self, key):
+        return [r[key] for r in self.rows]
+
+    def __len__(self):
+        return len(self.rows)
+
+
+def test_sft_dataset_multiturn_pretrain_and_truncation():
+    """Conversations: the loss covers every assistant turn and nothing else (shifted by one position). Pre-training
+    rows: the loss covers everything. A sample longer than max_length is cut and still ends with a real EOS id; a row
+    whose prompt nearly fills the window is dropped."""
+    tok = SyntheticTokenizer(1000)
+    s = _Strategy()
+    s.args = _args(apply_chat_template=True, output_key=None)
+    conv = [{"role": "user", "content": "11 12 13"}, {"role": "assistant", "content": "21 22"},
+            {"role": "user", "content": "31"}, {"role": "assistant", "content": "41 42 43"}]
+    ds = SFTDataset(_ListDataset([{"input": conv}]), tok, 64, s, multiturn=True)
+    ids, att, mask = ds[0]
+    assert ids[0].tolist() == [11, 12, 13, 21, 22, 31, 41, 42, 43, tok.eos_token_id]
+    toks = ids[0].tolist()
+    # position t is trained iff token t + 1 belongs to an assistant turn
+    want = [1.0 if toks[t + 1] in (21, 22, 41, 42, 43) else 0.0 for t in range(len(toks) - 1)] + [0.0]
+    assert mask[0].tolist() == want and att.all()
+
+    s2 = _Strategy()
+    s2.args = _args(output_key=None)
+    pre = SFTDataset(_ListDataset([{"input": " ".join(str(i) for i in range(100, 140))}]), tok, 16, s2,
+                     pretrain_mode=True)
+    ids, att, mask = pre[0]
+    assert ids.shape == (1, 16) and mask.sum() == 16 and ids[0, -1] == 115      # cut, no EOS forced, loss everywhere
+
+    s3 = _Strategy()
+    s3.args = _args()
+    rows = [{"input": " ".join(str(i) for i in range(200, 210)), "output": " ".join(str(i) for i in range(300, 330))},
+            {"input": " ".join(str(i) for i in range(400, 415)), "output": "5"},          # prompt of 15 >= 16 - 2
+            {"input": "7 8", "output": ""}]                                                # nothing to learn
+    cut = SFTDataset(_ListDataset(rows), tok, 16, s3)
+    assert len(cut) == 1
+    ids, att, mask = cut[0]
+    assert ids.shape == (1, 16) and int(ids[0, -1]) == tok.eos_token_id
+    assert mask[0].tolist() == [0.0] * 9 + [1.0] * 6 + [0.0]           # positions prompt_len - 1 .. L - 2
