@@ -198,11 +198,23 @@ def plan_placement(a, has_critic: bool, has_ref: bool, has_reward: bool) -> list
     return groups
 
 
+# Environment of the controller and, by inheritance, of every worker process it starts; a value the user exported wins
+# (the reference passes the same defaults to its actors: openrlhf/cli/train_ppo_ray.py, runtime_env of ray.init).
+ENV_DEFAULTS = {"TOKENIZERS_PARALLELISM": "true", "NCCL_DEBUG": "WARN"}
+
+
+def apply_env_defaults(environ=None) -> dict:
+    environ = os.environ if environ is None else environ
+    for key, value in ENV_DEFAULTS.items():
+        environ.setdefault(key, value)
+    return {k: environ[k] for k in ENV_DEFAULTS}
+
+
 def train(args):
     import torch
 
     a = args
-    os.environ.setdefault("TOKENIZERS_PARALLELISM", "true")
+    apply_env_defaults()
     strategy = get_strategy(a)                      # controller-side copy: flags + CPU helpers, no process group
     has_critic = a.critic.model_name_or_path is not None
     has_ref = a.algo.kl.init_coef > 0

@@ -154,3 +154,11 @@ def test_worker_death_restarts_the_job_from_its_last_checkpoint(tmp_path):
     # steps before the death, then the resumed run continues after the last checkpointed step up to the last one
     assert steps[-1] == 4 and steps.count(1) == 1 and len(steps) >= 4, steps
     assert os.path.exists(os.path.join(str(tmp_path / "out"), "config.json"))
+
+
+def test_worker_environment_defaults_yield_to_the_user():
+    from openrlhf_b200.cli.train_ppo_ray import apply_env_defaults
+
+    assert apply_env_defaults({}) == {"TOKENIZERS_PARALLELISM": "true", "NCCL_DEBUG": "WARN"}
+    user = {"NCCL_DEBUG": "INFO", "TOKENIZERS_PARALLELISM": "false", "OTHER": "1"}
+    assert apply_env_defaults(user) == {"TOKENIZERS_PARALLELISM": "false", "NCCL_DEBUG": "INFO"} and user["OTHER"] == "1"
