@@ -1,5 +1,6 @@
-"""ZeRO-3 engine (sharded parameters, layer slots, per-layer gradient reduction) against the ZeRO-2 engine on the same
-data: identical parameters after two optimizer steps with gradient accumulation. Two gloo ranks, and one rank."""
+"""ZeRO-3 engine (sharded parameters, rotating or persistent layer slots, per-layer gradient reduction) against the
+ZeRO-2 engine on the same data: identical parameters after two optimizer steps with gradient accumulation. Two gloo
+ranks, and one rank."""
 import os
 
 import pytest
@@ -53,11 +54,15 @@ def _rank_main(rank, world, port, q, ckpt):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("ckpt", [False, True])
-def test_zero3_matches_zero2_two_ranks(ckpt):
+@pytest.mark.parametrize("ckpt,persist", [(False, "0"), (True, "0"), (False, "1"), (True, "1")])
+def test_zero3_matches_zero2_two_ranks(ckpt, persist, monkeypatch):
+    """persist = "1": every layer keeps its gathered parameters in a slot of its own between optimizer steps (gathered
+    once per step instead of twice per micro-batch); "0": two rotating slots. Same result either way."""
+    monkeypatch.setenv("OPENRLHF_B200_ZERO3_PERSIST", persist)       # inherited by the spawned ranks
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, 29745 + int(ckpt), q, ckpt)) for r in range(2)]
+    port = 29745 + int(ckpt) + 2 * int(persist)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, ckpt)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
