@@ -345,6 +345,12 @@ class WorkerHandle:
             self.proc.terminate()
 
 
+def batch_engine_call(engines: list, method_name: str, *args, **kwargs) -> list:
+    """Call the same method on every engine handle and gather the results (the reference's batch_vllm_engine_call,
+    openrlhf/trainer/ray/vllm_engine.py:316-329)."""
+    return get([e.call(method_name, *args, **kwargs) for e in engines])
+
+
 def free_port() -> int:
     import socket
 

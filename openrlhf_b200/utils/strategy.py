@@ -464,6 +464,11 @@ class Strategy:
 DeepspeedStrategy = Strategy  # the name user code written against the reference imports
 
 
+# the reference's name of this class (openrlhf/utils/deepspeed/deepspeed.py): user code that type-checks or subclasses
+# `DeepspeedStrategy` keeps working
+DeepspeedStrategy = Strategy
+
+
 def get_strategy(args) -> Strategy:
     """Build the strategy from the hierarchical flag namespace (openrlhf/utils/utils.py:25-37)."""
     train = getattr(args, "train", SimpleNamespace())

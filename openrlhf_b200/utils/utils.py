@@ -246,3 +246,11 @@ def zero_pad_sequences(sequences: List[torch.Tensor], side: str = "left", value:
 def remove_pad_token(input_ids: torch.Tensor, attention_mask: torch.Tensor):
     """Per-row token tensors with the padding (left or right) removed."""
     return [ids[mask.bool()] for ids, mask in zip(input_ids, attention_mask)]
+
+
+def get_strategy(args):
+    """The strategy object of a parsed flag namespace (the reference exposes it from this module:
+    openrlhf/utils/utils.py); built in utils/strategy.py."""
+    from .strategy import get_strategy as build
+
+    return build(args)

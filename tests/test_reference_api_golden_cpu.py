@@ -71,3 +71,42 @@ def test_gradient_accumulation_window_is_normalised_by_its_global_token_count():
     assert float(total) == pytest.approx(28. / 7.)                                # one token mean over the window
     per_micro = (aggregate_loss(*micro[0]) + aggregate_loss(*micro[1])) / 2
     assert float(per_micro) != pytest.approx(28. / 7.)                            # (1.5 + 5) / 2: not the same thing
+
+
+def test_reference_import_paths_resolve_to_this_package():
+    """Module paths and public names a user of the reference imports (its __init__ export lists, the places its RL
+    utilities live, the strategy class name) resolve to the same module objects as this package's own paths."""
+    import importlib
+
+    expected = {
+        "openrlhf.models": ["Actor", "SFTLoss", "DPOLoss", "GPTLMLoss", "LogExpLoss", "PairWiseLoss", "PolicyLoss",
+                            "ValueLoss", "aggregate_loss", "get_llm_for_sequence_regression"],
+        "openrlhf.datasets": ["PromptDataset", "RewardDataset", "SFTDataset"],
+        "openrlhf.utils": ["extract_boxed_answer", "grade_answer", "get_strategy", "get_tokenizer"],
+        "openrlhf.utils.utils": ["get_strategy", "get_tokenizer"],
+        "openrlhf.utils.agent": ["AgentExecutorBase", "AgentInstanceBase"],
+        "openrlhf.utils.deepspeed": ["DeepspeedStrategy"],
+        "openrlhf.trainer.ppo_utils": ["AdaptiveKLController", "Experience", "FixedKLController", "NaiveReplayBuffer",
+                                       "apply_length_penalties", "apply_overlong_penalty",
+                                       "apply_stop_properly_penalty", "balance_experiences", "make_experience_batch",
+                                       "split_experience_batch"],
+        "openrlhf.trainer.ppo_utils.experience_maker": [],
+        "openrlhf.trainer.ppo_utils.samples_generator": ["SamplesGenerator"],
+        "openrlhf.trainer.ppo_trainer": ["PPOTrainer"],
+        "openrlhf.trainer.ppo_trainer_async": ["PPOTrainerAsync"],
+        "openrlhf.trainer.sft_trainer": ["SFTTrainer"],
+        "openrlhf.trainer.rm_trainer": ["RewardModelTrainer"],
+        "openrlhf.trainer.dpo_trainer": ["DPOTrainer"],
+        "openrlhf.trainer.ray": ["batch_vllm_engine_call"],
+        "openrlhf.trainer.ray.launcher": ["RayActorGroup"],
+    }
+    for path, names in expected.items():
+        mod = importlib.import_module(path)
+        missing = [n for n in names if not hasattr(mod, n)]
+        assert not missing, (path, missing)
+    import openrlhf.trainer.ppo_utils.experience as old_path
+    import openrlhf_b200.rl.experience as new_path
+    from openrlhf.utils.deepspeed import DeepspeedStrategy
+    from openrlhf_b200.utils.strategy import Strategy
+
+    assert old_path is new_path and DeepspeedStrategy is Strategy
