@@ -69,6 +69,22 @@ class Actor(nn.Module):
     def gradient_checkpointing_disable(self):
         self.model.gradient_checkpointing = False
 
+    def print_trainable_parameters(self):
+        """One line with the trainable and total parameter counts (LoRA adapters included), like the PEFT helper the
+        reference forwards to (openrlhf/models/actor.py:304-305). Returns (trainable, total)."""
+        total = trainable = 0
+        for _, p in self.model.named_specs():
+            total += p.numel()
+            trainable += p.numel() if p.requires_grad else 0
+        lora = getattr(self.model, "lora", None)
+        if lora is not None:
+            n = sum(p.numel() for p in lora.parameters())
+            total += n
+            trainable += sum(p.numel() for p in lora.parameters() if p.requires_grad)
+        print(f"trainable params: {trainable:,} || all params: {total:,} || trainable%: "
+              f"{100.0 * trainable / max(total, 1):.4f}")
+        return trainable, total
+
     # ------------------------------------------------------------------ native packed API
     def forward_packed(self, pb: PackedBatch, return_entropy: bool = False, context_parallel=None,
                        pixel_values=None, image_grid_thw=None):

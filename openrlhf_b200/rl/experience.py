@@ -43,6 +43,16 @@ def _map_tensors(obj, fn):
     return obj
 
 
+def to(obj, device):
+    """Tensors inside `obj` (a tensor, or lists / dicts of them) moved to `device`; everything else is returned as is."""
+    return _map_tensors(obj, lambda t: t.to(device))
+
+
+def pin_memory(obj):
+    """Tensors inside `obj` copied into page-locked host memory (for asynchronous host-to-device copies)."""
+    return _map_tensors(obj, lambda t: t.pin_memory())
+
+
 @dataclass
 class Experience:
     # trajectory

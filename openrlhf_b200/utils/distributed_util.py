@@ -54,3 +54,11 @@ def stateless_process_group(host: str, port: int, rank: int, world: int, backend
         opts._timeout = to
         return dist.ProcessGroupNCCL(store, rank, world, opts)
     raise ValueError(f"unknown backend {backend}")
+
+
+def stateless_init_process_group(master_address, master_port, rank, world_size, device):
+    """Same call as the reference's helper of this name (openrlhf/utils/distributed_util.py:13-26): a communicator
+    between training processes and rollout workers that is independent of the default process group. NCCL for a
+    CUDA device, gloo otherwise."""
+    backend = "nccl" if device is not None and torch.device(device).type == "cuda" else "gloo"
+    return stateless_process_group(master_address, master_port, rank, world_size, backend=backend, device=device)

@@ -111,10 +111,19 @@ def _normalize(expr):
     return expr.strip().lower() if len(expr) > 1 else expr.strip()
 
 
+def count_unknown_letters_in_expr(expr: str) -> int:
+    """Distinct letters that are not part of a known function or constant name: free symbols sympy would have to carry."""
+    return len(set(re.findall(r"[a-zA-Z]", re.sub(r"sqrt|frac|pi|oo", "", expr))))
+
+
 def should_allow_eval(expr: str) -> bool:
-    if len(set(re.findall(r"[a-zA-Z]", re.sub(r"sqrt|frac|pi|oo", "", expr)))) > 2:
+    """Expressions handed to sympy stay small: at most two free symbols, no braced / parenthesised or chained powers,
+    no exponent of two or more digits (a tower like 9^99^9 would run until the time limit), no Python syntax."""
+    if count_unknown_letters_in_expr(expr) > 2:
         return False
-    return not any(b in expr for b in ("^{", "^(", "__", "import", "lambda"))
+    if any(b in expr for b in ("^{", "^(", "__", "import", "lambda")):
+        return False
+    return re.search(r"\^[0-9]+\^|\^[0-9][0-9]+", expr) is None
 
 
 def are_equal_under_sympy(ground_truth_normalized: str, given_normalized: str, timeout: int = 120) -> bool:
