@@ -193,6 +193,7 @@ class RolloutEngine:
         self.sleeping = False
         self.paused = False
         self.decode_steps = 0
+        self._quiet_bursts = 0     # consecutive decode bursts in which no row finished and nothing was waiting
         # scheduler state: admission order, chunked-prefill budget, prefix cache, preemption counters
         self.max_prefill_tokens = max(int(max_prefill_tokens), PAGE)
         self._order = 0
@@ -858,7 +859,12 @@ class RolloutEngine:
         # (only while nothing waits for admission or for its next prefill chunk)
         busy = bool(self.waiting) or any(r is not None and r.prefilled >= 0 for r in self.rows)
         fixed_length = not busy and all(self._req[self.rows[i].request_id][1].ignore_eos for i in live)
-        cap = self.check_interval * (8 if fixed_length else 1)
+        if busy:
+            self._quiet_bursts = 0
+        # rows that may stop on EOS: the burst grows to 2x and then 4x the check interval while nothing waits and
+        # no row has finished for a while (long generations with rare stops), and falls back when one does
+        grow = 1 << min(self._quiet_bursts // 2, 2)
+        cap = self.check_interval * (8 if fixed_length else (1 if busy else grow))
         steps = max(1, min([cap] + left)) if left else 0
         if steps:
             def short(k):
@@ -888,6 +894,7 @@ class RolloutEngine:
         # ---- retirement
         act = self.active[:B].cpu()
         done_rows = [i for i in live if act[i] == 0]
+        self._quiet_bursts = 0 if done_rows else self._quiet_bursts + 1
         if done_rows:
             gcount = self.gen_count[:B].cpu()
             idx = torch.tensor(done_rows, device=self.device)
