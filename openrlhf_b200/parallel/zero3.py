@@ -271,8 +271,8 @@ class Zero3Engine:
                     pieces.append((sp.offset, sp.offset + n, w))
         if self.on_gpu and self.world > 1 and OVERLAP:
             if self._side is None:
-                # high priority: the copy's few blocks are placed as soon as a slot frees up instead of queueing
-                # behind the waves of the compute stream's kernels
+                # high priority: the copy's blocks are placed as soon as slots free up instead of queueing behind the
+                # waves of the compute stream's kernels
                 self._side = torch.cuda.Stream(device=self.device, priority=-1)
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(self.device))
